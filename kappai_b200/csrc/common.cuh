@@ -1,0 +1,85 @@
+// Shared helpers of the kernel libraries: element types, conversions,
+// reductions and the launcher conventions.
+//
+// Conventions of every launcher (extern "C"):
+//   * pointers are raw device pointers, sizes are in elements, `stream` is a
+//     cudaStream_t passed as void*;
+//   * `dtype` selects the storage type of activations / weights / cache:
+//     0 = float32 (the true 32-bit path), 1 = bfloat16;
+//   * the return value is 0 or a cudaError_t / a negative argument error;
+//   * statistics (norm sums, softmax, conv sums, rotation) are float32 in both
+//     modes; only storage and matrix operands differ.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KP_DTYPE_F32 0
+#define KP_DTYPE_BF16 1
+
+#define KP_ERR_BAD_ARG (-22)
+#define KP_ERR_UNSUPPORTED (-95)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum with a fixed tree (the same for every launch shape, so a
+// row's statistic does not depend on what else is in the batch).  `smem` holds
+// at least 32 floats.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? smem[lane] : 0.f;
+    r = warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* smem) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarp) ? smem[lane] : -INFINITY;
+    r = warp_max(r);
+    return r;
+}
+
+static inline int kp_launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return (int)e;
+}
+
+#define KP_DISPATCH_DTYPE(dtype, T, ...)                 \
+    do {                                                 \
+        if ((dtype) == KP_DTYPE_F32) {                   \
+            typedef float T;                             \
+            __VA_ARGS__;                                 \
+        } else if ((dtype) == KP_DTYPE_BF16) {           \
+            typedef bf16 T;                              \
+            __VA_ARGS__;                                 \
+        } else {                                         \
+            return KP_ERR_BAD_ARG;                       \
+        }                                                \
+    } while (0)

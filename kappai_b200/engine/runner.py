@@ -1,0 +1,153 @@
+"""The step function: one batch of (request, its next tokens) from the cache.
+
+``ModelRunner`` owns the model, the device cache and the cache manager, and
+runs steps.  A step takes, for each request in it, that request's next tokens
+(a portion of a prompt, cut anywhere, or one decoded token) and the places
+among them whose logits are wanted; it runs only those tokens, as one batch,
+reading what earlier steps left in the cache, and returns the logits at the
+wanted places.  The reference's step function has the same contract
+(src/recipe/exec.c:704-758: embed rows, run layers, gather the rows that need
+logits, final norm, head).
+
+Everything above (scheduler, sampling, trace replay, the entry points) drives
+this one function; there is no second forward pass.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager, OutOfPages
+from ..cache.spec import PagedKVSpec, StateSpec
+from ..cache.storage import CacheStorage
+from ..config.registry import load_config
+from ..parts.base import BuildEnv
+from ..weights.loader import load_weights
+from .batch import Segment, StepContext, build_step_context
+from .model import Model
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    req: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def require_cuda(device) -> torch.device:
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise EngineError(f"kappai_b200 runs on a CUDA device only, not '{device}'")
+    if not torch.cuda.is_available():
+        raise EngineError("no CUDA device is available; kappai_b200 has no CPU path")
+    return device
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, dtype: str = "bfloat16", max_tokens: int = 4096,
+                 max_requests: int = 4, page_size: int = 64, max_model_len: Optional[int] = None,
+                 device="cuda:0"):
+        """``max_tokens``: how many tokens the live requests may hold together,
+        each request's count rounded up to a whole page; the page pools are
+        made for exactly this many.  ``max_requests``: state slots."""
+        if dtype not in DTYPES:
+            raise EngineError(f"dtype '{dtype}': expected bfloat16 or float32")
+        self.device = require_cuda(device)
+        self.dtype = DTYPES[dtype]
+        self.arch, self.config = load_config(model_dir)
+        self.spec = self.arch.build_spec(self.config)
+        if page_size < 1:
+            raise EngineError("page_size must be positive")
+        self.page_size = page_size
+        n_pages = max(1, -(-max_tokens // page_size))
+        self.max_model_len = min(self.spec.max_positions, max_model_len or n_pages * page_size)
+        torch.cuda.set_device(self.device)
+        env = BuildEnv(self.device, self.dtype, self.max_model_len)
+        self.model = Model(self.spec, env)
+        load_weights(self.model, model_dir)
+        specs = self.model.cache_specs()
+        borrowing = self.model.cache_borrowing()
+        group_keys = []
+        for s in specs:
+            if isinstance(s, PagedKVSpec) and s.group_key not in group_keys:
+                group_keys.append(s.group_key)
+        self.storage = CacheStorage(specs, borrowing, {gk: n_pages for gk in group_keys}, page_size,
+                                    max_requests, self.dtype, self.device)
+        self.cache = CacheManager({gk: (n_pages, page_size, self.storage.groups[gk].window)
+                                   for gk in group_keys}, max_requests)
+        self.group_page_size = {gk: page_size for gk in group_keys}
+        self.vocab_size = self.spec.vocab_size
+
+    # -- requests
+    def is_live(self, req: Hashable) -> bool:
+        return req in self.cache.requests
+
+    def length(self, req: Hashable) -> int:
+        return self.cache.requests[req].length
+
+    def end(self, req: Hashable) -> None:
+        """The request is finished: its pages and its slot are given back."""
+        self.cache.free(req)
+
+    def can_run(self, req: Hashable, n_new: int) -> bool:
+        """Would pages (and, for a new request, a slot) be there for ``n_new`` more tokens?"""
+        if req in self.cache.requests:
+            return self.cache.can_extend(req, self.cache.requests[req].length + n_new)
+        if not self.cache.can_admit():
+            return False
+        return all(-(-n_new // p.page_size) <= p.n_free for p in self.cache.pools.values())
+
+    # -- the step
+    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+        """Admit new requests, take pages for the new tokens and build the
+        step's tables.  Nothing is kept if any entry cannot be served."""
+        admitted, extended = [], []
+        try:
+            segs, after = [], []
+            for e in entries:
+                if len(e.tokens) < 1:
+                    raise EngineError(f"request {e.req!r}: no tokens in this step")
+                if e.req not in self.cache.requests:
+                    self.cache.admit(e.req)
+                    admitted.append(e.req)
+                rc = self.cache.requests[e.req]
+                new_len = rc.length + len(e.tokens)
+                if new_len > self.max_model_len:
+                    raise EngineError(f"request {e.req!r}: {new_len} tokens exceed the limit of "
+                                      f"{self.max_model_len} positions")
+                self.cache.extend(e.req, new_len)
+                extended.append(e.req)
+                segs.append(Segment(
+                    req=e.req, tokens=e.tokens, pos_start=rc.length, want=e.want, slot=rc.slot,
+                    block_tables={gk: self.cache.block_table(e.req, gk) for gk in self.group_page_size},
+                    token_slots={gk: self.cache.token_slots(e.req, gk, rc.length, len(e.tokens))
+                                 for gk in self.group_page_size}))
+                after.append((e.req, new_len))
+            ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len)
+            return ctx, after
+        except Exception:
+            for r in admitted:
+                self.cache.free(r)
+            # pages taken for requests that were already live stay with them: they
+            # cover positions the request will need anyway and are freed with it
+            raise
+
+    def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        return self.model.forward(ctx, self.storage.views)
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one step; float32 logits [wanted, vocab] on the device, in the
+        order of the entries and of their ``want`` (None if nothing is wanted)."""
+        ctx, after = self.prepare(entries)
+        logits = self.run(ctx)
+        for req, new_len in after:
+            self.cache.advance(req, new_len)
+        return logits

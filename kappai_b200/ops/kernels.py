@@ -1,0 +1,241 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks its tensors (device, dtype, layout), launches on the
+current CUDA stream and raises on any error.  There is no CPU path: a tensor
+that is not on a CUDA device is refused.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_STORE_F32, EPI_ACCUM_F32 = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dt}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name}: expected a CUDA tensor (kappai_b200 has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: expected a contiguous tensor")
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        if status == -95:
+            raise KernelError(f"{what}: size not supported by this kernel")
+        if status == -22:
+            raise KernelError(f"{what}: bad argument")
+        raise KernelError(f"{what}: CUDA error {status}")
+
+
+def _rows_2d(t: torch.Tensor, name: str) -> int:
+    """Leading dimension (in elements) of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name}: expected a 2-D tensor with contiguous rows")
+    return t.stride(0)
+
+
+# -------------------------------------------------------------------- rowwise
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
+    n, d = out.shape
+    if table.shape[1] != d or ids.numel() != n:
+        raise KernelError("embed_rows: shape mismatch")
+    lib = load_library("rowwise")
+    _check(lib.kp_embed_rows(_ptr(table), _ptr(ids), _ptr(out), n, d, ctypes.c_float(scale),
+                             dtype_code(table.dtype), _stream()), "embed_rows")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = rmsnorm(x[rows[r]] if rows is given else x[r])."""
+    _need(x, "x", torch.float32); _need(w, "w", torch.float32); _need(out, "out")
+    n, d = out.shape
+    if x.shape[1] != d or w.numel() != d:
+        raise KernelError("rmsnorm_rows: shape mismatch")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n:
+            raise KernelError("rmsnorm_rows: rows/out mismatch")
+    elif x.shape[0] != n:
+        raise KernelError("rmsnorm_rows: x/out mismatch")
+    lib = load_library("rowwise")
+    _check(lib.kp_rmsnorm_rows(_ptr(x), _ptr(w), _ptr(out), _ptr(rows), n, d, ctypes.c_float(eps),
+                               dtype_code(out.dtype), _stream()), "rmsnorm_rows")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    n, ff = out.shape
+    if gate_up.shape != (n, 2 * ff):
+        raise KernelError("swiglu: shape mismatch")
+    lib = load_library("rowwise")
+    _check(lib.kp_swiglu(_ptr(gate_up), _ptr(out), n, ff, dtype_code(out.dtype), _stream()), "swiglu")
+    return out
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    _need(src, "src"); _need(dst, "dst")
+    if src.numel() != dst.numel():
+        raise KernelError("cast: size mismatch")
+    lib = load_library("rowwise")
+    _check(lib.kp_cast(_ptr(src), _ptr(dst), ctypes.c_longlong(src.numel()), dtype_code(src.dtype),
+                       dtype_code(dst.dtype), _stream()), "cast")
+    return dst
+
+
+# ----------------------------------------------------------------------- gemm
+
+def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """out = a @ w.T (+ bias); with ``accumulate`` out (float32) += that."""
+    _need(a, "a", contiguous=False); _need(w, "w", a.dtype, contiguous=False); _need(out, "out", contiguous=False)
+    lda, ldw, ldc = _rows_2d(a, "a"), _rows_2d(w, "w"), _rows_2d(out, "out")
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm: bias size")
+    if accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("gemm: accumulation needs a float32 output")
+        epi = EPI_ACCUM_F32
+    elif out.dtype == a.dtype:
+        epi = EPI_STORE
+    elif out.dtype == torch.float32:
+        epi = EPI_STORE_F32
+    else:
+        raise KernelError("gemm: output dtype must be the operand dtype or float32")
+    lib = load_library("gemm_simt")
+    _check(lib.kp_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldc, epi,
+                               dtype_code(a.dtype), _stream()), "gemm_nt_simt")
+    return out
+
+
+# ------------------------------------------------------------------ shortconv
+
+def shortconv_forward(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                      row_seg: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor,
+                      seg_slot: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(p, "p", contiguous=False); _need(w, "w", torch.float32); _need(state, "state", torch.float32)
+    _need(out, "out", p.dtype, contiguous=False)
+    for t, nm in ((row_seg, "row_seg"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (seg_slot, "seg_slot")):
+        _need(t, nm, torch.int32)
+    n, d = out.shape
+    K = w.shape[1]
+    if p.shape != (n, 3 * d) or w.shape[0] != d or state.shape[1:] != (K - 1, d):
+        raise KernelError("shortconv_forward: shape mismatch")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    lib = load_library("shortconv")
+    _check(lib.kp_shortconv_forward(_ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(row_seg),
+                                    _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(out), _rows_2d(out, "out"),
+                                    n, d, K, dtype_code(p.dtype), _stream()), "shortconv_forward")
+    return out
+
+
+def shortconv_update_state(p: torch.Tensor, state: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor,
+                           seg_slot: torch.Tensor, n_seg: int) -> None:
+    _need(p, "p", contiguous=False); _need(state, "state", torch.float32)
+    d = p.shape[1] // 3
+    K = state.shape[1] + 1
+    if state.shape[2] != d:
+        raise KernelError("shortconv_update_state: shape mismatch")
+    lib = load_library("shortconv")
+    _check(lib.kp_shortconv_update_state(_ptr(p), _rows_2d(p, "p"), _ptr(state), _ptr(cu_rows), _ptr(seg_pos),
+                                         _ptr(seg_slot), n_seg, d, K, dtype_code(p.dtype), _stream()),
+           "shortconv_update_state")
+
+
+# ------------------------------------------------------------------ attention
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], eps: float,
+                    cos_tab: Optional[torch.Tensor], sin_tab: Optional[torch.Tensor], rotary_dim: int,
+                    interleaved: bool, positions: torch.Tensor, slot_map: Optional[torch.Tensor],
+                    q_out: Optional[torch.Tensor], cache: Optional[torch.Tensor], page_size: int, H: int, G: int,
+                    hd: int) -> Optional[torch.Tensor]:
+    """Norm + rotate q and k; write q to ``q_out`` and, if ``cache`` is given,
+    k and v to their pages.  ``cache`` is one layer's [pages, 2, G, page_size, hd].
+    With ``q_out`` None, q and k are changed in place and no cache is written."""
+    _need(qkv, "qkv", contiguous=False)
+    _need(positions, "positions", torch.int32)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (H + 2 * G) * hd:
+        raise KernelError("qk_norm_rope_kv: shape mismatch")
+    if q_out is not None:
+        _need(q_out, "q_out", qkv.dtype, contiguous=False)
+        if q_out.shape != (n, H * hd):
+            raise KernelError("qk_norm_rope_kv: q_out shape")
+    elif cache is not None:
+        raise KernelError("qk_norm_rope_kv: the in-place form writes no cache")
+    for t, nm in ((q_w, "q_w"), (k_w, "k_w")):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != hd:
+                raise KernelError(f"qk_norm_rope_kv: {nm} size")
+    if cos_tab is not None:
+        _need(cos_tab, "cos_tab", torch.float32); _need(sin_tab, "sin_tab", torch.float32)
+        if cos_tab.shape[1] != rotary_dim // 2:
+            raise KernelError("qk_norm_rope_kv: table width")
+    write_kv = cache is not None
+    if write_kv:
+        _need(cache, "cache", qkv.dtype); _need(slot_map, "slot_map", torch.int32)
+        if tuple(cache.shape[1:]) != (2, G, page_size, hd):
+            raise KernelError(f"qk_norm_rope_kv: cache layout {tuple(cache.shape)}")
+    lib = load_library("qkrope")
+    _check(lib.kp_qk_norm_rope_kv(_ptr(qkv), _rows_2d(qkv, "qkv"), _ptr(q_w), _ptr(k_w), ctypes.c_float(eps),
+                                  _ptr(cos_tab), _ptr(sin_tab), rotary_dim, int(interleaved), _ptr(positions),
+                                  _ptr(slot_map), _ptr(q_out), 0 if q_out is None else _rows_2d(q_out, "q_out"), _ptr(cache),
+                                  page_size,
+                                  n, H, G, hd, int(write_kv), dtype_code(qkv.dtype), _stream()), "qk_norm_rope_kv")
+    return q_out
+
+
+def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
+                   positions: torch.Tensor, out: torch.Tensor, scale: float, window: Optional[int],
+                   page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+    _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
+    _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
+    _need(positions, "positions", torch.int32)
+    n = q.shape[0]
+    if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
+        raise KernelError("attention_rows: shape mismatch")
+    lib = load_library("attention")
+    _check(lib.kp_attention_rows(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
+                                 _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"),
+                                 ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
+                                 dtype_code(q.dtype), _stream()), "attention_rows")
+    return out

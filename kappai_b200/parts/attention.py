@@ -1,0 +1,107 @@
+"""Grouped-query attention over the paged cache.
+
+``q,k,v = h Wq^T, h Wk^T, h Wv^T`` (run as one product against the rows
+[Wq; Wk; Wv], as the reference does with ``--fuse qkv``, src/model.c:1440-1448);
+optional per-head RMSNorm of q and k with one weight [head_dim] shared by the
+heads, before the rotation (src/models/lfm.c:36-39); position encoding; keys and
+values into the cache; causal softmax attention with ``scale`` over the keys
+``max(0, p - window + 1) .. p`` (src/backend/cpu/scalar/core.c:383-433);
+``out = attn Wo^T`` added to the residual (src/models/lfm.c:51,
+src/recipe/builders.c:381).
+
+Sizes and constants (params): hidden_size, num_heads, num_kv_heads, head_dim,
+scale, qk_norm_eps (None: no q/k norm), window (None: all keys), position (a
+``position`` PartSpec), bias.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..cache.spec import PagedKVSpec
+from ..config.schema import ConfigError, PartSpec
+from ..ops import kernels as K
+from ..ops.linear import linear
+from .base import Part, WeightSpec, make_part, register_part
+
+
+class Attention(Part):
+    category = "mixer"
+
+    def __init__(self, params, env):
+        super().__init__(params, env)
+        self.d = int(self._p("hidden_size"))
+        self.H = int(self._p("num_heads"))
+        self.G = int(self._p("num_kv_heads"))
+        self.hd = int(self._p("head_dim"))
+        self.scale = float(self._p("scale"))
+        eps = self._p("qk_norm_eps", None)
+        self.qk_norm_eps: Optional[float] = None if eps is None else float(eps)
+        self.window: Optional[int] = self._p("window", None)
+        self.bias = bool(self._p("bias", False))
+        if self.H < 1 or self.G < 1 or self.H % self.G:
+            raise ConfigError(f"attention: num_heads={self.H} must be a multiple of num_kv_heads={self.G}")
+        if self.hd % 16 or not (16 <= self.hd <= 256):
+            raise ConfigError(f"attention: head_dim={self.hd} is not supported by the kernels "
+                              "(a multiple of 16 from 16 to 256)")
+        pos = self._p("position", None)
+        if pos is None:
+            pos = PartSpec("none")
+        elif isinstance(pos, dict):
+            pos = PartSpec(**pos)
+        self.position = make_part("position", pos, env)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        d, H, G, hd = self.d, self.H, self.G, self.hd
+        s = {"q_proj.weight": WeightSpec((H * hd, d)), "k_proj.weight": WeightSpec((G * hd, d)),
+             "v_proj.weight": WeightSpec((G * hd, d)), "out_proj.weight": WeightSpec((d, H * hd))}
+        if self.qk_norm_eps is not None:
+            s["q_norm.weight"] = WeightSpec((hd,), "norm")
+            s["k_norm.weight"] = WeightSpec((hd,), "norm")
+        if self.bias:
+            for n, sz in (("q_proj", H * hd), ("k_proj", G * hd), ("v_proj", G * hd), ("out_proj", d)):
+                s[n + ".bias"] = WeightSpec((sz,), "bias")
+        return s
+
+    def bind(self, w):
+        self.w_qkv = torch.cat([w["q_proj.weight"], w["k_proj.weight"], w["v_proj.weight"]], 0).contiguous()
+        self.w_o = w["out_proj.weight"].contiguous()
+        self.b_qkv = self.b_o = None
+        if self.bias:
+            self.b_qkv = torch.cat([w[n + ".bias"].float() for n in ("q_proj", "k_proj", "v_proj")]).contiguous()
+            self.b_o = w["out_proj.bias"].float().contiguous()
+        self.q_w = self.k_w = None
+        if self.qk_norm_eps is not None:
+            self.q_w = w["q_norm.weight"].float().contiguous()
+            self.k_w = w["k_norm.weight"].float().contiguous()
+
+    def cache_spec(self):
+        return PagedKVSpec(self.G, self.hd, self.window)
+
+    def forward(self, h, residual, ctx, cache):
+        """``cache``: a :class:`~kappai_b200.cache.storage.KVLayerView`."""
+        H, G, hd = self.H, self.G, self.hd
+        view = ctx.paged[cache.group]
+        qkv = linear(h, self.w_qkv, self.b_qkv)
+        q = torch.empty((ctx.n_rows, H * hd), dtype=qkv.dtype, device=qkv.device)
+        kv_out = cache.tensor if cache.writes else None
+        if hasattr(self.position, "fused_rotary"):
+            cos, sin, rot, inter = self.position.fused_rotary()
+            K.qk_norm_rope_kv(qkv, self.q_w, self.k_w, self.qk_norm_eps or 0.0, cos, sin, rot, inter,
+                              ctx.positions, view.slot_map, q, kv_out, view.page_size, H, G, hd)
+        else:
+            # a position encoding of its own: norm in place, let it change q and k, then scatter
+            if self.q_w is not None:
+                K.qk_norm_rope_kv(qkv, self.q_w, self.k_w, self.qk_norm_eps, None, None, 0, False, ctx.positions,
+                                  None, None, None, view.page_size, H, G, hd)
+            self.position.apply(qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], ctx)
+            K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q, kv_out,
+                              view.page_size, H, G, hd)
+        o = torch.empty_like(q)
+        K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
+                         self.window, view.page_size, H, G, hd)
+        linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
+
+
+register_part("mixer", "attention", Attention)

@@ -1,0 +1,42 @@
+"""Two tiny LFM2 configurations that differ in every size and option, and
+helpers that write them as model folders with random weights."""
+import os
+import tempfile
+
+TINY_A = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=256, hidden_size=64, num_hidden_layers=4,
+    num_attention_heads=4, num_key_value_heads=2,
+    layer_types=["conv", "full_attention", "conv", "full_attention"],
+    max_position_embeddings=128, norm_eps=1e-5, conv_L_cache=3, conv_bias=False,
+    block_ff_dim=192, block_auto_adjust_ff_dim=False, rope_theta=10000.0, tie_embedding=True)
+TINY_A_SEED = 0
+
+TINY_B = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=512, hidden_size=96, num_hidden_layers=6,
+    num_attention_heads=6, num_key_value_heads=3,
+    layer_types=["full_attention", "conv", "conv", "full_attention", "conv", "conv"],
+    max_position_embeddings=256, norm_eps=1e-6, conv_L_cache=4, conv_bias=True,
+    block_ff_dim=384, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=32,
+    rope_theta=1000000.0, tie_embedding=False)
+TINY_B_SEED = 1
+
+# a third shape: sizes that are no power of two, head_dim 48 given explicitly (not hidden/heads),
+# one kv head, an odd vocabulary, K = 2
+TINY_C = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=331, hidden_size=120, num_hidden_layers=3,
+    num_attention_heads=5, num_key_value_heads=1, head_dim=48,
+    layer_types=["conv", "full_attention", "full_attention"],
+    max_position_embeddings=512, norm_eps=1e-5, conv_L_cache=2, conv_bias=False,
+    block_ff_dim=200, block_auto_adjust_ff_dim=False, rope_theta=50000.0, tie_embedding=True)
+TINY_C_SEED = 7
+
+CONFIGS = {"A": (TINY_A, TINY_A_SEED), "B": (TINY_B, TINY_B_SEED), "C": (TINY_C, TINY_C_SEED)}
+
+
+def make_model_dir(name, root=None):
+    from kappai_b200.weights import write_random_model
+
+    cfg, seed = CONFIGS[name]
+    d = tempfile.mkdtemp(prefix=f"tiny_{name}_", dir=root)
+    write_random_model(cfg, d, seed)
+    return d
