@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 # the kernel libraries of this package, in csrc/
-LIBRARIES = ["rowwise", "gemm_simt", "shortconv", "qkrope", "attention"]
+LIBRARIES = ["rowwise", "gemm_simt", "shortconv", "qkrope", "attention", "sampling"]
 
 
 class KernelBuildError(RuntimeError):
