@@ -161,4 +161,5 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         max_context=max(s.pos_start + len(s.tokens) for s in segments),
         decode_only=all(len(s.tokens) == 1 for s in segments))
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
+    ctx.h2d_bytes = flat.numel() * 4
     return ctx

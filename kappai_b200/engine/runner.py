@@ -85,6 +85,7 @@ class ModelRunner:
                                    for gk in group_keys}, max_requests)
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
+        self.last_h2d_bytes = 0
 
     # -- requests
     def is_live(self, req: Hashable) -> bool:
@@ -147,6 +148,7 @@ class ModelRunner:
         """Run one step; float32 logits [wanted, vocab] on the device, in the
         order of the entries and of their ``want`` (None if nothing is wanted)."""
         ctx, after = self.prepare(entries)
+        self.last_h2d_bytes = ctx.h2d_bytes
         logits = self.run(ctx)
         for req, new_len in after:
             self.cache.advance(req, new_len)

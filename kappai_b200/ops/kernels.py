@@ -17,6 +17,9 @@ F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_ACCUM_F32 = 0, 1, 2
 
 
+LAUNCHES = [0]      # kernel launchers called so far (a launcher may launch more than one kernel)
+
+
 class KernelError(RuntimeError):
     pass
 
@@ -47,6 +50,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
 
 
 def _check(status: int, what: str) -> None:
+    LAUNCHES[0] += 1
     if status != 0:
         if status == -95:
             raise KernelError(f"{what}: size not supported by this kernel")
