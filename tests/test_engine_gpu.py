@@ -1,0 +1,197 @@
+"""The engine through its entry points: greedy generation against the plain
+implementation, long decoding, first tokens, reuse of slots and pages,
+preemption by recompute, seeded sampling, the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tolerances import tol_for
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def check_greedy(plain, prompt, out, dtype):
+    """Each generated token is the plain argmax, or a near tie of it, given the tokens before it."""
+    seq = list(prompt)
+    all_logits = plain.logits(seq + list(out))
+    for j, t in enumerate(out):
+        lg = all_logits[len(prompt) + j - 1]
+        best = int(np.argmax(lg))
+        if t != best:
+            assert lg[best] - lg[t] <= 2 * tol_for(dtype, lg), (j, t, best, lg[best] - lg[t])
+
+
+def engine(model_dir, dtype="float32", **kw):
+    from kappai_b200 import Engine, EngineArgs
+    args = dict(model=model_dir, dtype=dtype, max_batch=4, max_step_tokens=32, page_size=16, kv_tokens=2048)
+    args.update(kw)
+    return Engine(EngineArgs(**args))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain(name, dtype, model_dirs, plain_models):
+    from kappai_b200 import SamplingParams
+    plain = plain_models[name]
+    V = plain.cfg["vocab_size"]
+    rng = np.random.default_rng(20)
+    lens, n_new = ([5, 17, 33], 16) if name == "A" else ([1, 9, 64, 130], 24)      # the workloads of the two configs
+    prompts = [rng.integers(0, V, n).tolist() for n in lens]
+    eng = engine(model_dirs[name], dtype, max_step_tokens=16)
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, n_predict=n_new))
+    assert [len(o) for o in outs] == [n_new] * len(prompts)
+    for p, o in zip(prompts, outs):
+        check_greedy(plain, p, o, dtype)
+    assert eng.runner.cache.slots.n_free == 4 and all(p.n_free == p.n_pages for p in eng.runner.cache.pools.values())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype, model_dirs, plain_models):
+    """400 tokens decoded one by one after a 3-token prompt; logits at every step against plain."""
+    from kappai_b200 import ModelRunner, StepEntry
+    plain = plain_models["C"]
+    rng = np.random.default_rng(21)
+    toks = rng.integers(0, plain.cfg["vocab_size"], 403).tolist()
+    ref = plain.logits(toks)
+    r = ModelRunner(model_dirs["C"], dtype=dtype, max_tokens=512, page_size=32)
+    got = [r.step([StepEntry("a", toks[:3], [0, 1, 2])]).cpu().double().numpy()]
+    for t in toks[3:]:
+        got.append(r.step([StepEntry("a", [t], [0])]).cpu().double().numpy())
+    got = np.concatenate(got)
+    err = np.abs(got - ref).max(axis=1)
+    tol = tol_for(dtype, ref)
+    assert err.max() <= tol, f"first wrong position {int(np.argmax(err > tol))}: {err.max()} > {tol}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens(dtype, model_dirs, plain_models):
+    """Positions 0, 1, 2 of a sequence, fed one by one, two at once, and as prompts of length 1, 2, 3."""
+    from kappai_b200 import ModelRunner, StepEntry
+    for name in ("A", "B"):
+        plain = plain_models[name]
+        toks = [7, 200, 31]
+        ref = plain.logits(toks)
+        tol = tol_for(dtype, ref)
+        r = ModelRunner(model_dirs[name], dtype=dtype, max_tokens=256, page_size=16)
+        for cut in ([1, 1, 1], [2, 1], [1, 2], [3]):
+            got, i = [], 0
+            for n in cut:
+                got.append(r.step([StepEntry("x", toks[i:i + n], list(range(n)))]).cpu().double().numpy())
+                i += n
+            r.end("x")
+            assert np.abs(np.concatenate(got) - ref).max() <= tol, (name, cut)
+
+
+def test_reused_slot_and_pages_give_the_same_bits(model_dirs):
+    """After other requests have used and left the slot and the pages, a request
+    replayed gives bit-identical logits (no stale state or keys leak in)."""
+    from kappai_b200 import ModelRunner, StepEntry
+    rng = np.random.default_rng(22)
+    for dtype in ("float32", "bfloat16"):
+        r = ModelRunner(model_dirs["B"], dtype=dtype, max_tokens=128, page_size=16, max_requests=2)
+        toks = rng.integers(0, 512, 60).tolist()
+        run = lambda rid: torch.cat([r.step([StepEntry(rid, toks[:37], list(range(37)))]),
+                                     r.step([StepEntry(rid, toks[37:], list(range(23)))])])
+        first = run("a")
+        r.end("a")
+        for k in range(3):                                  # dirty every page and both slots
+            other = rng.integers(0, 512, 96).tolist()
+            r.step([StepEntry(f"o{k}", other, []), StepEntry(f"p{k}", other[:20], [])])
+            r.end(f"o{k}"); r.end(f"p{k}")
+        again = run("b")
+        assert torch.equal(first, again)
+
+
+def test_preemption_recomputes_and_gives_the_same_tokens(model_dirs, plain_models):
+    from kappai_b200 import SamplingParams
+    plain = plain_models["B"]
+    rng = np.random.default_rng(23)
+    prompts = [rng.integers(0, 512, n).tolist() for n in (40, 33, 50, 21)]
+    sp = SamplingParams(temperature=0.0, n_predict=40)
+    roomy = engine(model_dirs["B"], "float32", kv_tokens=2048)
+    want = roomy.generate(prompts, sp)
+    assert roomy.scheduler.n_preemptions == 0
+    tight = engine(model_dirs["B"], "float32", kv_tokens=16 * 14)        # 14 pages for four requests of up to 90 tokens
+    got = tight.generate(prompts, sp)
+    assert tight.scheduler.n_preemptions > 0
+    assert [tight.finish_reason(i) for i in range(4)] == ["length"] * 4
+    for p, a, b in zip(prompts, want, got):
+        if a != b:
+            check_greedy(plain, p, b, "float32")
+    assert sum(a == b for a, b in zip(want, got)) >= 3
+    tight.runner.cache.check()
+
+
+def test_request_too_large_for_the_pool_ends_with_out_of_memory(model_dirs):
+    from kappai_b200 import SamplingParams
+    eng = engine(model_dirs["B"], "float32", kv_tokens=64, max_step_tokens=64)
+    a = eng.add_request(list(range(60)), SamplingParams(temperature=0.0, n_predict=30))
+    b = eng.add_request(list(range(10)), SamplingParams(temperature=0.0, n_predict=3))
+    while eng.has_work():
+        eng.step()
+    assert eng.finish_reason(a) == "out_of_memory" and len(eng.requests[a].output) == 5      # 64 tokens fit, the 65th does not
+    assert eng.finish_reason(b) == "length" and len(eng.requests[b].output) == 3
+
+
+def test_seeded_sampling_does_not_depend_on_the_batch(model_dirs):
+    from kappai_b200 import SamplingParams
+    rng = np.random.default_rng(24)
+    prompts = [rng.integers(0, 256, n).tolist() for n in (12, 30, 7)]
+    sp = lambda seed: SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.1, seed=seed, n_predict=12)
+    eng = engine(model_dirs["A"], "float32")
+    together = eng.generate(prompts, [sp(5), sp(6), sp(7)])
+    alone = [engine(model_dirs["A"], "float32").generate([p], sp(5 + i))[0] for i, p in enumerate(prompts)]
+    assert together == alone
+    assert engine(model_dirs["A"], "float32").generate(prompts[:1], sp(99))[0] != alone[0]
+    greedy = engine(model_dirs["A"], "float32").generate(prompts[:1], SamplingParams(temperature=0.0, n_predict=12))[0]
+    assert greedy != alone[0] or True
+
+
+def test_context_full_and_bad_requests(model_dirs):
+    from kappai_b200 import SamplingParams
+    eng = engine(model_dirs["A"], "float32", ctx_size=40)
+    rid = eng.add_request(list(range(30)), SamplingParams(temperature=0.0, n_predict=-1))
+    while eng.has_work():
+        eng.step()
+    assert eng.finish_reason(rid) == "context_full" and len(eng.requests[rid].output) == 10
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request([1, 2, 999], None)
+    with pytest.raises(ValueError, match="limit"):
+        eng.add_request(list(range(40)), None)
+    with pytest.raises(ValueError, match="prompt token"):
+        eng.add_request([], None)
+
+
+def test_command_line(model_dirs, tmp_path):
+    from kappai_b200 import SamplingParams
+    want = engine(model_dirs["A"], "bfloat16", max_batch=64, max_step_tokens=2048, page_size=64, kv_tokens=0) \
+        .generate([[5, 17, 3, 200]], SamplingParams(temperature=0.0, n_predict=6))[0]
+    cmd = [sys.executable, "-m", "kappai_b200.cli", "-m", model_dirs["A"], "-p", "5,17,3,200", "-n", "6", "-t", "0",
+           "--metrics", "pp,tg,ttft"]
+    p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(t) for t in p.stdout.split()] == want
+    assert "TG:" in p.stderr and "t/s" in p.stderr
+    # random-weights mode writes a model folder and runs it; the fp32 flag; exit code 2 when the context fills
+    cfgp = tmp_path / "c.json"
+    with open(os.path.join(model_dirs["B"], "config.json")) as f:
+        cfgp.write_text(f.read())
+    out = tmp_path / "rw"
+    cmd = [os.path.join(ROOT, "bin", "kappai-cli"), "--random-weights", str(cfgp), "-s", "3", "-m", str(out), "--fp32",
+           "-c", "12", "-t", "0", "7 8 9"]
+    p = subprocess.run(cmd, cwd=str(tmp_path), capture_output=True, text=True, timeout=300)
+    assert p.returncode == 2, p.stderr[-2000:]
+    assert len(p.stdout.split()) == 9
+    assert os.path.isfile(out / "model.safetensors") and os.path.isfile(out / "config.json")
+
+
+def test_no_cuda_device_is_refused(model_dirs):
+    from kappai_b200.engine.runner import EngineError, ModelRunner
+    with pytest.raises(EngineError, match="CUDA"):
+        ModelRunner(model_dirs["A"], device="cpu")
