@@ -1,0 +1,238 @@
+// Split-KV attention for rows that each read a long cache (decode steps and
+// very short portions): the keys of one (row, kv head) are cut into chunks of
+// 256 at multiples of 256 of the absolute key index; one CTA per (chunk, kv
+// head, row) computes, for all R = H/G query heads that share the kv head, the
+// chunk's scores, its maximum m, its sum l of exp(s - m) and the unnormalised
+// sum of exp(s - m) V; a second kernel merges the chunks of a row in order.
+// Same formulas as attention.cu (src/backend/cpu/scalar/core.c:383-433); the
+// chunk grid does not depend on the batch, so neither does the result.
+//
+// Scratch (global memory beyond inputs and outputs, given by the caller):
+//   part_acc [n_rows][H][n_chunks][hd] float, part_ml [n_rows][H][n_chunks][2] float.
+// Only the chunks that intersect a row's key range are written and read.
+#include "common.cuh"
+
+#define AD_CHUNK 256
+#define AD_THREADS 256
+#define AD_RMAX 8
+#define KP_MAX_HEAD_DIM 256
+
+template <typename T> struct Vec16;
+template <> struct Vec16<bf16> { static constexpr int N = 8; };
+template <> struct Vec16<float> { static constexpr int N = 4; };
+
+template <typename T>
+__device__ __forceinline__ void unpack16(const uint4& v, float* f);
+template <>
+__device__ __forceinline__ void unpack16<bf16>(const uint4& v, float* f) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+template <>
+__device__ __forceinline__ void unpack16<float>(const uint4& v, float* f) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y); f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+
+__device__ __forceinline__ void key_range(int pos, int window, int& k_lo, int& k_hi) {
+    k_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    k_hi = pos;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, const int* __restrict__ block_table,
+                  int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
+                  float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
+                  int page_size, int H, int G, int hd) {
+    extern __shared__ float smem[];
+    const int R = H / G;
+    float* qs = smem;                              // [R][hd]
+    float* ps = qs + R * hd;                       // [R][AD_CHUNK]
+    float* red = ps + R * AD_CHUNK;                // [n_slices][R][hd]  (also used for the small reductions)
+    __shared__ float wred[AD_THREADS / 32][AD_RMAX];
+    __shared__ float stat_m[AD_RMAX], stat_l[AD_RMAX];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int chunk = blockIdx.x, g = blockIdx.y, row = blockIdx.z;
+    int k_lo, k_hi;
+    key_range(positions[row], window, k_lo, k_hi);
+    const int c0 = chunk * AD_CHUNK;
+    if (c0 > k_hi || c0 + AD_CHUNK - 1 < k_lo) return;          // the chunk holds none of this row's keys
+    const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
+    const size_t page_stride = (size_t)2 * G * page_size * hd;
+    const size_t k_off = (size_t)g * page_size * hd, v_off = ((size_t)G + g) * page_size * hd;
+
+    for (int i = tid; i < R * hd; i += AD_THREADS)
+        qs[i] = to_f32(q[(size_t)row * ldq + (size_t)(g * R) * hd + i]);
+    __syncthreads();
+
+    // scores: one key a thread, all R heads
+    const int key = c0 + tid;
+    const bool valid = key >= k_lo && key <= k_hi;
+    float s[AD_RMAX];
+#pragma unroll
+    for (int r = 0; r < AD_RMAX; r++) s[r] = 0.f;
+    if (valid) {
+        const T* kp = cache + (size_t)bt[key / page_size] * page_stride + k_off + (size_t)(key % page_size) * hd;
+        constexpr int VN = Vec16<T>::N;
+        for (int i = 0; i < hd; i += VN) {
+            float kf[VN];
+            unpack16<T>(*reinterpret_cast<const uint4*>(kp + i), kf);
+#pragma unroll
+            for (int r = 0; r < AD_RMAX; r++) {
+                if (r < R) {
+                    const float* qr = qs + r * hd + i;
+#pragma unroll
+                    for (int j = 0; j < VN; j++) s[r] = fmaf(qr[j], kf[j], s[r]);
+                }
+            }
+        }
+    }
+    // per head: chunk maximum, exp, chunk sum
+#pragma unroll
+    for (int r = 0; r < AD_RMAX; r++) {
+        if (r < R) {
+            s[r] = valid ? s[r] * scale : -INFINITY;
+            const float m = warp_max(s[r]);
+            if (lane == 0) wred[warp][r] = m;
+        }
+    }
+    __syncthreads();
+    if (tid < R) {
+        float m = wred[0][tid];
+        for (int w = 1; w < AD_THREADS / 32; w++) m = fmaxf(m, wred[w][tid]);
+        stat_m[tid] = m;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < AD_RMAX; r++) {
+        if (r < R) {
+            const float p = valid ? expf(s[r] - stat_m[r]) : 0.f;
+            ps[r * AD_CHUNK + tid] = p;
+            const float l = warp_sum(p);
+            if (lane == 0) wred[warp][r] = l;
+        }
+    }
+    __syncthreads();
+    if (tid < R) {
+        float l = 0.f;
+        for (int w = 0; w < AD_THREADS / 32; w++) l += wred[w][tid];
+        stat_l[tid] = l;
+    }
+
+    // P V: thread = (pair of dims, slice of keys); slices are summed in order afterwards
+    const int pairs = hd >> 1;
+    const int n_slices = AD_THREADS / pairs;
+    const int per = (AD_CHUNK + n_slices - 1) / n_slices;
+    const int pair = tid % pairs, slice = tid / pairs;
+    float acc[AD_RMAX][2];
+#pragma unroll
+    for (int r = 0; r < AD_RMAX; r++) acc[r][0] = acc[r][1] = 0.f;
+    if (slice < n_slices) {
+        const int kk_lo = max(slice * per, k_lo - c0), kk_hi = min(min((slice + 1) * per, AD_CHUNK) - 1, k_hi - c0);
+        for (int kk = kk_lo; kk <= kk_hi; kk++) {
+            const int key2 = c0 + kk;
+            const T* vp = cache + (size_t)bt[key2 / page_size] * page_stride + v_off +
+                          (size_t)(key2 % page_size) * hd + 2 * pair;
+            const float v0 = to_f32(vp[0]), v1 = to_f32(vp[1]);
+#pragma unroll
+            for (int r = 0; r < AD_RMAX; r++) {
+                if (r < R) {
+                    const float p = ps[r * AD_CHUNK + kk];
+                    acc[r][0] = fmaf(p, v0, acc[r][0]);
+                    acc[r][1] = fmaf(p, v1, acc[r][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < AD_RMAX; r++) {
+            if (r < R) {
+                red[((size_t)slice * R + r) * hd + 2 * pair] = acc[r][0];
+                red[((size_t)slice * R + r) * hd + 2 * pair + 1] = acc[r][1];
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < R * hd; e += AD_THREADS) {
+        const int r = e / hd, d = e % hd;
+        float v = 0.f;
+        for (int sl = 0; sl < n_slices; sl++) v += red[((size_t)sl * R + r) * hd + d];
+        part_acc[(((size_t)row * H + g * R + r) * n_chunks + chunk) * hd + d] = v;
+    }
+    if (tid < R) {
+        float* ml = part_ml + (((size_t)row * H + g * R + tid) * n_chunks + chunk) * 2;
+        ml[0] = stat_m[tid];
+        ml[1] = stat_l[tid];
+    }
+}
+
+template <typename T>
+__global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                  const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
+                                  int window, int H, int hd) {
+    const int h = blockIdx.x, row = blockIdx.y;
+    int k_lo, k_hi;
+    key_range(positions[row], window, k_lo, k_hi);
+    const int c_lo = k_lo / AD_CHUNK, c_hi = k_hi / AD_CHUNK;
+    const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
+    float m = -INFINITY;
+    for (int c = c_lo; c <= c_hi; c++) m = fmaxf(m, ml[2 * c]);
+    float l = 0.f;
+    for (int c = c_lo; c <= c_hi; c++) l += ml[2 * c + 1] * expf(ml[2 * c] - m);
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const float* pa = part_acc + ((size_t)row * H + h) * n_chunks * hd;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        float v = 0.f;
+        for (int c = c_lo; c <= c_hi; c++) v = fmaf(pa[(size_t)c * hd + d], expf(ml[2 * c] - m), v);
+        out[(size_t)row * ldo + (size_t)h * hd + d] = from_f32<T>(v * inv);
+    }
+}
+
+static size_t split_smem_bytes(int R, int hd) {
+    const int pairs = hd / 2;
+    const int n_slices = AD_THREADS / pairs;
+    return sizeof(float) * ((size_t)R * hd + (size_t)R * AD_CHUNK + (size_t)n_slices * R * hd);
+}
+
+extern "C" {
+
+// Elements of float scratch the split kernel needs for these sizes (part_acc then part_ml).
+long long kp_attention_split_scratch(int n_rows, int H, int hd, int n_chunks) {
+    return (long long)n_rows * H * n_chunks * (hd + 2);
+}
+
+// n_chunks: chunks of 256 keys the grid covers; must reach the largest position in the batch.
+int kp_attention_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                       const int* row_seg, const int* positions, void* out, int ldo, float* scratch, int n_chunks,
+                       float scale, int window, int page_size, int n, int H, int G, int hd, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (hd < 16 || hd > KP_MAX_HEAD_DIM || (hd & 15)) return KP_ERR_UNSUPPORTED;
+    if (G < 1 || H % G != 0 || H / G > AD_RMAX || page_size < 1 || n_chunks < 1) return KP_ERR_UNSUPPORTED;
+    if (n > 65535 || G > 65535) return KP_ERR_UNSUPPORTED;
+    const int R = H / G;
+    const size_t smem = split_smem_bytes(R, hd);
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_chunks, G, n);
+    dim3 mgrid(H, n);
+    const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
+    KP_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        attn_split_kernel<T><<<grid, AD_THREADS, smem, s>>>((const T*)q, ldq, (const T*)cache, block_table, max_blocks,
+                                                            row_seg, positions, part_acc, part_ml, n_chunks, scale,
+                                                            window, page_size, H, G, hd);
+        attn_merge_kernel<T><<<mgrid, mthreads, 0, s>>>(part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window,
+                                                        H, hd);
+    });
+    return kp_launch_status();
+}
+
+}  // extern "C"

@@ -243,3 +243,82 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
                                  ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
                                  dtype_code(q.dtype), _stream()), "attention_rows")
     return out
+
+
+SPLIT_CHUNK = 256          # keys a chunk of the split-KV attention
+SPLIT_MAX_RATIO = 8        # query heads per kv head it takes
+
+
+def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
+    """Float elements of scratch that :func:`attention_split` needs."""
+    return n_rows * H * n_chunks * (hd + 2)
+
+
+def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
+                    positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
+                    window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+    """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
+    must cover the largest position of the batch; ``scratch`` is float32."""
+    _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
+    _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
+    _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
+    n = q.shape[0]
+    if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
+        raise KernelError("attention_split: shape mismatch")
+    if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
+        raise KernelError("attention_split: scratch too small")
+    lib = load_library("attention_decode")
+    _check(lib.kp_attention_split(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
+                                  _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
+                                  n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
+                                  dtype_code(q.dtype), _stream()), "attention_split")
+    LAUNCHES[0] += 1
+    return out
+
+
+# ---------------------------------------------------------------- skinny gemm
+
+SKINNY_MAX_M = 64
+EPI_SWIGLU = 3
+
+
+def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Can the weight-streaming kernel take this product?"""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[0] <= SKINNY_MAX_M
+            and a.shape[1] % 32 == 0 and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+    """out = a @ w.T (+ bias) for up to 64 rows of bfloat16 ``a``.  With
+    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
+    _need(out, "out", contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or out.shape != (M, n_out):
+        raise KernelError(f"gemm_skinny: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm_skinny: bias size")
+    if swiglu:
+        if out.dtype != torch.bfloat16:
+            raise KernelError("gemm_skinny: the SwiGLU epilogue writes bfloat16")
+        epi = EPI_SWIGLU
+    elif accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("gemm_skinny: accumulation needs a float32 output")
+        epi = EPI_ACCUM_F32
+    elif out.dtype == torch.bfloat16:
+        epi = EPI_STORE
+    elif out.dtype == torch.float32:
+        epi = EPI_STORE_F32
+    else:
+        raise KernelError("gemm_skinny: output dtype")
+    lib = load_library("gemm_skinny")
+    _check(lib.kp_gemm_skinny(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                              _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_skinny")
+    return out

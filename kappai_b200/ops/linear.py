@@ -1,8 +1,9 @@
 """Matrix products ``out = a @ w.T (+ bias)`` with W row-major [out, in].
 
 One door for every product of the model; it picks the kernel by dtype and
-shape.  float32 operands always run the CUDA-core float32 kernel (the true
-32-bit path).  The product is this package's own kernel in every case; no
+shape: float32 operands always run the CUDA-core float32 kernel (the true
+32-bit path); bfloat16 products of up to 64 rows run the weight-streaming
+kernel (decode steps).  The product is this package's own kernel in every case; no
 library matrix product is called.
 """
 from __future__ import annotations
@@ -33,4 +34,18 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             tmp = K.gemm_nt_simt(a32, w, torch.empty((M, N), dtype=torch.float32, device=a.device), bias)
             return K.cast(tmp, out)
         raise K.KernelError(f"linear: operand dtypes {a.dtype} and {w.dtype} do not go together")
+    if K.skinny_ok(a, w):
+        return K.gemm_skinny(a, w, out, bias, accumulate)
     return K.gemm_nt_simt(a, w, out, bias, accumulate)
+
+
+def linear_swiglu(a: torch.Tensor, w_gate_up: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``silu(a @ Wg.T) * (a @ Wu.T)`` with ``w_gate_up = [Wg; Wu]``; one fused
+    kernel where there is one for the shape, else product then activation.
+    Gate and up are rounded to the storage type before the activation either way."""
+    ff = w_gate_up.shape[0] // 2
+    act = torch.empty((a.shape[0], ff), dtype=a.dtype, device=a.device)
+    if K.skinny_ok(a, w_gate_up):
+        return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True)
+    gu = linear(a, w_gate_up, bias)
+    return K.swiglu(gu, act)

@@ -26,6 +26,9 @@ from ..ops.linear import linear
 from .base import Part, WeightSpec, make_part, register_part
 
 
+SPLIT_MAX_SEG_LEN = 4      # steps whose longest segment is at most this use the split-KV kernel
+
+
 class Attention(Part):
     category = "mixer"
 
@@ -99,8 +102,19 @@ class Attention(Part):
             K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q, kv_out,
                               view.page_size, H, G, hd)
         o = torch.empty_like(q)
-        K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
-                         self.window, view.page_size, H, G, hd)
+        if ctx.max_seg_len <= SPLIT_MAX_SEG_LEN and H // G <= K.SPLIT_MAX_RATIO:
+            # rows that each read a long cache (decode): split the keys over many CTAs
+            n_chunks = ctx.attn_chunks if getattr(ctx, "attn_chunks", None) else -(-ctx.max_context // K.SPLIT_CHUNK)
+            need = K.attention_split_scratch(ctx.n_rows, H, hd, n_chunks)
+            ws = self.env.shared.get("attn_scratch")
+            if ws is None or ws.numel() < need:
+                ws = torch.empty(max(need, 1 << 16), dtype=torch.float32, device=q.device)
+                self.env.shared["attn_scratch"] = ws
+            K.attention_split(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, ws, n_chunks,
+                              self.scale, self.window, view.page_size, H, G, hd)
+        else:
+            K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
+                             self.window, view.page_size, H, G, hd)
         linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
 
 

@@ -14,7 +14,7 @@ from typing import Dict
 import torch
 
 from ..ops import kernels as K
-from ..ops.linear import linear
+from ..ops.linear import linear, linear_swiglu
 from .base import Part, WeightSpec, register_part
 
 
@@ -45,9 +45,7 @@ class SwiGLU(Part):
             self.b_down = w["down_proj.bias"].float().contiguous()
 
     def forward(self, h, residual, ctx):
-        gu = linear(h, self.w_gu, self.b_gu)
-        act = torch.empty((h.shape[0], self.ff), dtype=gu.dtype, device=gu.device)
-        K.swiglu(gu, act)
+        act = linear_swiglu(h, self.w_gu, self.b_gu)
         linear(act, self.w_down, self.b_down, out=residual, accumulate=True)
 
 

@@ -1,0 +1,91 @@
+"""The split-KV attention kernel alone: against whole-sequence attention and
+against the general kernel, over head sizes, group ratios, page sizes, windows
+and chunk edges (positions around multiples of 256)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as P
+from test_kernels_gpu import dev, i32, paged_setup, rt, tol
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def run_split(q_rows, cache, bt, row_seg, pos, scale, window, page, H, G, hd, dtype, n_chunks=None):
+    from kappai_b200.ops import kernels as Kn
+    n = len(pos)
+    n_chunks = n_chunks or -(-(max(pos) + 1) // Kn.SPLIT_CHUNK)
+    ws = torch.full((Kn.attention_split_scratch(n, H, hd, n_chunks),), float("nan"), device="cuda")
+    out = torch.empty((n, H * hd), dtype=dtype, device="cuda")
+    Kn.attention_split(dev(q_rows, dtype), dev(cache, dtype), i32(bt), i32(row_seg), i32(pos), out, ws, n_chunks,
+                       scale, window, page, H, G, hd)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,hd,page,window", [
+    (4, 2, 16, 16, None), (5, 1, 48, 32, None), (32, 8, 64, 64, None), (8, 2, 128, 16, 300), (2, 2, 256, 8, None),
+    (8, 1, 32, 64, None), (6, 3, 80, 128, 17)])
+def test_split_matches_whole_sequence_attention(dtype, H, G, hd, page, window):
+    rng = np.random.default_rng(40)
+    seq_lens = [1, 255, 256, 257, 700, 513]
+    cache, bt, ks, vs = paged_setup(rng, seq_lens, page, G, hd, dtype)
+    scale = 1.0 / math.sqrt(hd)
+    qs = [rt(rng.standard_normal((L, H, hd)), dtype) for L in seq_lens]
+    # the last row of every request (a decode step), plus two rows of the longest (a short portion)
+    pos = [L - 1 for L in seq_lens] + [697, 698]
+    row_seg = list(range(len(seq_lens))) + [4, 4]
+    q_rows = np.stack([qs[s][p] for s, p in zip(row_seg, pos)]).reshape(len(pos), H * hd)
+    out = run_split(q_rows, cache, bt, row_seg, pos, scale, window, page, H, G, hd, dtype)
+    got = out.cpu().double().numpy().reshape(len(pos), H, hd)
+    for j, (s, p) in enumerate(zip(row_seg, pos)):
+        ref = P.attention(qs[s][:p + 1], ks[s][:p + 1], vs[s][:p + 1], scale, window)[-1]
+        np.testing.assert_allclose(got[j], ref, rtol=tol(dtype), atol=tol(dtype), err_msg=f"row {j} (pos {p})")
+    # a wider grid than needed (as under a captured graph) changes nothing
+    out2 = run_split(q_rows, cache, bt, row_seg, pos, scale, window, page, H, G, hd, dtype, n_chunks=7)
+    assert torch.equal(out, out2)
+    # and the general kernel agrees closely
+    from kappai_b200.ops import kernels as Kn
+    gen = torch.empty_like(out)
+    Kn.attention_rows(dev(q_rows, dtype), dev(cache, dtype), i32(bt), i32(row_seg), i32(pos), gen, scale, window, page,
+                      H, G, hd)
+    assert (gen.float() - out.float()).abs().max().item() <= tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far", [0, 255, 256, 511, 512, 1000])
+def test_split_finds_one_far_key(dtype, far):
+    rng = np.random.default_rng(41)
+    H, G, hd, page, L = 8, 2, 64, 64, 1001
+    cache, bt, ks, vs = paged_setup(rng, [L], page, G, hd, dtype)
+    q = rt(rng.standard_normal((1, H, hd)) * 0.01, dtype)
+    for h in range(H):
+        q[0, h] = ks[0][far, h // (H // G)] * 8.0
+    out = run_split(q.reshape(1, -1), cache, bt, [0], [L - 1], 1.0 / math.sqrt(hd), None, page, H, G, hd, dtype)
+    got = out.cpu().double().numpy().reshape(H, hd)
+    for h in range(H):
+        np.testing.assert_allclose(got[h], vs[0][far, h // (H // G)], atol=2e-2)
+
+
+def test_split_row_does_not_depend_on_the_batch():
+    rng = np.random.default_rng(42)
+    H, G, hd, page = 32, 8, 64, 64
+    seq_lens = [900, 300, 2048]
+    cache, bt, ks, vs = paged_setup(rng, seq_lens, page, G, hd, torch.bfloat16)
+    q = rt(rng.standard_normal((3, H * hd)), torch.bfloat16)
+    pos = [L - 1 for L in seq_lens]
+    both = run_split(q, cache, bt, [0, 1, 2], pos, 0.125, None, page, H, G, hd, torch.bfloat16)
+    for r in range(3):
+        alone = run_split(q[r:r + 1], cache, bt, [r], pos[r:r + 1], 0.125, None, page, H, G, hd, torch.bfloat16)
+        assert torch.equal(alone[0], both[r])
+
+
+def test_split_refuses_large_group_ratio():
+    from kappai_b200.ops import kernels as Kn
+    q = torch.zeros((1, 16 * 16), device="cuda")
+    with pytest.raises(Kn.KernelError, match="not supported"):
+        Kn.attention_split(q, torch.zeros((1, 2, 1, 16, 16), device="cuda"), i32([[0]]), i32([0]), i32([0]),
+                           torch.empty_like(q), torch.zeros(100000, device="cuda"), 1, 1.0, None, 16, 16, 1, 16)

@@ -381,3 +381,56 @@ def test_kernels_refuse_what_they_cannot_do():
     with pytest.raises(Kn.KernelError, match="not supported"):
         Kn.attention_rows(q, torch.zeros((1, 2, 1, 4, 512), device="cuda"), i32([[0]]), i32([0]), i32([0]),
                           torch.empty_like(q), 1.0, None, 4, 2, 1, 512)
+
+
+# ------------------------------------------------- weight-streaming (decode) gemm
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 33, 48, 49, 64])
+@pytest.mark.parametrize("N,K", [(331, 64), (2050, 2048), (96, 5632), (7, 32)])
+def test_gemm_skinny(M, N, K):
+    from kappai_b200.ops import kernels as Kn
+    rng = np.random.default_rng(30)
+    dt = torch.bfloat16
+    a = rt(rng.standard_normal((M, K)), dt)
+    w = rt(rng.standard_normal((N, K)) / math.sqrt(K), dt)
+    b = rng.standard_normal(N).astype(np.float32)
+    A, W = dev(a, dt), dev(w, dt)
+    assert Kn.skinny_ok(A, W)
+    ref = P.linear(a, w, b.astype(np.float64))
+    out = Kn.gemm_skinny(A, W, torch.empty((M, N), dtype=torch.float32, device="cuda"), dev(b))
+    np.testing.assert_allclose(out.cpu().double().numpy(), ref, rtol=2e-5, atol=2e-5 * math.sqrt(K))
+    out16 = Kn.gemm_skinny(A, W, torch.empty((M, N), dtype=dt, device="cuda"), dev(b))
+    np.testing.assert_allclose(out16.cpu().double().numpy(), ref, rtol=1e-2, atol=2e-2)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    acc = dev(res).clone()
+    Kn.gemm_skinny(A, W, acc, None, accumulate=True)
+    np.testing.assert_allclose(acc.cpu().double().numpy(), res + P.linear(a, w), rtol=2e-5, atol=2e-5 * math.sqrt(K))
+    # the same row alone gives the same bits
+    r = M // 2
+    alone = Kn.gemm_skinny(A[r:r + 1], W, torch.empty((1, N), dtype=torch.float32, device="cuda"), dev(b))
+    assert torch.equal(alone[0], out[r])
+
+
+@pytest.mark.parametrize("M", [1, 8, 20, 64])
+@pytest.mark.parametrize("ff,K", [(100, 64), (5632, 2048), (333, 96)])
+def test_gemm_skinny_swiglu(M, ff, K):
+    from kappai_b200.ops import kernels as Kn
+    from kappai_b200.ops.linear import linear_swiglu
+    rng = np.random.default_rng(31)
+    dt = torch.bfloat16
+    a = rt(rng.standard_normal((M, K)), dt)
+    w = rt(rng.standard_normal((2 * ff, K)) * (2.0 / math.sqrt(K)), dt)
+    b = rng.standard_normal(2 * ff).astype(np.float32) * 0.1
+    gu = rt(P.linear(a, w, b.astype(np.float64)), dt)              # gate and up are stored in bfloat16
+    ref = P.swiglu(gu[:, :ff], gu[:, ff:])
+    for bias in (dev(b), None):
+        if bias is None:
+            gu = rt(P.linear(a, w), dt)
+            ref = P.swiglu(gu[:, :ff], gu[:, ff:])
+        out = linear_swiglu(dev(a, dt), dev(w, dt), bias)
+        assert out.shape == (M, ff) and out.dtype == dt
+        np.testing.assert_allclose(out.cpu().double().numpy(), ref, rtol=2e-2, atol=2e-2)
+        # fused and unfused agree to the last bfloat16 rounding
+        unf = Kn.swiglu(Kn.gemm_nt_simt(dev(a, dt), dev(w, dt), torch.empty((M, 2 * ff), dtype=dt, device="cuda"), bias),
+                        torch.empty((M, ff), dtype=dt, device="cuda"))
+        assert ((out.float() - unf.float()).abs() <= 2e-2 * unf.float().abs() + 2e-2).all().item()
