@@ -201,13 +201,10 @@ def run_decode(runner, batch, prompt_len, steps, warmup, rng):
         t = argmax(logits)
         tok = t if tok is None else torch.cat([tok, t])
 
+    entries = [StepEntry(rid, [0], [0]) for rid in ids]
+
     def one_step(tok):
-        ctx, after = runner.prepare([StepEntry(rid, [0], [0]) for rid in ids])
-        ctx.token_ids.copy_(tok)                       # the sampled tokens never leave the device
-        logits = runner.run(ctx)
-        for req, n in after:
-            runner.cache.advance(req, n)
-        return argmax(logits)
+        return argmax(runner.step(entries, device_tokens=tok))     # the sampled tokens never leave the device
 
     for _ in range(warmup):
         tok = one_step(tok)

@@ -42,14 +42,17 @@ __device__ __forceinline__ void key_range(int pos, int window, int& k_lo, int& k
     k_hi = pos;
 }
 
-template <typename T>
+// HD, RR: head size and query heads per kv head fixed at compile time (loops unroll, loads overlap);
+// 0 means "taken from the arguments".
+template <typename T, int HD, int RR>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, const int* __restrict__ block_table,
                   int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
-                  int page_size, int H, int G, int hd) {
+                  int page_size, int H, int G, int hd_rt) {
     extern __shared__ float smem[];
-    const int R = H / G;
+    const int hd = HD ? HD : hd_rt;
+    const int R = RR ? RR : H / G;
     float* qs = smem;                              // [R][hd]
     float* ps = qs + R * hd;                       // [R][AD_CHUNK]
     float* red = ps + R * AD_CHUNK;                // [n_slices][R][hd]  (also used for the small reductions)
@@ -70,6 +73,23 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
         qs[i] = to_f32(q[(size_t)row * ldq + (size_t)(g * R) * hd + i]);
     __syncthreads();
 
+    // (head size 64, 16-bit cache) the values this thread multiplies later are fetched now, so that their
+    // latency passes under the scores and the softmax: thread = (pair of dims, slice of 32 keys)
+    constexpr bool PREFETCH_V = (HD == 64) && (sizeof(T) == 2);
+    uint32_t vpre[PREFETCH_V ? 32 : 1];
+    if (PREFETCH_V) {
+        const int pair_p = tid & 31, slice_p = tid >> 5;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int key2 = c0 + slice_p * 32 + j;
+            uint32_t v = 0;
+            if (key2 >= k_lo && key2 <= k_hi)
+                v = *reinterpret_cast<const uint32_t*>(cache + (size_t)bt[key2 / page_size] * page_stride + v_off +
+                                                       (size_t)(key2 % page_size) * hd + 2 * pair_p);
+            vpre[j] = v;
+        }
+    }
+
     // scores: one key a thread, all R heads
     const int key = c0 + tid;
     const bool valid = key >= k_lo && key <= k_hi;
@@ -79,6 +99,7 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     if (valid) {
         const T* kp = cache + (size_t)bt[key / page_size] * page_stride + k_off + (size_t)(key % page_size) * hd;
         constexpr int VN = Vec16<T>::N;
+#pragma unroll
         for (int i = 0; i < hd; i += VN) {
             float kf[VN];
             unpack16<T>(*reinterpret_cast<const uint4*>(kp + i), kf);
@@ -132,8 +153,30 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     float acc[AD_RMAX][2];
 #pragma unroll
     for (int r = 0; r < AD_RMAX; r++) acc[r][0] = acc[r][1] = 0.f;
-    if (slice < n_slices) {
+    if (PREFETCH_V) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const int kk = slice * 32 + j;                       // keys outside the row's range have p = 0
+            const float v0 = __uint_as_float(vpre[j] << 16), v1 = __uint_as_float(vpre[j] & 0xffff0000u);
+#pragma unroll
+            for (int r = 0; r < AD_RMAX; r++) {
+                if (r < R) {
+                    const float p = ps[r * AD_CHUNK + kk];
+                    acc[r][0] = fmaf(p, v0, acc[r][0]);
+                    acc[r][1] = fmaf(p, v1, acc[r][1]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < AD_RMAX; r++) {
+            if (r < R) {
+                red[((size_t)slice * R + r) * hd + 2 * pair] = acc[r][0];
+                red[((size_t)slice * R + r) * hd + 2 * pair + 1] = acc[r][1];
+            }
+        }
+    } else if (slice < n_slices) {
         const int kk_lo = max(slice * per, k_lo - c0), kk_hi = min(min((slice + 1) * per, AD_CHUNK) - 1, k_hi - c0);
+#pragma unroll 8
         for (int kk = kk_lo; kk <= kk_hi; kk++) {
             const int key2 = c0 + kk;
             const T* vp = cache + (size_t)bt[key2 / page_size] * page_stride + v_off +
@@ -221,17 +264,19 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
     dim3 grid(n_chunks, G, n);
     dim3 mgrid(H, n);
     const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
+#define AD_LAUNCH(T, HD, RR)                                                                                      \
+    attn_split_kernel<T, HD, RR><<<grid, AD_THREADS, smem, s>>>((const T*)q, ldq, (const T*)cache, block_table,       \
+                                                                max_blocks, row_seg, positions, part_acc, part_ml,    \
+                                                                n_chunks, scale, window, page_size, H, G, hd)
     KP_DISPATCH_DTYPE(dtype, T, {
-        if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(attn_split_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        attn_split_kernel<T><<<grid, AD_THREADS, smem, s>>>((const T*)q, ldq, (const T*)cache, block_table, max_blocks,
-                                                            row_seg, positions, part_acc, part_ml, n_chunks, scale,
-                                                            window, page_size, H, G, hd);
+        if (hd == 64 && R == 4) AD_LAUNCH(T, 64, 4);
+        else if (hd == 64) AD_LAUNCH(T, 64, 0);
+        else if (hd == 128) AD_LAUNCH(T, 128, 0);
+        else AD_LAUNCH(T, 0, 0);
         attn_merge_kernel<T><<<mgrid, mthreads, 0, s>>>(part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window,
                                                         H, hd);
     });
+#undef AD_LAUNCH
     return kp_launch_status();
 }
 

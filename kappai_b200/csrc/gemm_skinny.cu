@@ -6,12 +6,21 @@
 // thread loads 16 contiguous bytes of its W row and of its activation rows
 // straight into the mma fragment layout (the k order inside a block of 32 is
 // permuted identically for both operands, which a dot product does not see),
-// with several blocks in flight.  The 8 partial sums of a CTA are added in warp
-// order, so an output depends on its own activation row only, whatever M is.
+// with several blocks in flight.  The partial sums of a CTA's warps are added
+// in warp order, so an output depends on its own activation row only, whatever
+// M is.
 //
+// Fused in front (NORM, M <= 16): the A operand is RMSNorm of the float32
+// residual, a = bf16((x * rsqrt(mean(x^2) + eps)) * w), computed by the CTA
+// while its first weight loads are in flight (src/backend/cpu/scalar/quants.c:
+// 1489-1512 for the formula).  `rows` optionally gathers the rows of x.
 // Epilogues: bias; store bf16 / store fp32 / accumulate into fp32 (residual);
 // SwiGLU (W holds gate rows then up rows, ff apart; the CTA streams both and
 // writes silu(g)*u).  K must be a multiple of 32 and rows 16-byte aligned.
+//
+// The kernels are launched with programmatic dependent launch: the weight
+// loads of the first iteration do not depend on the kernel before, so they are
+// issued before griddepcontrol.wait and overlap that kernel's tail.
 #include "common.cuh"
 
 #define EPI_STORE 0
@@ -20,7 +29,8 @@
 #define EPI_SWIGLU 3
 
 #define SK_WARPS 8
-#define SK_UNROLL 4
+#define SK_U 4                 // k-blocks of 32 a warp has in flight per stage
+#define SK_THREADS (SK_WARPS * 32)
 
 __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
     uint4 v;
@@ -28,7 +38,6 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint4 ld_cached(const uint4* p) { return __ldg(p); }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -38,27 +47,99 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MT: m16 tiles of batch rows; HALF: only rows 0..7 of the single tile exist (M <= 8)
-template <int MT, bool HALF, int EPI>
-__global__ void __launch_bounds__(SK_WARPS * 32)
-gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw,
-                   const float* __restrict__ bias, void* __restrict__ Cv, int ldc, int M, int N, int K, int ff) {
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 8 normalised activations of row x at k..k+7 as four packed bf16 pairs
+__device__ __forceinline__ uint4 normed8(const float* __restrict__ x, const float* __restrict__ nw, float scale) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(x)), b = __ldg(reinterpret_cast<const float4*>(x) + 1);
+    const float4 wa = __ldg(reinterpret_cast<const float4*>(nw)), wb = __ldg(reinterpret_cast<const float4*>(nw) + 1);
+    uint4 r;
+    r.x = pack_bf16((a.x * scale) * wa.x, (a.y * scale) * wa.y);
+    r.y = pack_bf16((a.z * scale) * wa.z, (a.w * scale) * wa.w);
+    r.z = pack_bf16((b.x * scale) * wb.x, (b.y * scale) * wb.y);
+    r.w = pack_bf16((b.z * scale) * wb.z, (b.w * scale) * wb.w);
+    return r;
+}
+
+struct SkinnyArgs {
+    const bf16* A; int lda;              // bf16 activations (NORM = false)
+    const float* X; int ldx;             // float32 residual (NORM = true)
+    const float* norm_w; float eps;
+    const int* rows;                     // optional gather of the rows of X
+    const bf16* W; int ldw;
+    const float* bias;
+    void* C; int ldc;
+    int M, N, K, ff;
+};
+
+// MT: m16 tiles of batch rows; HALF: only rows 0..7 of the single tile exist (M <= 8).
+// Each warp walks its k-blocks in stages of SK_U blocks, two stages in flight: the loads of the next
+// stage are issued before the products of the current one.
+template <int MT, bool HALF, int EPI, bool NORM>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const SkinnyArgs p) {
     constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;          // weight streams
+    constexpr int U = SK_U;
+    constexpr int STEP = SK_WARPS * U;
     __shared__ float red[SK_WARPS][NW][MT][4][32];
+    __shared__ float scales[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int M = p.M, K = p.K;
     const int n0 = blockIdx.x * 8;
-    const int n_out = (EPI == EPI_SWIGLU) ? ff : N;          // output columns
+    const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;      // output columns
     const int wrow = min(n0 + g, n_out - 1);
     const uint4* wp[NW];
-    wp[0] = reinterpret_cast<const uint4*>(W + (size_t)wrow * ldw) + t;
-    if (NW == 2) wp[1] = reinterpret_cast<const uint4*>(W + (size_t)(ff + wrow) * ldw) + t;
-    const uint4* ap[MT][2];
+    wp[0] = reinterpret_cast<const uint4*>(p.W + (size_t)wrow * p.ldw) + t;
+    if (NW == 2) wp[1] = reinterpret_cast<const uint4*>(p.W + (size_t)(p.ff + wrow) * p.ldw) + t;
+    const int nkb = K >> 5;
+
+    uint4 wa[U][NW], wb[U][NW];
+    auto load_stage = [&](uint4 (&wv)[U][NW], int kb0) {
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int kb = kb0 + u * SK_WARPS;
+            if (kb < nkb) {
+#pragma unroll
+                for (int w = 0; w < NW; w++) wv[u][w] = ld_stream(wp[w] + (size_t)kb * 4);
+            }
+        }
+    };
+    // weights of the first stage: independent of everything that ran before
+    load_stage(wa, warp);
+    pdl_wait();                                               // now the activations are there
+    pdl_launch_dependents();
+
+    int r0[MT], r1[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
-        const int r0 = min(mt * 16 + g, M - 1), r1 = min(mt * 16 + g + 8, M - 1);
-        ap[mt][0] = reinterpret_cast<const uint4*>(A + (size_t)r0 * lda) + t;
-        ap[mt][1] = reinterpret_cast<const uint4*>(A + (size_t)r1 * lda) + t;
+        r0[mt] = min(mt * 16 + g, M - 1);
+        r1[mt] = min(mt * 16 + g + 8, M - 1);
+        if (NORM && p.rows) { r0[mt] = p.rows[r0[mt]]; r1[mt] = p.rows[r1[mt]]; }
     }
+    if (NORM) {
+        // per-row scale: warp w takes rows w and w + SK_WARPS (M <= 16)
+        for (int row = warp; row < M; row += SK_WARPS) {
+            const int xr = p.rows ? p.rows[row] : row;
+            const float4* xp = reinterpret_cast<const float4*>(p.X + (size_t)xr * p.ldx);
+            float ss = 0.f;
+            for (int i = lane; i < (K >> 2); i += 32) {
+                const float4 v = __ldg(xp + i);
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) scales[row] = 1.0f / sqrtf(ss / (float)K + p.eps);
+        }
+        __syncthreads();
+    }
+    float sc0 = 0.f, sc1 = 0.f;
+    if (NORM) { sc0 = scales[min(g, M - 1)]; sc1 = scales[min(g + 8, M - 1)]; }
+
     float acc[NW][MT][4];
 #pragma unroll
     for (int w = 0; w < NW; w++)
@@ -67,26 +148,22 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[w][mt][i] = 0.f;
 
-    const int nkb = K >> 5;
-    for (int kb0 = warp; kb0 < nkb; kb0 += SK_WARPS * SK_UNROLL) {
-        uint4 wv[SK_UNROLL][NW];
+    auto compute_stage = [&](const uint4 (&wv)[U][NW], int kb0) {
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; u++) {
-            const int kb = kb0 + u * SK_WARPS;
-            if (kb < nkb) {
-#pragma unroll
-                for (int w = 0; w < NW; w++) wv[u][w] = ld_stream(wp[w] + (size_t)kb * 4);
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < SK_UNROLL; u++) {
+        for (int u = 0; u < U; u++) {
             const int kb = kb0 + u * SK_WARPS;
             if (kb < nkb) {
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint4 lo = ld_cached(ap[mt][0] + (size_t)kb * 4);
-                    uint4 hi = make_uint4(0, 0, 0, 0);
-                    if (!HALF) hi = ld_cached(ap[mt][1] + (size_t)kb * 4);
+                    uint4 lo, hi = make_uint4(0, 0, 0, 0);
+                    if (NORM) {
+                        const int k = kb * 32 + 8 * t;
+                        lo = normed8(p.X + (size_t)r0[mt] * p.ldx + k, p.norm_w + k, sc0);
+                        if (!HALF) hi = normed8(p.X + (size_t)r1[mt] * p.ldx + k, p.norm_w + k, sc1);
+                    } else {
+                        lo = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r0[mt] * p.lda) + kb * 4 + t);
+                        if (!HALF) hi = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r1[mt] * p.lda) + kb * 4 + t);
+                    }
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
                         mma_bf16(acc[w][mt], lo.x, hi.x, lo.y, hi.y, wv[u][w].x, wv[u][w].y);
@@ -94,6 +171,14 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
                     }
                 }
             }
+        }
+    };
+    for (int kb0 = warp; kb0 < nkb; kb0 += 2 * STEP) {
+        if (kb0 + STEP < nkb) load_stage(wb, kb0 + STEP);
+        compute_stage(wa, kb0);
+        if (kb0 + STEP < nkb) {
+            if (kb0 + 2 * STEP < nkb) load_stage(wa, kb0 + 2 * STEP);
+            compute_stage(wb, kb0 + STEP);
         }
     }
 #pragma unroll
@@ -103,8 +188,8 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
 #pragma unroll
             for (int i = 0; i < 4; i++) red[warp][w][mt][i][lane] = acc[w][mt][i];
     __syncthreads();
-    // sum the warps' partials in order and write: thread (mt, i, lane) <- element i of tile mt of lane's fragment
-    for (int e = threadIdx.x; e < MT * 4 * 32; e += SK_WARPS * 32) {
+    // sum the warps' partials in warp order and write: element i of tile mt of lane l's fragment
+    for (int e = threadIdx.x; e < MT * 4 * 32; e += SK_THREADS) {
         const int l = e & 31, i = (e >> 5) & 3, mt = e >> 7;
         const int m = mt * 16 + (l >> 2) + ((i & 2) ? 8 : 0);
         const int n = n0 + (l & 3) * 2 + (i & 1);
@@ -112,67 +197,101 @@ gemm_skinny_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__
         float v = 0.f;
 #pragma unroll
         for (int w8 = 0; w8 < SK_WARPS; w8++) v += red[w8][0][mt][i][l];
-        if (bias) v += bias[n];
-        const size_t o = (size_t)m * ldc + n;
+        if (p.bias) v += p.bias[n];
+        const size_t o = (size_t)m * p.ldc + n;
         if (EPI == EPI_SWIGLU) {
             float u = 0.f;
 #pragma unroll
             for (int w8 = 0; w8 < SK_WARPS; w8++) u += red[w8][NW - 1][mt][i][l];
-            if (bias) u += bias[ff + n];
+            if (p.bias) u += p.bias[p.ff + n];
             // gate and up are rounded to the storage type before the activation, as the unfused path stores them
             const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-            ((bf16*)Cv)[o] = from_f32<bf16>((gq / (1.0f + expf(-gq))) * uq);
+            ((bf16*)p.C)[o] = from_f32<bf16>((gq / (1.0f + expf(-gq))) * uq);
         } else if (EPI == EPI_STORE) {
-            ((bf16*)Cv)[o] = from_f32<bf16>(v);
+            ((bf16*)p.C)[o] = from_f32<bf16>(v);
         } else if (EPI == EPI_STORE_F32) {
-            ((float*)Cv)[o] = v;
+            ((float*)p.C)[o] = v;
         } else {
-            ((float*)Cv)[o] += v;
+            ((float*)p.C)[o] += v;
         }
     }
 }
 
-template <int MT, bool HALF>
-static int launch_epi(const bf16* A, int lda, const bf16* W, int ldw, const float* bias, void* C, int ldc, int M,
-                      int N, int K, int ff, int epi, cudaStream_t s) {
-    const int n_out = epi == EPI_SWIGLU ? ff : N;
-    dim3 grid((n_out + 7) / 8);
-    switch (epi) {
-        case EPI_STORE:
-            gemm_skinny_kernel<MT, HALF, EPI_STORE><<<grid, SK_WARPS * 32, 0, s>>>(A, lda, W, ldw, bias, C, ldc, M, N, K, ff);
-            break;
-        case EPI_STORE_F32:
-            gemm_skinny_kernel<MT, HALF, EPI_STORE_F32><<<grid, SK_WARPS * 32, 0, s>>>(A, lda, W, ldw, bias, C, ldc, M, N, K, ff);
-            break;
-        case EPI_ACCUM_F32:
-            gemm_skinny_kernel<MT, HALF, EPI_ACCUM_F32><<<grid, SK_WARPS * 32, 0, s>>>(A, lda, W, ldw, bias, C, ldc, M, N, K, ff);
-            break;
-        case EPI_SWIGLU:
-            gemm_skinny_kernel<MT, HALF, EPI_SWIGLU><<<grid, SK_WARPS * 32, 0, s>>>(A, lda, W, ldw, bias, C, ldc, M, N, K, ff);
-            break;
-        default:
-            return KP_ERR_BAD_ARG;
-    }
-    return kp_launch_status();
+template <typename Kern>
+static int launch_pdl(Kern kern, dim3 grid, cudaStream_t s, const SkinnyArgs& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(SK_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    return (int)e;
 }
 
-// epi: 0 store bf16, 1 store f32, 2 accumulate f32, 3 SwiGLU (N = 2*ff rows of W, output [M, ff] bf16)
-extern "C" int kp_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc,
-                              int M, int N, int K, int epi, void* stream) {
-    if (M <= 0 || N <= 0) return 0;
-    if (M > 64 || K < 32 || (K & 31) || (lda & 7) || (ldw & 7)) return KP_ERR_UNSUPPORTED;
-    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
-    int ff = 0;
+template <int MT, bool HALF, bool NORM>
+static int launch_epi(const SkinnyArgs& a, int epi, cudaStream_t s) {
+    const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
+    dim3 grid((n_out + 7) / 8);
+    switch (epi) {
+        case EPI_STORE: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE, NORM>, grid, s, a);
+        case EPI_STORE_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE_F32, NORM>, grid, s, a);
+        case EPI_ACCUM_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_ACCUM_F32, NORM>, grid, s, a);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_SWIGLU, NORM>, grid, s, a);
+        default: return KP_ERR_BAD_ARG;
+    }
+}
+
+template <bool NORM>
+static int launch_m(const SkinnyArgs& a, int epi, cudaStream_t s) {
+    if (a.M <= 8) return launch_epi<1, true, NORM>(a, epi, s);
+    if (a.M <= 16) return launch_epi<1, false, NORM>(a, epi, s);
+    if (NORM) return KP_ERR_UNSUPPORTED;
+    if (a.M <= 32) return launch_epi<2, false, false>(a, epi, s);
+    if (a.M <= 48) return launch_epi<3, false, false>(a, epi, s);
+    return launch_epi<4, false, false>(a, epi, s);
+}
+
+static int check_common(int M, int N, int K, int ldw, const void* W, int epi, int* ff) {
+    if (M > 64 || K < 32 || (K & 31) || (ldw & 7) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
+    *ff = 0;
     if (epi == EPI_SWIGLU) {
         if (N & 1) return KP_ERR_BAD_ARG;
-        ff = N / 2;
+        *ff = N / 2;
     }
-    const bf16* a = (const bf16*)A;
-    const bf16* w = (const bf16*)W;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (M <= 8) return launch_epi<1, true>(a, lda, w, ldw, bias, C, ldc, M, N, K, ff, epi, s);
-    if (M <= 16) return launch_epi<1, false>(a, lda, w, ldw, bias, C, ldc, M, N, K, ff, epi, s);
-    if (M <= 32) return launch_epi<2, false>(a, lda, w, ldw, bias, C, ldc, M, N, K, ff, epi, s);
-    if (M <= 48) return launch_epi<3, false>(a, lda, w, ldw, bias, C, ldc, M, N, K, ff, epi, s);
-    return launch_epi<4, false>(a, lda, w, ldw, bias, C, ldc, M, N, K, ff, epi, s);
+    return 0;
 }
+
+extern "C" {
+
+// epi: 0 store bf16, 1 store f32, 2 accumulate f32, 3 SwiGLU (N = 2*ff rows of W, output [M, ff] bf16)
+int kp_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                   int K, int epi, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    SkinnyArgs a = {};
+    int st = check_common(M, N, K, ldw, W, epi, &a.ff);
+    if (st) return st;
+    if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;
+    a.A = (const bf16*)A; a.lda = lda; a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc;
+    a.M = M; a.N = N; a.K = K;
+    return launch_m<false>(a, epi, (cudaStream_t)stream);
+}
+
+// The same with RMSNorm of the float32 rows X (optionally gathered by `rows`) fused in front; M <= 16.
+int kp_gemm_skinny_norm(const float* X, int ldx, const float* norm_w, float eps, const int* rows, const void* W,
+                        int ldw, const float* bias, void* C, int ldc, int M, int N, int K, int epi, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    SkinnyArgs a = {};
+    int st = check_common(M, N, K, ldw, W, epi, &a.ff);
+    if (st) return st;
+    if (M > 16 || (ldx & 3) || ((uintptr_t)X & 15) || ((uintptr_t)norm_w & 15)) return KP_ERR_UNSUPPORTED;
+    a.X = X; a.ldx = ldx; a.norm_w = norm_w; a.eps = eps; a.rows = rows;
+    a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
+    return launch_m<true>(a, epi, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -262,7 +262,62 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     }
 }
 
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int r = block_argmax(logits + (size_t)blockIdx.x * V, V, 1.0f, s_val, s_idx, nullptr);
+    if (threadIdx.x == 0) out[blockIdx.x] = r;
+}
+
+// Two stages for large vocabularies: ARGMAX_SLICES blocks a row each find the best of their slice
+// (lowest index on ties), then one warp a row picks the best slice (lowest slice on ties).
+#define ARGMAX_SLICES 32
+__global__ void __launch_bounds__(256)
+argmax_slices_kernel(const float* __restrict__ logits, int V, float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float s_val[32];
+    __shared__ int s_idx[32];
+    const int row = blockIdx.y, sl = blockIdx.x;
+    const int per = (V + ARGMAX_SLICES - 1) / ARGMAX_SLICES;
+    const int b = sl * per, e = min(b + per, V);
+    float mx;
+    int r = 0x7fffffff;
+    if (b < e) r = b + block_argmax(logits + (size_t)row * V + b, e - b, 1.0f, s_val, s_idx, &mx);
+    if (threadIdx.x == 0) {
+        part_val[row * ARGMAX_SLICES + sl] = b < e ? mx : -INFINITY;
+        part_idx[row * ARGMAX_SLICES + sl] = r;
+    }
+}
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float bv = part_val[row * ARGMAX_SLICES + lane];
+    int bi = part_idx[row * ARGMAX_SLICES + lane];
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = bi == 0x7fffffff ? 0 : bi;
+}
+
 extern "C" {
+
+// scratch: n * 32 floats then n * 32 ints, or null (one block a row; for small vocabularies)
+int kp_argmax_rows(const float* logits, int n, int V, int* out, void* scratch, void* stream) {
+    if (n <= 0) return 0;
+    if (V < 1) return KP_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (scratch == nullptr || V < 8192 || n > 65535) {
+        argmax_rows_kernel<<<n, SAMPLE_THREADS, 0, s>>>(logits, V, out);
+    } else {
+        float* pv = (float*)scratch;
+        int* pi = (int*)(pv + (size_t)n * ARGMAX_SLICES);
+        argmax_slices_kernel<<<dim3(ARGMAX_SLICES, n), 256, 0, s>>>(logits, V, pv, pi);
+        argmax_final_kernel<<<n, 32, 0, s>>>(pv, pi, out);
+    }
+    return kp_launch_status();
+}
 
 int kp_repeat_penalty(float* logits, int n, int V, const int* recent, int max_recent, const float* penalty,
                       void* stream) {

@@ -81,7 +81,46 @@ __global__ void shortconv_state_kernel(const T* __restrict__ p, int ldp, float* 
     }
 }
 
+// Every segment is one row (a decode step): output and new state by the same
+// thread, so one launch does both.  Row r belongs to segment r.
+template <typename T>
+__global__ void shortconv_decode_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ w,
+                                        const float* __restrict__ bias, float* __restrict__ state,
+                                        const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
+                                        T* __restrict__ out, int ldo, int n, int d, int K) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int row = blockIdx.y;
+    if (c >= d || row >= n) return;
+    const bool fresh = seg_pos[row] == 0;
+    float* st = state + (size_t)seg_slot[row] * (K - 1) * d;
+    const float* wc = w + (size_t)c * K;
+    const float bx = bx_of(p, row, ldp, d, c);
+    float hist[KP_CONV_MAX_K - 1];
+    for (int k = 0; k < K - 1; k++) hist[k] = fresh ? 0.f : st[(size_t)k * d + c];
+    float sum;
+    if (K == 3) {
+        sum = hist[0] * wc[0] + hist[1] * wc[1] + bx * wc[2];
+    } else {
+        sum = bx * wc[K - 1];
+        for (int k = 0; k < K - 1; k++) sum += hist[k] * wc[k];
+    }
+    if (bias) sum += bias[c];
+    out[(size_t)row * ldo + c] = from_f32<T>(to_f32(p[(size_t)row * ldp + d + c]) * sum);
+    for (int k = 0; k + 1 < K - 1; k++) st[(size_t)k * d + c] = hist[k + 1];
+    st[(size_t)(K - 2) * d + c] = bx;
+}
+
 extern "C" {
+
+int kp_shortconv_decode(const void* p, int ldp, const float* w, const float* bias, float* state, const int* seg_pos,
+                        const int* seg_slot, void* out, int ldo, int n, int d, int K, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (K < 2 || K > KP_CONV_MAX_K || n > 65535) return KP_ERR_UNSUPPORTED;
+    dim3 grid((d + 127) / 128, n);
+    KP_DISPATCH_DTYPE(dtype, T, (shortconv_decode_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        (const T*)p, ldp, w, bias, state, seg_pos, seg_slot, (T*)out, ldo, n, d, K)));
+    return kp_launch_status();
+}
 
 int kp_shortconv_forward(const void* p, int ldp, const float* w, const float* bias, const float* state,
                          const int* row_seg, const int* cu_rows, const int* seg_pos, const int* seg_slot,

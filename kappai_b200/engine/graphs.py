@@ -1,0 +1,167 @@
+"""CUDA graphs for decode steps.
+
+A decode step (every segment one token, every token's logits wanted) launches
+about a hundred small kernels; from Python that is launch-bound.  Such a step
+is captured once per shape into a CUDA graph whose kernels read the step's
+tables (token ids, positions, slots, block tables) from a static device buffer;
+later steps of the same shape only refill that buffer (one pinned-memory copy)
+and replay.  The shape key is (number of requests, block-table width), the
+width being the next power of two of the blocks needed, so a graph is captured
+again only when the longest request doubles its pages.  The split-KV attention
+grid is fixed by that width.  Nothing else differs from the eager path: the same
+model code runs under capture.
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..ops import kernels as K
+from .batch import PagedView, StepContext
+
+N_PINNED = 4          # staging buffers in rotation, so a refill never overtakes a copy in flight
+
+
+def _align4(n: int) -> int:
+    return (n + 3) // 4 * 4
+
+
+class _DecodeGraph:
+    def __init__(self, runner, n: int, width: int):
+        self.n, self.width = n, width
+        dev = runner.device
+        groups = list(runner.group_page_size.items())
+        # layout of the static buffer (int32), every piece 16-byte aligned
+        off, self.off = 0, {}
+        for name in ("token_ids", "positions", "row_seg", "cu_rows", "seg_pos", "seg_slot", "logit_rows"):
+            self.off[name] = off
+            off += _align4(n + 1 if name == "cu_rows" else n)
+        for gk, _ in groups:
+            self.off[("slot_map", gk)] = off
+            off += _align4(n)
+            self.off[("block_table", gk)] = off
+            off += _align4(n * width)
+        self.size = off
+        self.dev = torch.zeros(off, dtype=torch.int32, device=dev)
+        self.pinned = [torch.zeros(off, dtype=torch.int32, pin_memory=True) for _ in range(N_PINNED)]
+        self.events = [None] * N_PINNED
+        self.turn = 0
+        for p in self.pinned:                       # the pieces that never change
+            a = p.numpy()
+            a[self.off["row_seg"]:self.off["row_seg"] + n] = np.arange(n)
+            a[self.off["cu_rows"]:self.off["cu_rows"] + n + 1] = np.arange(n + 1)
+            a[self.off["logit_rows"]:self.off["logit_rows"] + n] = np.arange(n)
+        piece = lambda name, m: self.dev[self.off[name]:self.off[name] + m]
+        paged = {gk: PagedView(piece(("block_table", gk), n * width).view(n, width), piece(("slot_map", gk), n), ps)
+                 for gk, ps in groups}
+        max_ctx = min(runner.max_model_len, width * runner.page_size)
+        self.ctx = StepContext(
+            n_rows=n, n_seg=n, token_ids=piece("token_ids", n), positions=piece("positions", n),
+            row_seg=piece("row_seg", n), cu_rows=piece("cu_rows", n + 1), seg_pos=piece("seg_pos", n),
+            seg_slot=piece("seg_slot", n), logit_rows=piece("logit_rows", n), n_out=n, paged=paged,
+            host_cu_rows=list(range(n + 1)), host_seg_pos=[0] * n, host_seg_slot=[0] * n,
+            max_seg_len=1, max_context=max_ctx, decode_only=True)
+        self.ctx.h2d_bytes = off * 4
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.n_kernels = 0
+
+    def fill(self, runner, reqs: Sequence[Hashable], tokens: Optional[Sequence[int]]) -> None:
+        """Write this step's tables into the next staging buffer and start its copy."""
+        i = self.turn
+        self.turn = (i + 1) % N_PINNED
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        a = self.pinned[i].numpy()
+        n, o = self.n, self.off
+        cache = runner.cache
+        lens = [cache.requests[r].length for r in reqs]
+        if tokens is not None:
+            a[o["token_ids"]:o["token_ids"] + n] = tokens
+        a[o["positions"]:o["positions"] + n] = lens
+        a[o["seg_pos"]:o["seg_pos"] + n] = lens
+        a[o["seg_slot"]:o["seg_slot"] + n] = [cache.requests[r].slot for r in reqs]
+        for gk, ps in runner.group_page_size.items():
+            bt = a[o[("block_table", gk)]:o[("block_table", gk)] + n * self.width].reshape(n, self.width)
+            sm = a[o[("slot_map", gk)]:o[("slot_map", gk)] + n]
+            for j, r in enumerate(reqs):
+                t = cache.block_table(r, gk)
+                bt[j, :len(t)] = t
+                sm[j] = t[lens[j] // ps] * ps + lens[j] % ps
+        self.dev.copy_(self.pinned[i], non_blocking=True)
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class DecodeGraphs:
+    """Captured decode steps of one :class:`ModelRunner`."""
+
+    def __init__(self, runner):
+        self.runner = runner
+        self.graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        self.n_captures = 0
+        self.n_replays = 0
+
+    @staticmethod
+    def eligible(entries) -> bool:
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def width_for(self, blocks: int) -> int:
+        w = 8
+        while w < blocks:
+            w *= 2
+        return w
+
+    def step(self, entries, device_tokens: Optional[torch.Tensor]) -> torch.Tensor:
+        """Pages for the new tokens are already taken.  Returns the static
+        logits buffer [n, vocab] (valid until the next step of this shape)."""
+        r = self.runner
+        reqs = [e.req for e in entries]
+        n = len(reqs)
+        blocks = max(len(r.cache.block_table(q, gk)) for q in reqs for gk in r.group_page_size) \
+            if r.group_page_size else 1
+        key = (n, self.width_for(blocks))
+        g = self.graphs.get(key)
+        if g is None:
+            g = _DecodeGraph(r, n, key[1])
+            self.graphs[key] = g
+        tokens = None if device_tokens is not None else [int(e.tokens[0]) for e in entries]
+        g.fill(r, reqs, tokens)
+        if device_tokens is not None:
+            g.ctx.token_ids.copy_(device_tokens)
+        if g.graph is None:
+            # run once eagerly (kernels get built, scratch gets its size), restore the state it changed, capture
+            self._capture(g)
+        else:
+            g.graph.replay()
+            K.LAUNCHES[0] += g.n_kernels
+            self.n_replays += 1
+        r.last_h2d_bytes = g.ctx.h2d_bytes
+        return g.logits
+
+    def _capture(self, g: _DecodeGraph) -> None:
+        r = self.runner
+        # the eager warm-up run changes fixed-size state (and rewrites this step's keys, harmlessly);
+        # keep a copy of the state tensors and put them back before the captured run replays the step
+        from ..cache.storage import StateView
+        states = [v.tensor for v in r.storage.views if isinstance(v, StateView) and v.writes]
+        saved = [t.clone() for t in states]
+        torch.cuda.current_stream().synchronize()
+        r.model.forward(g.ctx, r.storage.views)
+        for t, s in zip(states, saved):
+            t.copy_(s)
+        torch.cuda.current_stream().synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = K.LAUNCHES[0]
+        with torch.cuda.graph(graph):
+            g.logits = r.model.forward(g.ctx, r.storage.views)
+        g.n_kernels = K.LAUNCHES[0] - before       # kernel launchers a replay stands for
+        for t, s in zip(states, saved):
+            t.copy_(s)
+        g.graph = graph
+        self.n_captures += 1
+        graph.replay()
+        self.n_replays += 1

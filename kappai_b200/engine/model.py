@@ -36,6 +36,11 @@ class Model:
         self.final_norm = self._make("norm", spec.final_norm) if spec.final_norm is not None else None
         self.head = self._make("head", spec.head)
         self.schedule = list(spec.schedule)
+        parts = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm]
+        # a decode step may be captured in a CUDA graph only if every part reads its tables from the device
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts if p is not None)
 
     def _make(self, category: str, ps: PartSpec) -> Part:
         part = make_part(category, ps, self.env)
@@ -83,7 +88,8 @@ class Model:
         if ctx.n_out == 0:
             return None
         if self.final_norm is not None:
-            h = self.final_norm.forward(x, rows=ctx.logit_rows)
+            h = (self.final_norm.lazy(x, rows=ctx.logit_rows) if hasattr(self.final_norm, "lazy")
+                 else self.final_norm.forward(x, rows=ctx.logit_rows))
         else:
             h = x.index_select(0, ctx.logit_rows.long()).to(self.env.dtype)
         return self.head.forward(h)

@@ -26,6 +26,7 @@ from ..config.registry import load_config
 from ..parts.base import BuildEnv
 from ..weights.loader import load_weights
 from .batch import Segment, StepContext, build_step_context
+from .graphs import DecodeGraphs
 from .model import Model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -54,10 +55,11 @@ def require_cuda(device) -> torch.device:
 class ModelRunner:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", max_tokens: int = 4096,
                  max_requests: int = 4, page_size: int = 64, max_model_len: Optional[int] = None,
-                 device="cuda:0"):
+                 device="cuda:0", cuda_graphs: bool = True):
         """``max_tokens``: how many tokens the live requests may hold together,
         each request's count rounded up to a whole page; the page pools are
-        made for exactly this many.  ``max_requests``: state slots."""
+        made for exactly this many.  ``max_requests``: state slots.
+        ``cuda_graphs``: replay decode steps from captured CUDA graphs."""
         if dtype not in DTYPES:
             raise EngineError(f"dtype '{dtype}': expected bfloat16 or float32")
         self.device = require_cuda(device)
@@ -86,6 +88,7 @@ class ModelRunner:
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
         self.last_h2d_bytes = 0
+        self.graphs: Optional[DecodeGraphs] = DecodeGraphs(self) if cuda_graphs else None
 
     # -- requests
     def is_live(self, req: Hashable) -> bool:
@@ -107,12 +110,13 @@ class ModelRunner:
         return all(-(-n_new // p.page_size) <= p.n_free for p in self.cache.pools.values())
 
     # -- the step
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
-        """Admit new requests, take pages for the new tokens and build the
-        step's tables.  Nothing is kept if any entry cannot be served."""
-        admitted, extended = [], []
+    def _reserve(self, entries: Sequence[StepEntry]) -> List[Tuple[Hashable, int, int]]:
+        """Admit new requests and take pages for every entry's new tokens.
+        Returns (request, length before, length after) per entry.  Nothing is
+        kept of a new request if any entry cannot be served."""
+        admitted = []
         try:
-            segs, after = [], []
+            plan = []
             for e in entries:
                 if len(e.tokens) < 1:
                     raise EngineError(f"request {e.req!r}: no tokens in this step")
@@ -125,15 +129,10 @@ class ModelRunner:
                     raise EngineError(f"request {e.req!r}: {new_len} tokens exceed the limit of "
                                       f"{self.max_model_len} positions")
                 self.cache.extend(e.req, new_len)
-                extended.append(e.req)
-                segs.append(Segment(
-                    req=e.req, tokens=e.tokens, pos_start=rc.length, want=e.want, slot=rc.slot,
-                    block_tables={gk: self.cache.block_table(e.req, gk) for gk in self.group_page_size},
-                    token_slots={gk: self.cache.token_slots(e.req, gk, rc.length, len(e.tokens))
-                                 for gk in self.group_page_size}))
-                after.append((e.req, new_len))
-            ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len)
-            return ctx, after
+                plan.append((e.req, rc.length, new_len))
+            if len({p[0] for p in plan}) != len(plan):
+                raise EngineError("a request appears twice in one step")
+            return plan
         except Exception:
             for r in admitted:
                 self.cache.free(r)
@@ -141,13 +140,43 @@ class ModelRunner:
             # cover positions the request will need anyway and are freed with it
             raise
 
+    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+        """Reserve cache for the entries and build the step's tables."""
+        plan = self._reserve(entries)
+        segs = []
+        for e, (req, old_len, new_len) in zip(entries, plan):
+            rc = self.cache.requests[req]
+            segs.append(Segment(
+                req=req, tokens=e.tokens, pos_start=old_len, want=e.want, slot=rc.slot,
+                block_tables={gk: self.cache.block_table(req, gk) for gk in self.group_page_size},
+                token_slots={gk: self.cache.token_slots(req, gk, old_len, len(e.tokens))
+                             for gk in self.group_page_size}))
+        ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len)
+        return ctx, [(req, new_len) for req, _, new_len in plan]
+
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         return self.model.forward(ctx, self.storage.views)
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
+             ) -> Optional[torch.Tensor]:
         """Run one step; float32 logits [wanted, vocab] on the device, in the
-        order of the entries and of their ``want`` (None if nothing is wanted)."""
+        order of the entries and of their ``want`` (None if nothing is wanted).
+        With ``device_tokens`` (int32, one per row, on the device) the token ids
+        of the entries are placeholders and those are run instead, so sampled
+        tokens need not visit the host between steps.  The returned tensor may
+        be reused by the next step: read it before."""
+        if self.graphs is not None and self.model.graph_safe and DecodeGraphs.eligible(entries):
+            for e in entries:
+                if not (0 <= int(e.tokens[0]) < self.vocab_size):
+                    raise EngineError(f"request {e.req!r}: token id {e.tokens[0]} outside the vocabulary")
+            plan = self._reserve(entries)
+            logits = self.graphs.step(entries, device_tokens)
+            for req, _, new_len in plan:
+                self.cache.advance(req, new_len)
+            return logits
         ctx, after = self.prepare(entries)
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens)
         self.last_h2d_bytes = ctx.h2d_bytes
         logits = self.run(ctx)
         for req, new_len in after:

@@ -171,6 +171,25 @@ def shortconv_forward(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Ten
     return out
 
 
+def shortconv_decode(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                     seg_pos: torch.Tensor, seg_slot: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Output and state update in one launch, for steps in which every segment is one row."""
+    _need(p, "p", contiguous=False); _need(w, "w", torch.float32); _need(state, "state", torch.float32)
+    _need(out, "out", p.dtype, contiguous=False)
+    _need(seg_pos, "seg_pos", torch.int32); _need(seg_slot, "seg_slot", torch.int32)
+    n, d = out.shape
+    K = w.shape[1]
+    if p.shape != (n, 3 * d) or w.shape[0] != d or state.shape[1:] != (K - 1, d) or seg_pos.numel() != n:
+        raise KernelError("shortconv_decode: shape mismatch")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    lib = load_library("shortconv")
+    _check(lib.kp_shortconv_decode(_ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(seg_pos),
+                                   _ptr(seg_slot), _ptr(out), _rows_2d(out, "out"), n, d, K, dtype_code(p.dtype),
+                                   _stream()), "shortconv_decode")
+    return out
+
+
 def shortconv_update_state(p: torch.Tensor, state: torch.Tensor, cu_rows: torch.Tensor, seg_pos: torch.Tensor,
                            seg_slot: torch.Tensor, n_seg: int) -> None:
     _need(p, "p", contiguous=False); _need(state, "state", torch.float32)
@@ -289,6 +308,88 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+USE_STREAM = True          # few-row products go to the bulk-copy kernel where their shape fits it
+STREAM_CHUNK = 256
+STREAM_MAX_SLAB = 96 * 1024
+
+
+def stream_fits(K: int, swiglu: bool) -> bool:
+    """Do 8 (16 with SwiGLU) rows of K bfloat16 fit the bulk-copy kernel's shared-memory slab?"""
+    if K < STREAM_CHUNK or K % STREAM_CHUNK or K // STREAM_CHUNK > 32:
+        return False
+    pitch = K * 2 + (64 if (K * 2) % 128 == 0 else 0)
+    return (16 if swiglu else 8) * pitch <= STREAM_MAX_SLAB
+
+
+def stream_pays(N: int, K: int) -> bool:
+    """Measured on B200: the bulk-copy kernel wins for short slabs and moderate grids (6144 x 2048: 6.4
+    against 8.1 us; 2048 x 2048: 3.5 against 4.4 us) and loses where a CTA's slab is long (K = 5632: two
+    CTAs an SM, 13.1 against 8.7 us) or the grid is huge (the 65536-row head: 66 against 48 us)."""
+    return K <= 2048 and N <= 16384
+
+
+def stream_status() -> int:
+    """0, or 1 if a bounded wait of the bulk-copy kernels gave up since the last call (synchronises)."""
+    return int(load_library("gemm_stream").kp_stream_status())
+
+
+SKINNY_NORM_MAX_M = 16
+
+
+def skinny_norm_ok(x: torch.Tensor, n_rows: int, w: torch.Tensor) -> bool:
+    """Can the weight-streaming kernel take RMSNorm(x) as its A operand?"""
+    return (x.dtype == torch.float32 and w.dtype == torch.bfloat16 and n_rows <= SKINNY_NORM_MAX_M
+            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 4 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny_norm(x: torch.Tensor, norm_w: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
+                     w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+    """out = rmsnorm(x[rows] if rows is given else x) @ w.T (+ bias), the norm
+    computed inside the product kernel (at most 16 rows)."""
+    _need(x, "x", torch.float32, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
+    _need(norm_w, "norm_w", torch.float32); _need(out, "out", contiguous=False)
+    K = x.shape[1]
+    M = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    N = w.shape[0]
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or out.shape != (M, n_out) or norm_w.numel() != K:
+        raise KernelError(f"gemm_skinny_norm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    epi = _skinny_epilogue(out, accumulate, swiglu)
+    if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K):
+        lib = load_library("gemm_stream")
+        _check(lib.kp_gemm_stream_norm(_ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows),
+                                       _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K,
+                                       epi, _stream()), "gemm_stream_norm")
+        return out
+    lib = load_library("gemm_skinny")
+    _check(lib.kp_gemm_skinny_norm(_ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows), _ptr(w),
+                                   _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, epi,
+                                   _stream()), "gemm_skinny_norm")
+    return out
+
+
+def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
+    if swiglu:
+        if out.dtype != torch.bfloat16:
+            raise KernelError("gemm_skinny: the SwiGLU epilogue writes bfloat16")
+        return EPI_SWIGLU
+    if accumulate:
+        if out.dtype != torch.float32:
+            raise KernelError("gemm_skinny: accumulation needs a float32 output")
+        return EPI_ACCUM_F32
+    if out.dtype == torch.bfloat16:
+        return EPI_STORE
+    if out.dtype == torch.float32:
+        return EPI_STORE_F32
+    raise KernelError("gemm_skinny: output dtype")
+
+
 def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
     """out = a @ w.T (+ bias) for up to 64 rows of bfloat16 ``a``.  With
@@ -318,6 +419,11 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
         epi = EPI_STORE_F32
     else:
         raise KernelError("gemm_skinny: output dtype")
+    if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K):
+        lib = load_library("gemm_stream")
+        _check(lib.kp_gemm_stream(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                                  _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_stream")
+        return out
     lib = load_library("gemm_skinny")
     _check(lib.kp_gemm_skinny(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
                               _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_skinny")

@@ -31,6 +31,8 @@ SPLIT_MAX_SEG_LEN = 4      # steps whose longest segment is at most this use the
 
 class Attention(Part):
     category = "mixer"
+    graph_safe = True
+    accepts_normed_rows = True      # the input goes straight into ops.linear
 
     def __init__(self, params, env):
         super().__init__(params, env)

@@ -56,6 +56,10 @@ class BuildEnv:
 
 class Part:
     category = "part"
+    # True if forward() reads the step's tables from the device tensors of the context only (never from
+    # its host_* lists or other host values that change from step to step): such a part can be captured
+    # in a CUDA graph.  Parts registered from outside are not assumed to be.
+    graph_safe = False
 
     def __init__(self, params: Dict[str, Any], env: BuildEnv):
         self.params = dict(params)

@@ -18,6 +18,7 @@ from .base import Part, WeightSpec, register_part
 
 class TokenEmbedding(Part):
     category = "embedding"
+    graph_safe = True
 
     def __init__(self, params, env):
         super().__init__(params, env)
@@ -39,6 +40,7 @@ class TokenEmbedding(Part):
 
 class LMHead(Part):
     category = "head"
+    graph_safe = True
 
     def __init__(self, params, env):
         super().__init__(params, env)

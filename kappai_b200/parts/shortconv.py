@@ -29,6 +29,8 @@ MAX_KERNEL = 16
 
 class ShortConv(Part):
     category = "mixer"
+    graph_safe = True
+    accepts_normed_rows = True      # the input goes straight into ops.linear
 
     def __init__(self, params, env):
         super().__init__(params, env)
@@ -66,10 +68,13 @@ class ShortConv(Part):
         [n_slots, kernel_size - 1, hidden_size] float32."""
         p = linear(h, self.w_in, self.b_in)
         y = torch.empty((ctx.n_rows, self.d), dtype=p.dtype, device=p.device)
-        K.shortconv_forward(p, self.w_conv, self.b_conv, cache.tensor, ctx.row_seg, ctx.cu_rows, ctx.seg_pos,
-                            ctx.seg_slot, y)
-        if cache.writes:
-            K.shortconv_update_state(p, cache.tensor, ctx.cu_rows, ctx.seg_pos, ctx.seg_slot, ctx.n_seg)
+        if ctx.decode_only and cache.writes:
+            K.shortconv_decode(p, self.w_conv, self.b_conv, cache.tensor, ctx.seg_pos, ctx.seg_slot, y)
+        else:
+            K.shortconv_forward(p, self.w_conv, self.b_conv, cache.tensor, ctx.row_seg, ctx.cu_rows, ctx.seg_pos,
+                                ctx.seg_slot, y)
+            if cache.writes:
+                K.shortconv_update_state(p, cache.tensor, ctx.cu_rows, ctx.seg_pos, ctx.seg_slot, ctx.n_seg)
         linear(y, self.w_out, self.b_out, out=residual, accumulate=True)
 
 
