@@ -280,4 +280,18 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
     return kp_launch_status();
 }
 
+// The merge alone, for chunk partials that another kernel wrote into `scratch` in the same format.
+int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int window,
+                       int n, int H, int hd, int dtype, void* stream) {
+    if (n <= 0) return 0;
+    if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535) return KP_ERR_UNSUPPORTED;
+    const float* part_acc = scratch;
+    const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
+    dim3 mgrid(H, n);
+    const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
+    KP_DISPATCH_DTYPE(dtype, T, (attn_merge_kernel<T><<<mgrid, mthreads, 0, (cudaStream_t)stream>>>(
+        part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window, H, hd)));
+    return kp_launch_status();
+}
+
 }  // extern "C"

@@ -1,0 +1,429 @@
+// Tensor-core attention over the paged cache (bfloat16, head size 64 or 128).
+//
+// Two kernels share the tile machinery (K/V tiles of 64 keys brought into
+// shared memory with cp.async through the block table, swizzled so that
+// ldmatrix reads do not collide; S = Q K^T and O = P V with mma.m16n8k16;
+// softmax statistics in float32; P rounded to bfloat16 as a matrix operand):
+//
+//  * attn_split_mma: rows that each read a long cache (decode).  One CTA per
+//    (chunk of 256 keys, kv head, row); the R = H/G query heads that share the
+//    kv head are the rows of the m16 tile; each of the 4 warps takes one 64-key
+//    tile of the chunk; the warps' partial results are combined in warp order
+//    and written as the chunk's (m, l, unnormalised O) to scratch, in the format
+//    of attention_decode.cu, whose merge kernel finishes the row.
+//  * attn_prefill_mma: segments of many rows.  One CTA per (64 query rows of a
+//    segment, head): 4 warps x 16 rows, looping over the KV tiles up to the
+//    causal limit, double-buffered.
+//
+// Formulas as in attention.cu (src/backend/cpu/scalar/core.c:383-433).  Tiles
+// start at multiples of 64 of the absolute key index, chunks at multiples of
+// 256, so the order of summation does not depend on how a prompt was cut or
+// what else is in the batch.
+#include "common.cuh"
+
+#define AM_TILE 64
+#define AM_CHUNK 256
+#define AM_RMAX 8
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int sz = valid ? 16 : 0;                  // size 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                 "{%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile in shared memory: 64 rows (keys) of HD bf16; the 16-byte chunk c of row r lies at chunk c ^ (r & 7).
+template <int HD>
+__device__ __forceinline__ bf16* tile_chunk(bf16* tile, int r, int c) {
+    return tile + (size_t)r * HD + ((c ^ (r & 7)) << 3);
+}
+
+// Bring keys [k0, k0+64) of one kv head into a K tile and a V tile.  Keys outside [k_lo, k_hi] are zero-filled.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(bf16* Kt, bf16* Vt, const bf16* __restrict__ cache, const int* __restrict__ bt,
+                                             size_t page_stride, size_t k_off, size_t v_off, int page_size, int k0,
+                                             int k_lo, int k_hi, int tid, int nthreads) {
+    constexpr int CPR = HD / 8;                      // 16-byte chunks a row
+    for (int i = tid; i < AM_TILE * CPR; i += nthreads) {
+        const int r = i / CPR, c = i % CPR;
+        const int key = k0 + r;
+        const bool valid = key >= k_lo && key <= k_hi;
+        const bf16* src = cache;
+        if (valid) src = cache + (size_t)bt[key / page_size] * page_stride + (size_t)(key % page_size) * HD + c * 8;
+        cp_async16(tile_chunk<HD>(Kt, r, c), src + (valid ? k_off : 0), valid);
+        cp_async16(tile_chunk<HD>(Vt, r, c), src + (valid ? v_off : 0), valid);
+    }
+}
+
+// S[16 x 64] = Q[16 x HD] K^T for one warp; qf: the A fragments of Q (4 registers a k-step)
+template <int HD>
+__device__ __forceinline__ void qk_tile(float (&s)[8][4], const uint32_t (&qf)[HD / 16][4], bf16* Kt, int lane) {
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) s[nt][i] = 0.f;
+    const int j = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) {
+#pragma unroll
+        for (int nt = 0; nt < 8; nt += 2) {
+            uint32_t b[4];
+            ldmatrix_x4(b, tile_chunk<HD>(Kt, (nt + (j >> 1)) * 8 + r, ks * 2 + (j & 1)));
+            mma_bf16(s[nt], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[0], b[1]);
+            mma_bf16(s[nt + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[2], b[3]);
+        }
+    }
+}
+
+// O[16 x HD] += P[16 x 64] V for one warp; pf: P as A fragments (4 registers a k-step of 16 keys)
+template <int HD>
+__device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&pf)[4][4], bf16* Vt, int lane) {
+    const int j = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < 4; kk++) {
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; dn += 2) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, tile_chunk<HD>(Vt, kk * 16 + (j & 1) * 8 + r, dn + (j >> 1)));
+            mma_bf16(o[dn], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b[0], b[1]);
+            mma_bf16(o[dn + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ decode (split over chunks)
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
+                      const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
+                      const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                      int n_chunks, float scale, int window, int page_size, int H, int G) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [4][64][HD]
+    bf16* Vs = Ks + 4 * AM_TILE * HD;                             // [4][64][HD]
+    float* wO = reinterpret_cast<float*>(Vs + 4 * AM_TILE * HD);  // [4][AM_RMAX][HD]
+    float* wm = wO + 4 * AM_RMAX * HD;                            // [4][AM_RMAX]
+    float* wl = wm + 4 * AM_RMAX;                                 // [4][AM_RMAX]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int chunk = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
+    const int R = H / G;
+    const int pos = positions[row];
+    const int k_lo = window > 0 ? max(0, pos - window + 1) : 0, k_hi = pos;
+    const int c0 = chunk * AM_CHUNK;
+    if (c0 > k_hi || c0 + AM_CHUNK - 1 < k_lo) return;
+    const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
+    const size_t page_stride = (size_t)2 * G * page_size * HD;
+    const size_t k_off = (size_t)kvh * page_size * HD, v_off = ((size_t)G + kvh) * page_size * HD;
+
+#pragma unroll
+    for (int w = 0; w < 4; w++)
+        load_kv_tile<HD>(Ks + w * AM_TILE * HD, Vs + w * AM_TILE * HD, cache, bt, page_stride, k_off, v_off, page_size,
+                         c0 + w * AM_TILE, k_lo, k_hi, tid, 128);
+    cp_async_commit();
+
+    // Q of the R heads of this kv head as rows 0..R-1 of the m16 tile (rows 8..15 do not exist: R <= 8)
+    uint32_t qf[HD / 16][4];
+    {
+        const bf16* qr = q + (size_t)row * ldq + (size_t)(kvh * R + min(g, R - 1)) * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t lo = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * t);
+            uint32_t hi = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * t);
+            if (g >= R) lo = hi = 0;
+            qf[ks][0] = lo; qf[ks][1] = 0; qf[ks][2] = hi; qf[ks][3] = 0;
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    bf16* Kt = Ks + warp * AM_TILE * HD;
+    bf16* Vt = Vs + warp * AM_TILE * HD;
+    const int t0 = c0 + warp * AM_TILE;                           // first key of this warp's tile
+    float s[8][4];
+    qk_tile<HD>(s, qf, Kt, lane);
+    // row g of the tile: columns 2t, 2t+1 of each n-tile are keys t0 + nt*8 + 2t (+1)
+    float m = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int key = t0 + nt * 8 + 2 * t + i;
+            const float v = (key >= k_lo && key <= k_hi) ? s[nt][i] * scale : -INFINITY;
+            s[nt][i] = v;
+            m = fmaxf(m, v);
+        }
+    }
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    float l = 0.f;
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; nt++) {
+        const float p0 = m == -INFINITY ? 0.f : expf(s[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(s[nt][1] - m);
+        // the sum runs over the values as they enter the product (rounded to bfloat16)
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        l += __low2float(pb) + __high2float(pb);
+        pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&pb);
+        pf[nt >> 1][(nt & 1) * 2 + 1] = 0;
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    float o[HD / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; dn++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
+    pv_tile<HD>(o, pf, Vt, lane);
+
+    if (g < R) {
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; dn++) {
+            wO[((size_t)warp * AM_RMAX + g) * HD + dn * 8 + 2 * t] = o[dn][0];
+            wO[((size_t)warp * AM_RMAX + g) * HD + dn * 8 + 2 * t + 1] = o[dn][1];
+        }
+        if (t == 0) { wm[warp * AM_RMAX + g] = m; wl[warp * AM_RMAX + g] = l; }
+    }
+    __syncthreads();
+    // the four warps' partial results, combined in warp order
+    for (int e = tid; e < R * HD; e += 128) {
+        const int r = e / HD, d = e % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, wm[w * AM_RMAX + r]);
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float mw = wm[w * AM_RMAX + r];
+            if (mw != -INFINITY) acc = fmaf(wO[((size_t)w * AM_RMAX + r) * HD + d], expf(mw - M), acc);
+        }
+        part_acc[(((size_t)row * H + kvh * R + r) * n_chunks + chunk) * HD + d] = acc;
+    }
+    if (tid < R) {
+        float M = -INFINITY, L = 0.f;
+        for (int w = 0; w < 4; w++) M = fmaxf(M, wm[w * AM_RMAX + tid]);
+        for (int w = 0; w < 4; w++) {
+            const float mw = wm[w * AM_RMAX + tid];
+            if (mw != -INFINITY) L = fmaf(wl[w * AM_RMAX + tid], expf(mw - M), L);
+        }
+        float* ml = part_ml + (((size_t)row * H + kvh * R + tid) * n_chunks + chunk) * 2;
+        ml[0] = M;
+        ml[1] = L;
+    }
+}
+
+// ------------------------------------------------------------------ prefill (segments of many rows)
+// One CTA: 64 consecutive rows (tile `qt` of segment `seg`) of one head.  tile_seg / tile_q0 list the tiles.
+template <int HD>
+__global__ void __launch_bounds__(128)
+attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_rows,
+                        const int* __restrict__ seg_pos, const int* __restrict__ tile_seg,
+                        const int* __restrict__ tile_row0, bf16* __restrict__ out, int ldo, float scale, int window,
+                        int page_size, int H, int G) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [2][64][HD]
+    bf16* Vs = Ks + 2 * AM_TILE * HD;                             // [2][64][HD]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int h = blockIdx.y, kvh = h / (H / G);
+    const int seg = tile_seg[blockIdx.x];
+    const int row0 = tile_row0[blockIdx.x];                        // first row of this tile (global row index)
+    const int seg_end = cu_rows[seg + 1];
+    const int n_rows = min(64, seg_end - row0);
+    const int pos0 = seg_pos[seg] + (row0 - cu_rows[seg]);         // position of the tile's first row
+    const int* bt = block_table + (size_t)seg * max_blocks;
+    const size_t page_stride = (size_t)2 * G * page_size * HD;
+    const size_t k_off = (size_t)kvh * page_size * HD, v_off = ((size_t)G + kvh) * page_size * HD;
+
+    // keys any row of the tile may read
+    const int k_hi_all = pos0 + n_rows - 1;
+    const int k_lo_all = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int tile_lo = k_lo_all / AM_TILE, tile_hi = k_hi_all / AM_TILE;
+
+    // this warp's 16 rows: rows r0 = warp*16 + g and r0 + 8
+    const int ra = warp * 16 + g, rb = ra + 8;
+    const int pos_a = pos0 + ra, pos_b = pos0 + rb;
+    const bool has_a = ra < n_rows, has_b = rb < n_rows;
+    uint32_t qf[HD / 16][4];
+    {
+        const bf16* qa = q + (size_t)(row0 + min(ra, n_rows - 1)) * ldq + (size_t)h * HD;
+        const bf16* qb = q + (size_t)(row0 + min(rb, n_rows - 1)) * ldq + (size_t)h * HD;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            qf[ks][0] = *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 2 * t);
+            qf[ks][1] = *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 2 * t);
+            qf[ks][2] = *reinterpret_cast<const uint32_t*>(qa + ks * 16 + 8 + 2 * t);
+            qf[ks][3] = *reinterpret_cast<const uint32_t*>(qb + ks * 16 + 8 + 2 * t);
+        }
+    }
+    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0, lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int dn = 0; dn < HD / 8; dn++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+
+    load_kv_tile<HD>(Ks, Vs, cache, bt, page_stride, k_off, v_off, page_size, tile_lo * AM_TILE, k_lo_all, k_hi_all,
+                     tid, 128);
+    cp_async_commit();
+    for (int kt = tile_lo; kt <= tile_hi; kt++) {
+        const int buf = (kt - tile_lo) & 1;
+        if (kt + 1 <= tile_hi) {
+            load_kv_tile<HD>(Ks + (buf ^ 1) * AM_TILE * HD, Vs + (buf ^ 1) * AM_TILE * HD, cache, bt, page_stride, k_off,
+                             v_off, page_size, (kt + 1) * AM_TILE, k_lo_all, k_hi_all, tid, 128);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const int t0 = kt * AM_TILE;
+        // a warp whose rows all lie before this tile (causal) or after its window has nothing to do in it
+        const int w_pos_hi = pos0 + min(warp * 16 + 15, n_rows - 1);
+        const int w_lo = window > 0 ? max(0, pos0 + warp * 16 - window + 1) : 0;
+        if (warp * 16 < n_rows && t0 <= w_pos_hi && t0 + AM_TILE - 1 >= w_lo) {
+            float s[8][4];
+            qk_tile<HD>(s, qf, Ks + buf * AM_TILE * HD, lane);
+            float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int key = t0 + nt * 8 + 2 * t + i;
+                    const float va = (has_a && key <= pos_a && key >= lo_a) ? s[nt][i] * scale : -INFINITY;
+                    const float vb = (has_b && key <= pos_b && key >= lo_b) ? s[nt][2 + i] * scale : -INFINITY;
+                    s[nt][i] = va; s[nt][2 + i] = vb;
+                    mx_a = fmaxf(mx_a, va); mx_b = fmaxf(mx_b, vb);
+                }
+            }
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+            mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+            mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+            const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+            const float ca = (m_a == -INFINITY) ? 0.f : expf(m_a - mn_a), cb = (m_b == -INFINITY) ? 0.f : expf(m_b - mn_b);
+            float sa = 0.f, sb = 0.f;
+            uint32_t pf[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                const float pa0 = mn_a == -INFINITY ? 0.f : expf(s[nt][0] - mn_a), pa1 = mn_a == -INFINITY ? 0.f : expf(s[nt][1] - mn_a);
+                const float pb0 = mn_b == -INFINITY ? 0.f : expf(s[nt][2] - mn_b), pb1 = mn_b == -INFINITY ? 0.f : expf(s[nt][3] - mn_b);
+                const __nv_bfloat162 xa = __floats2bfloat162_rn(pa0, pa1), xb = __floats2bfloat162_rn(pb0, pb1);
+                sa += __low2float(xa) + __high2float(xa);
+                sb += __low2float(xb) + __high2float(xb);
+                pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&xa);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&xb);
+            }
+            sa += __shfl_xor_sync(0xffffffffu, sa, 1); sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+            sb += __shfl_xor_sync(0xffffffffu, sb, 1); sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+            l_a = l_a * ca + sa; l_b = l_b * cb + sb;
+            m_a = mn_a; m_b = mn_b;
+#pragma unroll
+            for (int dn = 0; dn < HD / 8; dn++) { o[dn][0] *= ca; o[dn][1] *= ca; o[dn][2] *= cb; o[dn][3] *= cb; }
+            pv_tile<HD>(o, pf, Vs + buf * AM_TILE * HD, lane);
+        }
+        __syncthreads();                                          // the buffer is free for the load after next
+    }
+    const float ia = l_a > 0.f ? 1.0f / l_a : 0.f, ib = l_b > 0.f ? 1.0f / l_b : 0.f;
+    if (has_a) {
+        bf16* oa = out + (size_t)(row0 + ra) * ldo + (size_t)h * HD;
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; dn++)
+            *reinterpret_cast<uint32_t*>(oa + dn * 8 + 2 * t) = pack_bf16(o[dn][0] * ia, o[dn][1] * ia);
+    }
+    if (has_b) {
+        bf16* ob = out + (size_t)(row0 + rb) * ldo + (size_t)h * HD;
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; dn++)
+            *reinterpret_cast<uint32_t*>(ob + dn * 8 + 2 * t) = pack_bf16(o[dn][2] * ib, o[dn][3] * ib);
+    }
+}
+
+template <int HD>
+static int launch_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                        const int* row_seg, const int* positions, float* part_acc, float* part_ml, int n_chunks,
+                        float scale, int window, int page_size, int n, int H, int G, cudaStream_t s) {
+    const size_t smem = (size_t)8 * AM_TILE * HD * 2 + sizeof(float) * (4 * AM_RMAX * HD + 8 * AM_RMAX);
+    cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attn_split_mma_kernel<HD><<<dim3(n_chunks, G, n), 128, smem, s>>>(
+        (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
+        n_chunks, scale, window, page_size, H, G);
+    return kp_launch_status();
+}
+
+template <int HD>
+static int launch_prefill(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                          const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0, int n_tiles,
+                          void* out, int ldo, float scale, int window, int page_size, int H, int G, cudaStream_t s) {
+    const size_t smem = (size_t)4 * AM_TILE * HD * 2;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attn_prefill_mma_kernel<HD><<<dim3(n_tiles, H), 128, smem, s>>>(
+        (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
+        (bf16*)out, ldo, scale, window, page_size, H, G);
+    return kp_launch_status();
+}
+
+extern "C" {
+
+// The chunk partials of the split pass (bfloat16, head size 64 or 128, H/G <= 8).  The caller runs the merge
+// of attention_decode.cu afterwards (kp_attention_merge) on the same scratch.
+int kp_attention_split_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                           const int* row_seg, const int* positions, float* scratch, int n_chunks, float scale,
+                           int window, int page_size, int n, int H, int G, int hd, void* stream) {
+    if (n <= 0) return 0;
+    if ((hd != 64 && hd != 128) || G < 1 || H % G || H / G > AM_RMAX || page_size < 1 || n_chunks < 1 || n > 65535 ||
+        G > 65535 || (ldq & 1))
+        return KP_ERR_UNSUPPORTED;
+    float* part_acc = scratch;
+    float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch_split<64>(q, ldq, cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
+                                          n_chunks, scale, window, page_size, n, H, G, s);
+    return launch_split<128>(q, ldq, cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml, n_chunks,
+                             scale, window, page_size, n, H, G, s);
+}
+
+// tile_seg / tile_row0: for each tile of 64 rows its segment and its first row (device arrays, n_tiles long)
+int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
+                             const int* cu_rows, const int* seg_pos, const int* tile_seg, const int* tile_row0,
+                             int n_tiles, void* out, int ldo, float scale, int window, int page_size, int H, int G,
+                             int hd, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if ((hd != 64 && hd != 128) || G < 1 || H % G || page_size < 1 || H > 65535 || (ldq & 1) || (ldo & 1))
+        return KP_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (hd == 64) return launch_prefill<64>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
+                                            n_tiles, out, ldo, scale, window, page_size, H, G, s);
+    return launch_prefill<128>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
+                               out, ldo, scale, window, page_size, H, G, s);
+}
+
+}  // extern "C"

@@ -65,6 +65,12 @@ class StepContext:
     max_seg_len: int
     max_context: int               # largest position + 1 in the batch
     decode_only: bool              # every segment has one row
+    tile_seg: Optional[torch.Tensor] = None    # int32 [n_tiles]: segment of each tile of ROW_TILE consecutive rows
+    tile_row0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first row of each tile
+    n_tiles: int = 0
+
+
+ROW_TILE = 64                      # rows of one segment that a tiled kernel (prefill attention) takes at a time
 
 
 def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int], device: torch.device,
@@ -117,8 +123,15 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
     if len(set(seg_slot.tolist())) != n_seg:
         raise BatchError("two segments of one step name the same state slot")
 
+    tile_seg, tile_row0 = [], []
+    for i in range(n_seg):
+        for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), ROW_TILE):
+            tile_seg.append(i)
+            tile_row0.append(r0)
     parts = [token_ids, positions, row_seg, cu_rows, seg_pos, seg_slot,
-             np.asarray(logit_rows, dtype=np.int32)]
+             np.asarray(logit_rows, dtype=np.int32), np.asarray(tile_seg, dtype=np.int32),
+             np.asarray(tile_row0, dtype=np.int32)]
+    n_fixed = len(parts)
     paged_host = {}
     for gk, page_size in groups.items():
         max_blocks = max(1, max(len(s.block_tables.get(gk, ())) for s in segments))
@@ -159,7 +172,8 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         host_cu_rows=cu_rows.tolist(), host_seg_pos=seg_pos.tolist(), host_seg_slot=seg_slot.tolist(),
         max_seg_len=max(len(s.tokens) for s in segments),
         max_context=max(s.pos_start + len(s.tokens) for s in segments),
-        decode_only=all(len(s.tokens) == 1 for s in segments))
+        decode_only=all(len(s.tokens) == 1 for s in segments),
+        tile_seg=piece(7), tile_row0=piece(8), n_tiles=len(tile_seg))
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
     ctx.h2d_bytes = flat.numel() * 4
     return ctx

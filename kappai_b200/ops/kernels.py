@@ -287,11 +287,50 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     if scratch.numel() < attention_split_scratch(n, H, hd, n_chunks):
         raise KernelError("attention_split: scratch too small")
     lib = load_library("attention_decode")
+    if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
+        # tensor-core chunk pass, then the same merge
+        _check(load_library("attention_mma").kp_attention_split_mma(
+            _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(row_seg),
+            _ptr(positions), _ptr(scratch), n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
+            _stream()), "attention_split_mma")
+        _check(lib.kp_attention_merge(_ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), n_chunks,
+                                      int(window or 0), n, H, hd, dtype_code(q.dtype), _stream()), "attention_merge")
+        return out
     _check(lib.kp_attention_split(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
                                   _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
                                   n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
                                   dtype_code(q.dtype), _stream()), "attention_split")
     LAUNCHES[0] += 1
+    return out
+
+
+USE_MMA_ATTENTION = True       # bfloat16 attention with head size 64 or 128 runs on the tensor cores
+PREFILL_TILE = 64              # query rows a CTA of the prefill attention kernel
+
+
+def attention_prefill_ok(q: torch.Tensor, hd: int) -> bool:
+    return USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0
+
+
+def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, cu_rows: torch.Tensor,
+                      seg_pos: torch.Tensor, tile_seg: torch.Tensor, tile_row0: torch.Tensor, out: torch.Tensor,
+                      scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+    """Tensor-core causal attention for segments of many rows.  ``tile_seg`` / ``tile_row0`` list, for every
+    tile of 64 consecutive rows of a segment, its segment and its first row."""
+    _need(q, "q", torch.bfloat16, contiguous=False); _need(cache, "cache", torch.bfloat16)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    for t_, nm in ((block_table, "block_table"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (tile_seg, "tile_seg"),
+                   (tile_row0, "tile_row0")):
+        _need(t_, nm, torch.int32)
+    n = q.shape[0]
+    if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
+        raise KernelError("attention_prefill: shape mismatch")
+    if tile_seg.numel() != tile_row0.numel():
+        raise KernelError("attention_prefill: tile lists differ in length")
+    _check(load_library("attention_mma").kp_attention_prefill_mma(
+        _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
+        _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
+        int(window or 0), page_size, H, G, hd, _stream()), "attention_prefill_mma")
     return out
 
 
