@@ -36,7 +36,7 @@
 #define ST_CHUNK 256                         // columns a chunk (one mbarrier each)
 #define ST_MAX_CHUNKS 32
 #define ST_MAX_SLAB (96 * 1024)
-#define ST_SPIN_LIMIT (1 << 22)
+#define ST_WAIT_NS 1000000000ull             // one second: far beyond any legitimate wait
 
 __device__ int g_stream_status = 0;          // 0 ok; 1: a bounded wait gave up
 
@@ -54,11 +54,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// false if the barrier did not flip within the limit
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// false if the barrier did not flip within ST_WAIT_NS
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (int i = 0; i < ST_SPIN_LIMIT; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (now_ns() - t0 > ST_WAIT_NS) return false;
+    }
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -1,0 +1,336 @@
+// C[M,N] = A[M,K] * W[N,K]^T (bfloat16 in, float32 accumulation) on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought to shared memory by TMA.
+// The product of prompt portions (M > 64 rows).
+//
+// One CTA computes a 128 x BN tile of C (BN = 128 or 256).  Roles by warp:
+//   warp 0   : TMA producer.  For every k-block of 64 it waits for a free stage, arms the stage's "full"
+//              mbarrier with the byte count and issues the tiled loads of the A box (128 rows x 64) and the
+//              W box (BN rows x 64), both with the 128-byte swizzle, no multicast.
+//   warp 1   : allocates BN columns of tensor memory, then one lane issues the MMAs: four tcgen05.mma
+//              (128 x BN x 16) per stage, descriptors advanced by 32 bytes inside the swizzled rows;
+//              tcgen05.commit frees the stage ("empty" mbarrier) and, after the last k-block, signals
+//              "accumulator ready".
+//   warps 2-5: epilogue.  Each reads its 32 lanes of tensor memory with tcgen05.ld (32 columns at a
+//              time), applies bias / residual accumulation / SwiGLU and writes its rows of C.
+// Rows of A beyond M and rows of W beyond N are zero-filled by TMA (out-of-bounds fill) and masked at the
+// store; K needs no padding (the tail of the last k-block is zero-filled too) but K % 8 == 0 (16-byte rows).
+// Each output row sums its k-blocks in order, so a row's result does not depend on M.
+//
+// SwiGLU epilogue: W holds gate rows then up rows (ff apart).  The CTA's W tile is 128 gate rows and the
+// matching 128 up rows (two TMA boxes into one 256-row tile), so accumulator columns c and 128 + c are the
+// gate and up of one output column: the epilogue writes silu(gate) * up.
+//
+// Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
+// stops issuing work, still frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define EPI_STORE 0
+#define EPI_STORE_F32 1
+#define EPI_ACCUM_F32 2
+#define EPI_SWIGLU 3
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192                      // 6 warps
+#define TC_WAIT_NS 1000000000ull            // one second: far beyond any legitimate wait
+
+__device__ int g_tc_status = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// false if the barrier did not flip within TC_WAIT_NS
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = now_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (now_ns() - t0 > TC_WAIT_NS) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes (64 bf16), stored with
+// the 128-byte swizzle in atoms of 8 rows (1024 bytes): start address, leading offset 1 (16 bytes; unused by
+// swizzled K-major layouts), stride offset 1024 bytes between 8-row groups, version 1, layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N and M of the MMA.
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+struct TcArgs {
+    const float* bias;
+    void* C; int ldc;
+    int M, N, K, ff;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const TcArgs p) {
+    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr int N_OUT_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;       // output columns of the tile
+    extern __shared__ unsigned char smem[];
+    // STAGES x (A tile | B tile); the swizzled tiles must start on 1024-byte boundaries
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * (A_BYTES + B_BYTES));
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * N_OUT_TILE;
+    const int n_kb = (p.K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < n_kb; kb++) {
+                const int s = kb % STAGES;
+                if (!mbar_wait_bounded(&empty[s], ((kb / STAGES) & 1) ^ 1)) { *abort_flag = 1; break; }
+                unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
+                unsigned char* b_dst = a_dst + A_BYTES;
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
+                if (EPI == EPI_SWIGLU) {
+                    tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
+                    tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
+                } else {
+                    tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; kb++) {
+                const int s = kb % STAGES;
+                if (!mbar_wait_bounded(&full[s], (kb / STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
+                const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++)          // 32 bytes along K inside the swizzled row: +2 in the address field
+                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                umma_commit(&empty[s]);                        // the stage is free when these MMAs have read it
+            }
+            umma_commit(acc_ready);                            // arrives when every MMA above has completed
+        }
+    } else {
+        // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory = rows m0 + that
+        const int q = warp & 3;
+        const bool ready = mbar_wait_bounded(acc_ready, 0);
+        tc_fence_after();
+        if (ready && !*abort_flag) {
+            const int m = m0 + q * 32 + lane;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < N_OUT_TILE; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(lane_base + c, r);
+                uint32_t u[32];
+                if (EPI == EPI_SWIGLU) tmem_ld32(lane_base + BN / 2 + c, u);
+                if (m < p.M) {
+                    const int n_base = n0 + c;
+                    const int n_lim = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+                        bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (n_base + j < n_lim) {
+                                float v = __uint_as_float(r[j]);
+                                if (p.bias) v += p.bias[n_base + j];
+                                if (EPI == EPI_SWIGLU) {
+                                    float up = __uint_as_float(u[j]);
+                                    if (p.bias) up += p.bias[p.ff + n_base + j];
+                                    // gate and up are rounded to the storage type first, as the unfused path stores them
+                                    const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(up));
+                                    v = (gq / (1.0f + expf(-gq))) * uq;
+                                }
+                                dst[j] = from_f32<bf16>(v);
+                            }
+                        }
+                    } else {
+                        float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (n_base + j < n_lim) {
+                                float v = __uint_as_float(r[j]);
+                                if (p.bias) v += p.bias[n_base + j];
+                                if (EPI == EPI_ACCUM_F32) v += dst[j];
+                                dst[j] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(&g_tc_status, 1);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, BN);
+}
+
+// ------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x K bf16, row stride ld elements; box 64 (K) x box_rows, 128-byte swizzle, zero fill out of bounds
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return KP_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : KP_ERR_BAD_ARG;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const TcArgs& a, cudaStream_t s) {
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
+    const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+    dim3 grid((n_out + n_tile - 1) / n_tile, (a.M + TC_BM - 1) / TC_BM);
+    kern<<<grid, TC_THREADS, smem, s>>>(ta, tw, a);
+    return kp_launch_status();
+}
+
+extern "C" {
+
+// epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16)
+int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+               int K, int epi, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
+    if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
+    TcArgs a = {};
+    a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.ff = 0;
+    if (epi == EPI_SWIGLU) {
+        if (N & 1) return KP_ERR_BAD_ARG;
+        a.ff = N / 2;
+    }
+    const int n_out = epi == EPI_SWIGLU ? a.ff : N;
+    // the wide tile where it still fills the GPU, else the narrow one
+    const bool wide = epi != EPI_SWIGLU && ((long long)((n_out + 255) / 256) * ((M + TC_BM - 1) / TC_BM) >= 148);
+    alignas(64) CUtensorMap ta, tw;
+    int st = make_map(&ta, A, M, K, lda, TC_BM);
+    if (st) return st;
+    st = make_map(&tw, W, N, K, ldw, epi == EPI_SWIGLU ? 128 : (wide ? 256 : 128));
+    if (st) return st;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (epi) {
+        case EPI_STORE: return wide ? launch<256, 4, EPI_STORE>(ta, tw, a, s) : launch<128, 6, EPI_STORE>(ta, tw, a, s);
+        case EPI_STORE_F32: return wide ? launch<256, 4, EPI_STORE_F32>(ta, tw, a, s) : launch<128, 6, EPI_STORE_F32>(ta, tw, a, s);
+        case EPI_ACCUM_F32: return wide ? launch<256, 4, EPI_ACCUM_F32>(ta, tw, a, s) : launch<128, 6, EPI_ACCUM_F32>(ta, tw, a, s);
+        case EPI_SWIGLU: return launch<256, 4, EPI_SWIGLU>(ta, tw, a, s);
+        default: return KP_ERR_BAD_ARG;
+    }
+}
+
+// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
+int kp_tc_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -347,7 +347,44 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-USE_STREAM = True          # few-row products go to the bulk-copy kernel where their shape fits it
+USE_TC = True              # bfloat16 products of more than 64 rows run on tcgen05 tensor cores
+
+
+def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Can the tcgen05 kernel take this product (bfloat16, 16-byte aligned rows, K a multiple of 8)?"""
+    return (USE_TC and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
+    """out = a @ w.T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); with
+    ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
+    _need(out, "out", contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    n_out = N // 2 if swiglu else N
+    if w.shape[1] != K or out.shape != (M, n_out):
+        raise KernelError(f"gemm_tc: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm_tc: bias size")
+    epi = _skinny_epilogue(out, accumulate, swiglu)
+    lib = load_library("gemm_tc")
+    _check(lib.kp_gemm_tc(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                          _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_tc")
+    return out
+
+
+def tc_status() -> int:
+    """0, or 1 if a bounded wait of the tcgen05 kernel gave up since the last call (synchronises)."""
+    return int(load_library("gemm_tc").kp_tc_status())
+
+
+USE_STREAM = True         # few-row products go to the bulk-copy kernel where their shape fits it
 STREAM_CHUNK = 256
 STREAM_MAX_SLAB = 96 * 1024
 

@@ -3,7 +3,8 @@
 One door for every product of the model; it picks the kernel by dtype and
 shape: float32 operands always run the CUDA-core float32 kernel (the true
 32-bit path); bfloat16 products of up to 64 rows run the weight-streaming
-kernel (decode steps).  The product is this package's own kernel in every
+kernels (decode steps), larger ones the tcgen05 tensor-core kernel (prompt
+portions).  The product is this package's own kernel in every
 case; no library matrix product is called.
 
 The left operand may be a :class:`NormedRows`: "the RMSNorm of these float32
@@ -88,6 +89,8 @@ def linear(a: Operand, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
         raise K.KernelError(f"linear: operand dtypes {a.dtype} and {w.dtype} do not go together")
     if K.skinny_ok(a, w):
         return K.gemm_skinny(a, w, out, bias, accumulate)
+    if K.tc_ok(a, w) and out.stride(1) == 1:
+        return K.gemm_tc(a, w, out, bias, accumulate)
     return K.gemm_nt_simt(a, w, out, bias, accumulate)
 
 
@@ -102,5 +105,7 @@ def linear_swiglu(a: Operand, w_gate_up: torch.Tensor, bias: Optional[torch.Tens
     a = as_tensor(a)
     if K.skinny_ok(a, w_gate_up):
         return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True)
+    if K.tc_ok(a, w_gate_up):
+        return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True)
     gu = linear(a, w_gate_up, bias)
     return K.swiglu(gu, act)
