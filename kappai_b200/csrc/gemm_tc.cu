@@ -122,7 +122,13 @@ struct TcArgs {
     const float* bias;
     void* C; int ldc;
     int M, N, K, ff;
+    int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
 };
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+}
 
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
@@ -205,32 +211,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (m < p.M) {
                     const int n_base = n0 + c;
                     const int n_lim = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+                    // the 32 values of this thread's row, finished
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float x = __uint_as_float(r[j]);
+                        if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
+                        if (EPI == EPI_SWIGLU) {
+                            float up = __uint_as_float(u[j]);
+                            if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
+                            // gate and up are rounded to the storage type first, as the unfused path stores them
+                            const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
+                            x = (gq / (1.0f + expf(-gq))) * uq;
+                        }
+                        v[j] = x;
+                    }
+                    const bool whole = p.vec_ok && n_base + 32 <= n_lim;      // 16-byte stores of the whole piece
                     if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
                         bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
+                        if (whole) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (n_base + j < n_lim) {
-                                float v = __uint_as_float(r[j]);
-                                if (p.bias) v += p.bias[n_base + j];
-                                if (EPI == EPI_SWIGLU) {
-                                    float up = __uint_as_float(u[j]);
-                                    if (p.bias) up += p.bias[p.ff + n_base + j];
-                                    // gate and up are rounded to the storage type first, as the unfused path stores them
-                                    const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(up));
-                                    v = (gq / (1.0f + expf(-gq))) * uq;
-                                }
-                                dst[j] = from_f32<bf16>(v);
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 o;
+                                o.x = pack2(v[j], v[j + 1]); o.y = pack2(v[j + 2], v[j + 3]);
+                                o.z = pack2(v[j + 4], v[j + 5]); o.w = pack2(v[j + 6], v[j + 7]);
+                                *reinterpret_cast<uint4*>(dst + j) = o;
                             }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (n_base + j < n_lim) dst[j] = from_f32<bf16>(v[j]);
                         }
                     } else {
                         float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
+                        if (whole) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            if (n_base + j < n_lim) {
-                                float v = __uint_as_float(r[j]);
-                                if (p.bias) v += p.bias[n_base + j];
-                                if (EPI == EPI_ACCUM_F32) v += dst[j];
-                                dst[j] = v;
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if (EPI == EPI_ACCUM_F32) {
+                                    const float4 c4 = *reinterpret_cast<const float4*>(dst + j);
+                                    o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
+                                }
+                                *reinterpret_cast<float4*>(dst + j) = o;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                if (n_base + j < n_lim) {
+                                    float x = v[j];
+                                    if (EPI == EPI_ACCUM_F32) x += dst[j];
+                                    dst[j] = x;
+                                }
                             }
                         }
                     }
@@ -303,6 +334,10 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
     TcArgs a = {};
     a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K; a.ff = 0;
+    {
+        const int esz = (epi == EPI_STORE || epi == EPI_SWIGLU) ? 2 : 4;
+        a.vec_ok = (((uintptr_t)C & 15) == 0 && ((size_t)ldc * esz) % 16 == 0) ? 1 : 0;
+    }
     if (epi == EPI_SWIGLU) {
         if (N & 1) return KP_ERR_BAD_ARG;
         a.ff = N / 2;
