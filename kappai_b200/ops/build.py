@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 # the kernel libraries of this package, in csrc/
-LIBRARIES = ["rowwise", "gemm_simt", "gemm_skinny", "gemm_stream", "gemm_tc", "shortconv", "qkrope", "attention", "attention_decode", "attention_mma", "sampling"]
+LIBRARIES = ["rowwise", "gemm_simt", "gemm_skinny", "gemm_stream", "gemm_tc", "shortconv", "qkrope", "attention", "attention_decode", "attention_mma", "attention_noalloc", "sampling"]
 
 
 class KernelBuildError(RuntimeError):
@@ -63,9 +63,17 @@ def _headers() -> List[str]:
     return sorted(os.path.join(CSRC_DIR, f) for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
 
 
+def _included_sources(src: str) -> List[str]:
+    """``.cu`` files that ``src`` includes by name (a library built on another's kernels)."""
+    import re
+    with open(src, "r", encoding="utf-8") as f:
+        names = re.findall(r'^\s*#include\s+"([^"]+\.cu)"', f.read(), flags=re.M)
+    return [os.path.join(CSRC_DIR, n) for n in names if os.path.isfile(os.path.join(CSRC_DIR, n))]
+
+
 def _digest(src: str, extra_flags: List[str]) -> str:
     h = hashlib.sha256()
-    for p in [src] + _headers():
+    for p in [src] + _included_sources(src) + _headers():
         with open(p, "rb") as f:
             h.update(os.path.basename(p).encode())
             h.update(f.read())
