@@ -25,6 +25,7 @@ attention_rows_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, T* __restrict__ out, int ldo, float scale, int window,
                       int page_size, int H, int G, int hd) {
+    kp_pdl_begin();
     __shared__ float qs[KP_MAX_HEAD_DIM];
     __shared__ float ps[ATT_THREADS];
     __shared__ float red[32];
@@ -89,7 +90,7 @@ extern "C" int kp_attention_rows(const void* q, int ldq, const void* cache, cons
     if (G < 1 || H % G != 0 || page_size < 1) return KP_ERR_BAD_ARG;
     if (n > 65535) return KP_ERR_UNSUPPORTED;
     dim3 grid(H, n);
-    KP_DISPATCH_DTYPE(dtype, T, (attention_rows_kernel<T><<<grid, ATT_THREADS, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attention_rows_kernel<T>, dim3(grid), dim3(ATT_THREADS), 0, (cudaStream_t)stream, 
         (const T*)q, ldq, (const T*)cache, block_table, max_blocks, row_seg, positions, (T*)out, ldo, scale, window,
         page_size, H, G, hd)));
     return kp_launch_status();

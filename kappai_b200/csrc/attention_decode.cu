@@ -50,6 +50,7 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
                   int max_blocks, const int* __restrict__ row_seg, const int* __restrict__ positions,
                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_chunks, float scale, int window,
                   int page_size, int H, int G, int hd_rt) {
+    kp_pdl_begin();
     extern __shared__ float smem[];
     const int hd = HD ? HD : hd_rt;
     const int R = RR ? RR : H / G;
@@ -217,6 +218,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                   int window, int H, int hd) {
+    kp_pdl_begin();
     const int h = blockIdx.x, row = blockIdx.y;
     int k_lo, k_hi;
     key_range(positions[row], window, k_lo, k_hi);
@@ -265,7 +267,7 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
     dim3 mgrid(H, n);
     const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
 #define AD_LAUNCH(T, HD, RR)                                                                                      \
-    attn_split_kernel<T, HD, RR><<<grid, AD_THREADS, smem, s>>>((const T*)q, ldq, (const T*)cache, block_table,       \
+    kp_launch_pdl(attn_split_kernel<T, HD, RR>, dim3(grid), dim3(AD_THREADS), smem, s, (const T*)q, ldq, (const T*)cache, block_table,       \
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
                                                                 n_chunks, scale, window, page_size, H, G, hd)
     KP_DISPATCH_DTYPE(dtype, T, {
@@ -273,7 +275,7 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
         else if (hd == 64) AD_LAUNCH(T, 64, 0);
         else if (hd == 128) AD_LAUNCH(T, 128, 0);
         else AD_LAUNCH(T, 0, 0);
-        attn_merge_kernel<T><<<mgrid, mthreads, 0, s>>>(part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window,
+        kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window,
                                                         H, hd);
     });
 #undef AD_LAUNCH
@@ -289,7 +291,7 @@ int kp_attention_merge(const int* positions, void* out, int ldo, const float* sc
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     dim3 mgrid(H, n);
     const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
-    KP_DISPATCH_DTYPE(dtype, T, (attn_merge_kernel<T><<<mgrid, mthreads, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, (cudaStream_t)stream, 
         part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window, H, hd)));
     return kp_launch_status();
 }

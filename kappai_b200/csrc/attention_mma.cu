@@ -121,6 +121,7 @@ attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restric
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
                       int n_chunks, float scale, int window, int page_size, int H, int G) {
+    kp_pdl_begin();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [4][64][HD]
     bf16* Vs = Ks + 4 * AM_TILE * HD;                             // [4][64][HD]
@@ -244,6 +245,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
                         const int* __restrict__ seg_pos, const int* __restrict__ tile_seg,
                         const int* __restrict__ tile_row0, bf16* __restrict__ out, int ldo, float scale, int window,
                         int page_size, int H, int G) {
+    kp_pdl_begin();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [2][64][HD]
     bf16* Vs = Ks + 2 * AM_TILE * HD;                             // [2][64][HD]
@@ -372,7 +374,7 @@ static int launch_split(const void* q, int ldq, const void* cache, const int* bl
     const size_t smem = (size_t)8 * AM_TILE * HD * 2 + sizeof(float) * (4 * AM_RMAX * HD + 8 * AM_RMAX);
     cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_split_mma_kernel<HD><<<dim3(n_chunks, G, n), 128, smem, s>>>(
+    kp_launch_pdl(attn_split_mma_kernel<HD>, dim3(dim3(n_chunks, G, n)), dim3(128), smem, s, 
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
         n_chunks, scale, window, page_size, H, G);
     return kp_launch_status();
@@ -385,7 +387,7 @@ static int launch_prefill(const void* q, int ldq, const void* cache, const int* 
     const size_t smem = (size_t)4 * AM_TILE * HD * 2;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    attn_prefill_mma_kernel<HD><<<dim3(n_tiles, H), 128, smem, s>>>(
+    kp_launch_pdl(attn_prefill_mma_kernel<HD>, dim3(dim3(n_tiles, H)), dim3(128), smem, s, 
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0,
         (bf16*)out, ldo, scale, window, page_size, H, G);
     return kp_launch_status();

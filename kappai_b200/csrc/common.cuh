@@ -66,6 +66,31 @@ __device__ __forceinline__ float block_max(float v, float* smem) {
     return r;
 }
 
+// Programmatic dependent launch.  Every kernel of this package is launched with the attribute that lets
+// it start while the kernel before it in the stream is still running, and begins with kp_pdl_begin():
+// it waits until that kernel has finished and its writes are visible, then lets the kernel after it
+// start in turn.  So launch latency and a kernel's ramp-up hide under its predecessor.  Only work that
+// depends on nothing written by earlier kernels (loading weights) may come before kp_pdl_begin().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void kp_pdl_begin() { pdl_wait(); pdl_launch_dependents(); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t kp_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                        Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int kp_launch_status() {
     cudaError_t e = cudaGetLastError();
     return (int)e;

@@ -17,6 +17,7 @@ template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_nt_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* __restrict__ bias,
                     void* __restrict__ Cv, int M, int N, int K, int lda, int ldw, int ldc) {
+    kp_pdl_begin();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -76,11 +77,11 @@ static int launch(const void* A, const void* W, const float* bias, void* C, int 
                   int ldc, int epi, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (epi == EPI_STORE)
-        gemm_nt_simt_kernel<T, EPI_STORE><<<grid, 256, 0, s>>>((const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
+        kp_launch_pdl(gemm_nt_simt_kernel<T, EPI_STORE>, dim3(grid), dim3(256), 0, s, (const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
     else if (epi == EPI_STORE_F32)
-        gemm_nt_simt_kernel<T, EPI_STORE_F32><<<grid, 256, 0, s>>>((const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
+        kp_launch_pdl(gemm_nt_simt_kernel<T, EPI_STORE_F32>, dim3(grid), dim3(256), 0, s, (const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
     else if (epi == EPI_ACCUM_F32)
-        gemm_nt_simt_kernel<T, EPI_ACCUM_F32><<<grid, 256, 0, s>>>((const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
+        kp_launch_pdl(gemm_nt_simt_kernel<T, EPI_ACCUM_F32>, dim3(grid), dim3(256), 0, s, (const T*)A, (const T*)W, bias, C, M, N, K, lda, ldw, ldc);
     else
         return KP_ERR_BAD_ARG;
     return kp_launch_status();

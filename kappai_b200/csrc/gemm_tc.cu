@@ -133,6 +133,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const TcArgs p) {
+    kp_pdl_begin();
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr int N_OUT_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;       // output columns of the tile
     extern __shared__ unsigned char smem[];
@@ -320,7 +321,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const TcArgs& a,
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
     dim3 grid((n_out + n_tile - 1) / n_tile, (a.M + TC_BM - 1) / TC_BM);
-    kern<<<grid, TC_THREADS, smem, s>>>(ta, tw, a);
+    kp_launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, s, ta, tw, a);
     return kp_launch_status();
 }
 

@@ -25,6 +25,7 @@ qk_norm_rope_kv_kernel(const T* qkv, int ld, const float* __restrict__ q_w,
                        const int* __restrict__ positions, const int* __restrict__ slot_map,
                        T* q_out, int ldq, T* __restrict__ cache, int page_size,
                        int H, int G, int hd, int write_kv) {
+    kp_pdl_begin();
     __shared__ float buf[4][KP_MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.x * 4 + warp;          // 0..H-1 q, H..H+G-1 k, H+G..H+2G-1 v
@@ -86,7 +87,7 @@ extern "C" int kp_qk_norm_rope_kv(const void* qkv, int ld, const float* q_w, con
     if (cos_tab && (rot < 2 || rot > hd || (rot & 1))) return KP_ERR_BAD_ARG;
     if (n > 65535) return KP_ERR_UNSUPPORTED;
     dim3 grid((H + 2 * G + 3) / 4, n);
-    KP_DISPATCH_DTYPE(dtype, T, (qk_norm_rope_kv_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(qk_norm_rope_kv_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)qkv, ld, q_w, k_w, eps, cos_tab, sin_tab, rot, interleaved, positions, slot_map, (T*)q_out, ldq,
         (T*)cache, page_size, H, G, hd, write_kv)));
     return kp_launch_status();

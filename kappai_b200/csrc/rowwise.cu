@@ -7,6 +7,7 @@
 template <typename T>
 __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ x, int d, float scale) {
+    kp_pdl_begin();
     const int r = blockIdx.x;
     const T* src = table + (size_t)ids[r] * d;
     float* dst = x + (size_t)r * d;
@@ -18,6 +19,7 @@ __global__ void embed_rows_kernel(const T* __restrict__ table, const int* __rest
 template <typename T>
 __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                     T* __restrict__ y, const int* __restrict__ rows, int d, float eps) {
+    kp_pdl_begin();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float* src = x + (size_t)(rows ? rows[r] : r) * d;
@@ -38,6 +40,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 rmsnorm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
                         const int* __restrict__ rows, int d, float eps) {
+    kp_pdl_begin();
     __shared__ float red[32];
     const int r = blockIdx.x;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
@@ -75,6 +78,7 @@ rmsnorm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ w
 // gate_up rows hold [gate(ff) | up(ff)].
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int n, int ff) {
+    kp_pdl_begin();
     const size_t total = (size_t)n * ff;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t r = i / ff, c = i % ff;
@@ -86,6 +90,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ act, int
 
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    kp_pdl_begin();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_f32<TO>(to_f32(in[i]));
 }
@@ -101,7 +106,7 @@ extern "C" {
 
 int kp_embed_rows(const void* table, const int* ids, float* x, int n, int d, float scale, int dtype, void* stream) {
     if (n <= 0) return 0;
-    KP_DISPATCH_DTYPE(dtype, T, (embed_rows_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, x, d, scale)));
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(embed_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, x, d, scale)));
     return kp_launch_status();
 }
 
@@ -110,17 +115,17 @@ int kp_rmsnorm_rows(const float* x, const float* w, void* y, const int* rows, in
     if (n <= 0) return 0;
     if ((d & 3) == 0 && d <= 8192 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
         // which kernel runs depends on the row's size and alignment only, never on the batch
-        KP_DISPATCH_DTYPE(dtype, T, (rmsnorm_rows_vec_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>(x, w, (T*)y, rows, d, eps)));
+        KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
         return kp_launch_status();
     }
-    KP_DISPATCH_DTYPE(dtype, T, (rmsnorm_rows_kernel<T><<<n, 256, 0, (cudaStream_t)stream>>>(x, w, (T*)y, rows, d, eps)));
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
     return kp_launch_status();
 }
 
 int kp_swiglu(const void* gate_up, void* act, int n, int ff, int dtype, void* stream) {
     if (n <= 0) return 0;
     const int g = grid_for((size_t)n * ff, 256);
-    KP_DISPATCH_DTYPE(dtype, T, (swiglu_kernel<T><<<g, 256, 0, (cudaStream_t)stream>>>((const T*)gate_up, (T*)act, n, ff)));
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(swiglu_kernel<T>, dim3(g), dim3(256), 0, (cudaStream_t)stream, (const T*)gate_up, (T*)act, n, ff)));
     return kp_launch_status();
 }
 
@@ -130,9 +135,9 @@ int kp_cast(const void* in, void* out, long long n, int dtype_in, int dtype_out,
     const int g = grid_for((size_t)n, 256);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype_in == KP_DTYPE_F32 && dtype_out == KP_DTYPE_BF16)
-        cast_kernel<float, bf16><<<g, 256, 0, s>>>((const float*)in, (bf16*)out, (size_t)n);
+        kp_launch_pdl(cast_kernel<float, bf16>, dim3(g), dim3(256), 0, s, (const float*)in, (bf16*)out, (size_t)n);
     else if (dtype_in == KP_DTYPE_BF16 && dtype_out == KP_DTYPE_F32)
-        cast_kernel<bf16, float><<<g, 256, 0, s>>>((const bf16*)in, (float*)out, (size_t)n);
+        kp_launch_pdl(cast_kernel<bf16, float>, dim3(g), dim3(256), 0, s, (const bf16*)in, (float*)out, (size_t)n);
     else
         return KP_ERR_BAD_ARG;
     return kp_launch_status();

@@ -27,6 +27,7 @@ __device__ __forceinline__ unsigned int order_key(float f) {
 // positive logit by the penalty or multiplies a non-positive one (:205-216)
 __global__ void repeat_penalty_kernel(float* __restrict__ logits, int V, const int* __restrict__ recent,
                                       int max_recent, const float* __restrict__ penalty) {
+    kp_pdl_begin();
     const int row = blockIdx.x;
     const float pen = penalty[row];
     if (pen == 1.0f) return;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
                    const float* __restrict__ uniform, int* __restrict__ out) {
+    kp_pdl_begin();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     __shared__ double s_pref[SAMPLE_THREADS];
@@ -264,6 +266,7 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+    kp_pdl_begin();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     const int r = block_argmax(logits + (size_t)blockIdx.x * V, V, 1.0f, s_val, s_idx, nullptr);
@@ -275,6 +278,7 @@ argmax_rows_kernel(const float* __restrict__ logits, int V, int* __restrict__ ou
 #define ARGMAX_SLICES 32
 __global__ void __launch_bounds__(256)
 argmax_slices_kernel(const float* __restrict__ logits, int V, float* __restrict__ part_val, int* __restrict__ part_idx) {
+    kp_pdl_begin();
     __shared__ float s_val[32];
     __shared__ int s_idx[32];
     const int row = blockIdx.y, sl = blockIdx.x;
@@ -290,6 +294,7 @@ argmax_slices_kernel(const float* __restrict__ logits, int V, float* __restrict_
 }
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                     int* __restrict__ out) {
+    kp_pdl_begin();
     const int row = blockIdx.x, lane = threadIdx.x;
     float bv = part_val[row * ARGMAX_SLICES + lane];
     int bi = part_idx[row * ARGMAX_SLICES + lane];
@@ -309,12 +314,12 @@ int kp_argmax_rows(const float* logits, int n, int V, int* out, void* scratch, v
     if (V < 1) return KP_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (scratch == nullptr || V < 8192 || n > 65535) {
-        argmax_rows_kernel<<<n, SAMPLE_THREADS, 0, s>>>(logits, V, out);
+        kp_launch_pdl(argmax_rows_kernel, dim3(n), dim3(SAMPLE_THREADS), 0, s, logits, V, out);
     } else {
         float* pv = (float*)scratch;
         int* pi = (int*)(pv + (size_t)n * ARGMAX_SLICES);
-        argmax_slices_kernel<<<dim3(ARGMAX_SLICES, n), 256, 0, s>>>(logits, V, pv, pi);
-        argmax_final_kernel<<<n, 32, 0, s>>>(pv, pi, out);
+        kp_launch_pdl(argmax_slices_kernel, dim3(dim3(ARGMAX_SLICES, n)), dim3(256), 0, s, logits, V, pv, pi);
+        kp_launch_pdl(argmax_final_kernel, dim3(n), dim3(32), 0, s, pv, pi, out);
     }
     return kp_launch_status();
 }
@@ -322,7 +327,7 @@ int kp_argmax_rows(const float* logits, int n, int V, int* out, void* scratch, v
 int kp_repeat_penalty(float* logits, int n, int V, const int* recent, int max_recent, const float* penalty,
                       void* stream) {
     if (n <= 0 || max_recent <= 0) return 0;
-    repeat_penalty_kernel<<<n, 128, 0, (cudaStream_t)stream>>>(logits, V, recent, max_recent, penalty);
+    kp_launch_pdl(repeat_penalty_kernel, dim3(n), dim3(128), 0, (cudaStream_t)stream, logits, V, recent, max_recent, penalty);
     return kp_launch_status();
 }
 
@@ -331,7 +336,7 @@ int kp_sample_rows(const float* logits, int n, int V, const float* temperature, 
                    const float* min_p, const float* uniform, int* out, void* stream) {
     if (n <= 0) return 0;
     if (V < 1) return KP_ERR_BAD_ARG;
-    sample_rows_kernel<<<n, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, V, temperature, top_k, top_p, min_p,
+    kp_launch_pdl(sample_rows_kernel, dim3(n), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, V, temperature, top_k, top_p, min_p,
                                                                        uniform, out);
     return kp_launch_status();
 }

@@ -32,6 +32,7 @@ __global__ void shortconv_fwd_kernel(const T* __restrict__ p, int ldp, const flo
                                      const int* __restrict__ row_seg, const int* __restrict__ cu_rows,
                                      const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
                                      T* __restrict__ out, int ldo, int n, int d, int K) {
+    kp_pdl_begin();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int row = blockIdx.y;
     if (c >= d || row >= n) return;
@@ -65,6 +66,7 @@ template <typename T>
 __global__ void shortconv_state_kernel(const T* __restrict__ p, int ldp, float* __restrict__ state,
                                        const int* __restrict__ cu_rows, const int* __restrict__ seg_pos,
                                        const int* __restrict__ seg_slot, int n_seg, int d, int K) {
+    kp_pdl_begin();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int seg = blockIdx.y;
     if (c >= d || seg >= n_seg) return;
@@ -88,6 +90,7 @@ __global__ void shortconv_decode_kernel(const T* __restrict__ p, int ldp, const 
                                         const float* __restrict__ bias, float* __restrict__ state,
                                         const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
                                         T* __restrict__ out, int ldo, int n, int d, int K) {
+    kp_pdl_begin();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int row = blockIdx.y;
     if (c >= d || row >= n) return;
@@ -117,7 +120,7 @@ int kp_shortconv_decode(const void* p, int ldp, const float* w, const float* bia
     if (n <= 0) return 0;
     if (K < 2 || K > KP_CONV_MAX_K || n > 65535) return KP_ERR_UNSUPPORTED;
     dim3 grid((d + 127) / 128, n);
-    KP_DISPATCH_DTYPE(dtype, T, (shortconv_decode_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(shortconv_decode_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)p, ldp, w, bias, state, seg_pos, seg_slot, (T*)out, ldo, n, d, K)));
     return kp_launch_status();
 }
@@ -130,7 +133,7 @@ int kp_shortconv_forward(const void* p, int ldp, const float* w, const float* bi
     if (n > 65535 * 32) return KP_ERR_UNSUPPORTED;
     dim3 grid((d + 127) / 128, n);
     if (n > 65535) return KP_ERR_UNSUPPORTED;
-    KP_DISPATCH_DTYPE(dtype, T, (shortconv_fwd_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(shortconv_fwd_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)p, ldp, w, bias, state, row_seg, cu_rows, seg_pos, seg_slot, (T*)out, ldo, n, d, K)));
     return kp_launch_status();
 }
@@ -140,7 +143,7 @@ int kp_shortconv_update_state(const void* p, int ldp, float* state, const int* c
     if (n_seg <= 0) return 0;
     if (K < 2 || K > KP_CONV_MAX_K || n_seg > 65535) return KP_ERR_UNSUPPORTED;
     dim3 grid((d + 127) / 128, n_seg);
-    KP_DISPATCH_DTYPE(dtype, T, (shortconv_state_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>(
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(shortconv_state_kernel<T>, dim3(grid), dim3(128), 0, (cudaStream_t)stream, 
         (const T*)p, ldp, state, cu_rows, seg_pos, seg_slot, n_seg, d, K)));
     return kp_launch_status();
 }
