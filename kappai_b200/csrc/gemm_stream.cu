@@ -1,29 +1,30 @@
-// C[M,N] = A[M,K] * W[N,K]^T for few rows (M <= 64), weights streamed by the
-// bulk-copy engine: the decode-step product for the usual layer shapes.
+// C[M,N] = A[M,K] * W[N,K]^T for few rows (M <= 64), weights streamed by the bulk-copy engine through a
+// ring in shared memory: the decode-step product for the usual layer shapes.
 //
-// A CTA owns 8 rows of W (one n8 tile of mma.m16n8k16, batch rows on the m
-// side; 2 x 8 rows for the SwiGLU epilogue).  At its start, before anything
-// that depends on the kernel before it, it issues cp.async.bulk copies of its
-// whole slab of W (8 rows x K) into shared memory, chunk by chunk of 256
-// columns, each chunk signalling an mbarrier.  So the bytes in flight per SM
-// are the slabs of its resident CTAs (tens of KB each), not what registers can
-// hold.  The four warps then take the k-blocks of 32 of each chunk as it lands
-// (block b of a chunk goes to warp b % 4), read W fragments from shared memory
-// (rows padded so that the 16-byte fragment reads do not collide in banks) and
-// activation fragments from global memory, which L1 serves after the first CTA
-// of an SM.  The warps' partial sums are added in warp order: an output depends
-// on its own activation row only, whatever M is.
+// The work is reading W once from HBM, and a decode step is a chain of such products, each only a few
+// microseconds long.  So the kernel is built to keep HBM busy across kernel boundaries:
 //
-// Fused in front (NORM, M <= 16): A = bf16((x * rsqrt(mean(x^2)+eps)) * w) of
-// the float32 residual rows (src/backend/cpu/scalar/quants.c:1489-1512).
-// Epilogues: bias; store bf16 / fp32; accumulate into fp32; SwiGLU.
+//  * Persistent CTAs, two an SM.  A CTA walks the 8-row tiles of W it owns (tile t, t + grid, ...); for the
+//    SwiGLU epilogue a tile is 8 gate rows and the 8 matching up rows.
+//  * A producer warp streams the tiles' rows in chunks of 512 columns (one cp.async.bulk of 1 KB a row and
+//    chunk) into a ring of stages in shared memory; each stage has a "full" mbarrier (armed with the byte
+//    count) and an "empty" mbarrier (the consumer warps arrive when they have read it).  The producer
+//    runs ahead of the consumers, also across tile boundaries, so the stream never drains inside a kernel.
+//  * The ring is about 52 KB a CTA, under half an SM's shared memory, and the kernel is launched with
+//    programmatic dependent launch: the next product's CTAs become resident while this one still runs and
+//    their producers fill their rings before griddepcontrol.wait (weights depend on no earlier kernel).  The
+//    stream therefore does not drain between kernels either.
+//  * Eight consumer warps take the k-blocks of 32 of a stage (block b to warp b % 8), read W fragments from
+//    shared memory (rows padded: 16-byte reads of 8 rows hit all banks) and activation fragments from
+//    global memory (L1 serves them), and issue mma.m16n8k16 with the batch rows on the m side.  At a tile's
+//    end their partial sums are added in warp order, so an output depends on its own activation row only.
 //
-// Every mbarrier wait is bounded; a wait that gives up sets a status word that
-// the host can read (kp_stream_status), and the CTA still waits (bounded) for
-// its remaining copies before it returns.
+// Fused in front (NORM, M <= 16): A = bf16((x * rsqrt(mean(x^2)+eps)) * w) of the float32 residual rows
+// (src/backend/cpu/scalar/quants.c:1489-1512).  Epilogues: bias; store bf16 / fp32; accumulate into fp32;
+// SwiGLU.  Every mbarrier wait is bounded; a wait that gives up sets a status word (kp_stream_status) and
+// the warp stops waiting for further stages.
 //
-// Limits: K a multiple of 256; the slab (8 or 16 rows of K bf16 plus padding)
-// must fit in 96 KB.  Other shapes take the register-streaming kernel.
+// Limits: K a multiple of 512.  Other shapes take the register-streaming kernel.
 #include "common.cuh"
 
 #define EPI_STORE 0
@@ -31,11 +32,11 @@
 #define EPI_ACCUM_F32 2
 #define EPI_SWIGLU 3
 
-#define ST_WARPS 4
-#define ST_THREADS (ST_WARPS * 32)
-#define ST_CHUNK 256                         // columns a chunk (one mbarrier each)
-#define ST_MAX_CHUNKS 32
-#define ST_MAX_SLAB (96 * 1024)
+#define ST_CONSUMERS 8                       // consumer warps
+#define ST_THREADS ((ST_CONSUMERS + 1) * 32) // plus the producer warp
+#define ST_COLS 512                          // columns of a stage: 16 k-blocks of 32, 2 a consumer warp
+#define ST_ROW_BYTES (ST_COLS * 2 + 64)      // a stage row in shared memory: 1 KB of data, pitch = 64 mod 128
+#define ST_RING_BYTES (53 * 1024)            // 6 stages of 8 rows or 3 stages of 2 x 8 rows
 #define ST_WAIT_NS 1000000000ull             // one second: far beyond any legitimate wait
 
 __device__ int g_stream_status = 0;          // 0 ok; 1: a bounded wait gave up
@@ -47,6 +48,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -74,6 +78,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory"); }
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -107,46 +112,68 @@ struct StreamArgs {
     const float* bias;
     void* C; int ldc;
     int M, N, K, ff;
-    int pitch;                           // bytes between rows of the slab in shared memory
+    int n_stages;                        // stages of the ring
 };
 
-// shared memory: [slab: NW*8 rows of `pitch` bytes][barriers: n_chunks x 8 B][red: ST_WARPS*NW*MT*128 floats][scales]
+// shared memory: [ring: n_stages x NW*8 rows x ST_ROW_BYTES][full[n_stages]][empty[n_stages]][red][scales]
 template <int MT, bool HALF, int EPI, bool NORM>
 __global__ void __launch_bounds__(ST_THREADS)
 gemm_stream_kernel(const StreamArgs p) {
     constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int ROWS = NW * 8;
+    constexpr int STAGE_BYTES = ROWS * ST_ROW_BYTES;
     extern __shared__ __align__(128) unsigned char smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int M = p.M, K = p.K, pitch = p.pitch;
-    const int n_chunks = K / ST_CHUNK;
-    unsigned char* slab = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)NW * 8 * pitch);
-    float* red = reinterpret_cast<float*>(bars + ST_MAX_CHUNKS);
-    float* scales = red + ST_WARPS * NW * MT * 128;
-    const int n0 = blockIdx.x * 8;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int M = p.M, K = p.K, S = p.n_stages;
+    unsigned char* ring = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * STAGE_BYTES);
+    uint64_t* empty = full + S;
+    float* red = reinterpret_cast<float*>(empty + S);                    // [ST_CONSUMERS][NW][MT][4][32]
+    float* scales = red + ST_CONSUMERS * NW * MT * 128;                  // [16]
     const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+    const int n_tiles = (n_out + 7) >> 3;
+    const int n_chunks = K / ST_COLS;
 
     if (threadIdx.x == 0) {
-        for (int c = 0; c < n_chunks; c++) mbar_init(&bars[c], 1);
+        for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], ST_CONSUMERS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 0) {
-        // the whole slab: chunk c of row r is one copy of 512 bytes; lanes share the copies out
-        if (lane == 0)
-            for (int c = 0; c < n_chunks; c++) mbar_expect_tx(&bars[c], NW * 8 * ST_CHUNK * 2);
-        __syncwarp();
-        const int n_copies = NW * 8 * n_chunks;
-        for (int i = lane; i < n_copies; i += 32) {
-            const int r = i % (NW * 8), c = i / (NW * 8);            // consecutive lanes: the rows of one chunk
-            const int wrow = (r < 8 ? 0 : p.ff) + min(n0 + (r & 7), n_out - 1);
-            bulk_g2s(slab + (size_t)r * pitch + (size_t)c * ST_CHUNK * 2,
-                     p.W + (size_t)wrow * p.ldw + (size_t)c * ST_CHUNK, ST_CHUNK * 2, &bars[c]);
+
+    if (warp == ST_CONSUMERS) {
+        // ---- producer: the weights depend on no earlier kernel, so it starts at once (no wait on the kernel before)
+        pdl_launch_dependents();
+        int it = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+            const int n0 = tile * 8;
+            const bf16* src = nullptr;
+            if (lane < ROWS) {
+                const int wrow = (lane < 8 ? 0 : p.ff) + min(n0 + (lane & 7), n_out - 1);
+                src = p.W + (size_t)wrow * p.ldw;
+            }
+            for (int c = 0; c < n_chunks; c++, it++) {
+                const int s = it % S;
+                int ok = 1;
+                if (lane == 0) {
+                    ok = mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1) ? 1 : 0;
+                    if (ok) mbar_expect_tx(&full[s], ROWS * ST_COLS * 2);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                if (lane < ROWS)
+                    bulk_g2s(ring + (size_t)s * STAGE_BYTES + (size_t)lane * ST_ROW_BYTES, src + (size_t)c * ST_COLS,
+                             ST_COLS * 2, &full[s]);
+            }
         }
+        if (!alive && lane == 0) atomicExch(&g_stream_status, 1);
+        return;
     }
+
+    // ---- consumers
+    const int g = lane >> 2, t = lane & 3;
     pdl_wait();                                               // from here on the activations may be read
     pdl_launch_dependents();
-
     int r0[MT], r1[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
@@ -155,7 +182,7 @@ gemm_stream_kernel(const StreamArgs p) {
         if (NORM && p.rows) { r0[mt] = p.rows[r0[mt]]; r1[mt] = p.rows[r1[mt]]; }
     }
     if (NORM) {
-        for (int row = warp; row < M; row += ST_WARPS) {
+        for (int row = warp; row < M; row += ST_CONSUMERS) {
             const int xr = p.rows ? p.rows[row] : row;
             const float4* xp = reinterpret_cast<const float4*>(p.X + (size_t)xr * p.ldx);
             float ss = 0.f;
@@ -166,18 +193,10 @@ gemm_stream_kernel(const StreamArgs p) {
             ss = warp_sum(ss);
             if (lane == 0) scales[row] = 1.0f / sqrtf(ss / (float)K + p.eps);
         }
-        __syncthreads();
+        consumer_sync();
     }
     float sc0 = 0.f, sc1 = 0.f;
     if (NORM) { sc0 = scales[min(g, M - 1)]; sc1 = scales[min(g + 8, M - 1)]; }
-
-    float acc[NW][MT][4];
-#pragma unroll
-    for (int w = 0; w < NW; w++)
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[w][mt][i] = 0.f;
 
     auto load_acts = [&](uint4 (&lo)[MT], uint4 (&hi)[MT], int kb) {
 #pragma unroll
@@ -194,77 +213,102 @@ gemm_stream_kernel(const StreamArgs p) {
         }
     };
 
-    // a chunk holds 8 k-blocks of 32: warp w takes blocks w and w + 4
-    const unsigned char* wrow_s[NW];
+    int it = 0;
+    bool alive = true;
+    const int nkb = K >> 5;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const int n0 = tile * 8;
+        float acc[NW][MT][4];
 #pragma unroll
-    for (int w = 0; w < NW; w++) wrow_s[w] = slab + (size_t)(w * 8 + g) * pitch + 16 * t;
-    bool timed_out = false;
-    uint4 lo[2][MT], hi[2][MT];
-    load_acts(lo[0], hi[0], warp);
-    load_acts(lo[1], hi[1], warp + ST_WARPS);
-    for (int c = 0; c < n_chunks; c++) {
-        if (!mbar_wait_bounded(&bars[c], 0)) timed_out = true;
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int kb = c * 8 + warp + j * ST_WARPS;
-            uint4 wv[NW];
-#pragma unroll
-            for (int w = 0; w < NW; w++) wv[w] = *reinterpret_cast<const uint4*>(wrow_s[w] + (size_t)kb * 64);
+        for (int w = 0; w < NW; w++)
 #pragma unroll
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-                for (int w = 0; w < NW; w++) {
-                    mma_bf16(acc[w][mt], lo[j][mt].x, hi[j][mt].x, lo[j][mt].y, hi[j][mt].y, wv[w].x, wv[w].y);
-                    mma_bf16(acc[w][mt], lo[j][mt].z, hi[j][mt].z, lo[j][mt].w, hi[j][mt].w, wv[w].z, wv[w].w);
-                }
-            if (c + 1 < n_chunks) load_acts(lo[j], hi[j], kb + 8);       // the same block of the next chunk
+                for (int i = 0; i < 4; i++) acc[w][mt][i] = 0.f;
+        // this warp's k-blocks: warp, warp + 8, ... ; activations fetched two blocks ahead
+        uint4 lo[2][MT], hi[2][MT];
+        load_acts(lo[0], hi[0], warp);
+        load_acts(lo[1], hi[1], warp + ST_CONSUMERS);
+        for (int c = 0; c < n_chunks; c++, it++) {
+            const int s = it % S;
+            if (alive && !mbar_wait_bounded(&full[s], (it / S) & 1)) alive = false;
+            const unsigned char* stage = ring + (size_t)s * STAGE_BYTES + 16 * t;
+#pragma unroll
+            for (int j = 0; j < 16 / ST_CONSUMERS; j++) {
+                const int kbs = warp + j * ST_CONSUMERS;                  // block inside the stage
+                const int kb = c * 16 + kbs;
+                uint4 wv[NW];
+#pragma unroll
+                for (int w = 0; w < NW; w++)
+                    wv[w] = *reinterpret_cast<const uint4*>(stage + (size_t)(w * 8 + g) * ST_ROW_BYTES + kbs * 64);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int w = 0; w < NW; w++) {
+                        mma_bf16(acc[w][mt], lo[j & 1][mt].x, hi[j & 1][mt].x, lo[j & 1][mt].y, hi[j & 1][mt].y, wv[w].x, wv[w].y);
+                        mma_bf16(acc[w][mt], lo[j & 1][mt].z, hi[j & 1][mt].z, lo[j & 1][mt].w, hi[j & 1][mt].w, wv[w].z, wv[w].w);
+                    }
+                if (kb + 2 * ST_CONSUMERS < nkb) load_acts(lo[j & 1], hi[j & 1], kb + 2 * ST_CONSUMERS);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);                       // this warp has read the stage
         }
-    }
-    if (timed_out) atomicExch(&g_stream_status, 1);
-
+        // the tile's result: the warps' partial sums, added in warp order
 #pragma unroll
-    for (int w = 0; w < NW; w++)
+        for (int w = 0; w < NW; w++)
 #pragma unroll
-        for (int mt = 0; mt < MT; mt++)
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) red[(((warp * NW + w) * MT + mt) * 4 + i) * 32 + lane] = acc[w][mt][i];
-    __syncthreads();
-    for (int e = threadIdx.x; e < MT * 4 * 32; e += ST_THREADS) {
-        const int l = e & 31, i = (e >> 5) & 3, mt = e >> 7;
-        const int m = mt * 16 + (l >> 2) + ((i & 2) ? 8 : 0);
-        const int n = n0 + (l & 3) * 2 + (i & 1);
-        if (m >= M || n >= n_out) continue;
-        float v = 0.f;
+                for (int i = 0; i < 4; i++) red[(((warp * NW + w) * MT + mt) * 4 + i) * 32 + lane] = acc[w][mt][i];
+        consumer_sync();
+        for (int e = threadIdx.x; e < MT * 4 * 32; e += ST_CONSUMERS * 32) {
+            const int l = e & 31, i = (e >> 5) & 3, mt = e >> 7;
+            const int m = mt * 16 + (l >> 2) + ((i & 2) ? 8 : 0);
+            const int n = n0 + (l & 3) * 2 + (i & 1);
+            if (m >= M || n >= n_out) continue;
+            float v = 0.f;
 #pragma unroll
-        for (int w4 = 0; w4 < ST_WARPS; w4++) v += red[(((w4 * NW + 0) * MT + mt) * 4 + i) * 32 + l];
-        if (p.bias) v += p.bias[n];
-        const size_t o = (size_t)m * p.ldc + n;
-        if (EPI == EPI_SWIGLU) {
-            float u = 0.f;
+            for (int w4 = 0; w4 < ST_CONSUMERS; w4++) v += red[(((w4 * NW + 0) * MT + mt) * 4 + i) * 32 + l];
+            if (p.bias) v += p.bias[n];
+            const size_t o = (size_t)m * p.ldc + n;
+            if (EPI == EPI_SWIGLU) {
+                float u = 0.f;
 #pragma unroll
-            for (int w4 = 0; w4 < ST_WARPS; w4++) u += red[(((w4 * NW + NW - 1) * MT + mt) * 4 + i) * 32 + l];
-            if (p.bias) u += p.bias[p.ff + n];
-            // gate and up are rounded to the storage type before the activation, as the unfused path stores them
-            const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
-            ((bf16*)p.C)[o] = from_f32<bf16>((gq / (1.0f + expf(-gq))) * uq);
-        } else if (EPI == EPI_STORE) {
-            ((bf16*)p.C)[o] = from_f32<bf16>(v);
-        } else if (EPI == EPI_STORE_F32) {
-            ((float*)p.C)[o] = v;
-        } else {
-            ((float*)p.C)[o] += v;
+                for (int w4 = 0; w4 < ST_CONSUMERS; w4++) u += red[(((w4 * NW + NW - 1) * MT + mt) * 4 + i) * 32 + l];
+                if (p.bias) u += p.bias[p.ff + n];
+                // gate and up are rounded to the storage type before the activation, as the unfused path stores them
+                const float gq = to_f32(from_f32<bf16>(v)), uq = to_f32(from_f32<bf16>(u));
+                ((bf16*)p.C)[o] = from_f32<bf16>((gq / (1.0f + expf(-gq))) * uq);
+            } else if (EPI == EPI_STORE) {
+                ((bf16*)p.C)[o] = from_f32<bf16>(v);
+            } else if (EPI == EPI_STORE_F32) {
+                ((float*)p.C)[o] = v;
+            } else {
+                ((float*)p.C)[o] += v;
+            }
         }
+        consumer_sync();                                                 // red is free for the next tile
     }
+    if (!alive && lane == 0) atomicExch(&g_stream_status, 1);
 }
 
-static int slab_pitch(int K) {
-    const int row = K * 2;
-    return (row % 128 == 0) ? row + 64 : row;          // pitch = 64 mod 128: 16-byte reads of 8 rows spread over all banks
+static size_t smem_bytes(int NW, int MT, int n_stages) {
+    return (size_t)n_stages * NW * 8 * ST_ROW_BYTES + (size_t)2 * n_stages * 8 +
+           sizeof(float) * (ST_CONSUMERS * NW * MT * 128 + 16);
 }
 
-static size_t smem_bytes(int NW, int MT, int pitch) {
-    return (size_t)NW * 8 * pitch + ST_MAX_CHUNKS * 8 + sizeof(float) * (ST_WARPS * NW * MT * 128 + 16);
+static int n_sm() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
 }
+
+static int g_ctas_per_sm = 3;                // persistent CTAs an SM (tunable for measurements)
+static int g_ring_bytes = ST_RING_BYTES;     // bytes of the ring (tunable for measurements)
 
 template <typename Kern>
 static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const StreamArgs& a) {
@@ -272,24 +316,20 @@ static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const S
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(ST_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, kern, a);
+    return (int)kp_launch_pdl(kern, grid, dim3(ST_THREADS), smem, s, a);
 }
 
 template <int MT, bool HALF, bool NORM>
-static int launch_epi(const StreamArgs& a, int epi, cudaStream_t s) {
+static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
+    const int NW = epi == EPI_SWIGLU ? 2 : 1;
     const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
-    dim3 grid((n_out + 7) / 8);
-    const size_t sm = smem_bytes(epi == EPI_SWIGLU ? 2 : 1, MT, a.pitch);
+    const int n_tiles = (n_out + 7) / 8;
+    a.n_stages = g_ring_bytes / (NW * 8 * ST_ROW_BYTES);
+    if (a.n_stages < 2) a.n_stages = 2;             // 6 stages, or 3 with the SwiGLU epilogue
+    int g = n_sm() * g_ctas_per_sm;
+    if (g > n_tiles) g = n_tiles;
+    dim3 grid(g);
+    const size_t sm = smem_bytes(NW, MT, a.n_stages);
     switch (epi) {
         case EPI_STORE: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE, NORM>, grid, sm, s, a);
         case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, NORM>, grid, sm, s, a);
@@ -310,27 +350,20 @@ static int launch_m(const StreamArgs& a, int epi, cudaStream_t s) {
 }
 
 static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void* W, int epi) {
-    if (M > 64 || K < ST_CHUNK || (K % ST_CHUNK) || K / ST_CHUNK > ST_MAX_CHUNKS || (ldw & 7) || ((uintptr_t)W & 15))
-        return KP_ERR_UNSUPPORTED;
+    if (M > 64 || K < ST_COLS || (K % ST_COLS) || (ldw & 7) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     a.ff = 0;
     if (epi == EPI_SWIGLU) {
         if (N & 1) return KP_ERR_BAD_ARG;
         a.ff = N / 2;
     }
-    a.pitch = slab_pitch(K);
-    if ((size_t)(epi == EPI_SWIGLU ? 2 : 1) * 8 * a.pitch > ST_MAX_SLAB) return KP_ERR_UNSUPPORTED;
     return 0;
 }
 
 extern "C" {
 
-// 1 if this product fits the kernel's limits (K a multiple of 256, slab within 96 KB), else 0
-int kp_gemm_stream_fits(int M, int N, int K, int epi) {
-    StreamArgs a = {};
-    static const int dummy_aligned = 0;
-    (void)dummy_aligned;
-    return check_common(a, M, N, K, 8, (const void*)16, epi) == 0;
-}
+// Persistent CTAs an SM (1..4), for measurements.
+void kp_gemm_stream_set_ctas_per_sm(int n) { g_ctas_per_sm = n < 1 ? 1 : (n > 8 ? 8 : n); }
+void kp_gemm_stream_set_ring_kb(int kb) { g_ring_bytes = (kb < 18 ? 18 : (kb > 96 ? 96 : kb)) * 1024; }
 
 int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                    int K, int epi, void* stream) {

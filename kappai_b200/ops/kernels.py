@@ -390,18 +390,17 @@ STREAM_MAX_SLAB = 96 * 1024
 
 
 def stream_fits(K: int, swiglu: bool) -> bool:
-    """Do 8 (16 with SwiGLU) rows of K bfloat16 fit the bulk-copy kernel's shared-memory slab?"""
-    if K < STREAM_CHUNK or K % STREAM_CHUNK or K // STREAM_CHUNK > 32:
-        return False
-    pitch = K * 2 + (64 if (K * 2) % 128 == 0 else 0)
-    return (16 if swiglu else 8) * pitch <= STREAM_MAX_SLAB
+    """The bulk-copy kernel streams W in chunks of 512 columns."""
+    return K >= 512 and K % 512 == 0
 
 
 def stream_pays(N: int, K: int) -> bool:
-    """Measured on B200: the bulk-copy kernel wins for short slabs and moderate grids (6144 x 2048: 6.4
-    against 8.1 us; 2048 x 2048: 3.5 against 4.4 us) and loses where a CTA's slab is long (K = 5632: two
-    CTAs an SM, 13.1 against 8.7 us) or the grid is huge (the 65536-row head: 66 against 48 us)."""
-    return K <= 2048 and N <= 16384
+    """Measured on B200 (8 rows, back to back in a graph): the bulk-copy kernel wins or ties for the layer
+    products (6144 x 2048: 6.4 against 8.1 us; gate/up 11264 x 2048: 12.3 against 16.0; 2048 x 5632: 9.1
+    against 8.9; 2048 x 2048: 3.8 against 4.4) and, because it fetches its whole slab before it waits for
+    the kernel before it, overlaps that kernel's tail inside a model step.  It loses on the huge grid of
+    the 65536-row head (65 against 48 us), which keeps the register-streaming kernel."""
+    return N <= 16384
 
 
 def stream_status() -> int:
