@@ -25,6 +25,8 @@
 // the warp stops waiting for further stages.
 //
 // Limits: K a multiple of 512.  Other shapes take the register-streaming kernel.
+#include <type_traits>
+
 #include "common.cuh"
 
 #define EPI_STORE 0
@@ -225,33 +227,44 @@ gemm_stream_kernel(const StreamArgs p) {
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[w][mt][i] = 0.f;
-        // this warp's k-blocks: warp, warp + 8, ... ; activations fetched two blocks ahead
-        uint4 lo[2][MT], hi[2][MT];
-        load_acts(lo[0], hi[0], warp);
-        load_acts(lo[1], hi[1], warp + ST_CONSUMERS);
-        for (int c = 0; c < n_chunks; c++, it++) {
+        // this warp's k-blocks: warp, warp + 8, ... (two a stage); their activations are fetched PF blocks
+        // (one stage) ahead.  Fetching two stages ahead was measured and gained nothing.
+        constexpr int PF = 2;
+        uint4 lo[PF][MT], hi[PF][MT];
+#pragma unroll
+        for (int i = 0; i < PF; i++)
+            if (warp + i * ST_CONSUMERS < nkb) load_acts(lo[i], hi[i], warp + i * ST_CONSUMERS);
+        auto run_stage = [&](int c, auto slot0) {
+            constexpr int SLOT0 = decltype(slot0)::value;
             const int s = it % S;
             if (alive && !mbar_wait_bounded(&full[s], (it / S) & 1)) alive = false;
             const unsigned char* stage = ring + (size_t)s * STAGE_BYTES + 16 * t;
 #pragma unroll
-            for (int j = 0; j < 16 / ST_CONSUMERS; j++) {
+            for (int j = 0; j < 2; j++) {
+                constexpr int dummy = 0; (void)dummy;
                 const int kbs = warp + j * ST_CONSUMERS;                  // block inside the stage
                 const int kb = c * 16 + kbs;
                 uint4 wv[NW];
 #pragma unroll
                 for (int w = 0; w < NW; w++)
                     wv[w] = *reinterpret_cast<const uint4*>(stage + (size_t)(w * 8 + g) * ST_ROW_BYTES + kbs * 64);
+                const int sl = SLOT0 + j;
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
-                        mma_bf16(acc[w][mt], lo[j & 1][mt].x, hi[j & 1][mt].x, lo[j & 1][mt].y, hi[j & 1][mt].y, wv[w].x, wv[w].y);
-                        mma_bf16(acc[w][mt], lo[j & 1][mt].z, hi[j & 1][mt].z, lo[j & 1][mt].w, hi[j & 1][mt].w, wv[w].z, wv[w].w);
+                        mma_bf16(acc[w][mt], lo[sl][mt].x, hi[sl][mt].x, lo[sl][mt].y, hi[sl][mt].y, wv[w].x, wv[w].y);
+                        mma_bf16(acc[w][mt], lo[sl][mt].z, hi[sl][mt].z, lo[sl][mt].w, hi[sl][mt].w, wv[w].z, wv[w].w);
                     }
-                if (kb + 2 * ST_CONSUMERS < nkb) load_acts(lo[j & 1], hi[j & 1], kb + 2 * ST_CONSUMERS);
+                if (kb + PF * ST_CONSUMERS < nkb) load_acts(lo[sl], hi[sl], kb + PF * ST_CONSUMERS);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);                       // this warp has read the stage
+            it++;
+        };
+        for (int c = 0; c < n_chunks; c += PF / 2) {
+            run_stage(c, std::integral_constant<int, 0>{});
+            if (PF == 4 && c + 1 < n_chunks) run_stage(c + 1, std::integral_constant<int, (PF == 4 ? 2 : 0)>{});
         }
         // the tile's result: the warps' partial sums, added in warp order
 #pragma unroll

@@ -384,6 +384,7 @@ def tc_status() -> int:
     return int(load_library("gemm_tc").kp_tc_status())
 
 
+STREAM_MAX_M = 64          # rows up to which the bulk-copy kernel is preferred
 USE_STREAM = True         # few-row products go to the bulk-copy kernel where their shape fits it
 STREAM_CHUNK = 256
 STREAM_MAX_SLAB = 96 * 1024
@@ -494,7 +495,7 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
         epi = EPI_STORE_F32
     else:
         raise KernelError("gemm_skinny: output dtype")
-    if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K):
+    if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K) and M <= STREAM_MAX_M:
         lib = load_library("gemm_stream")
         _check(lib.kp_gemm_stream(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
                                   _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_stream")
