@@ -273,6 +273,31 @@ def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
     return n / dt, h2d, d2h
 
 
+def run_probe(model_dir, a, rng) -> int:
+    """A few eager steps for a profiler: every kernel is a launch of its own (no graph), sizes as in the bench."""
+    import torch
+    from kappai_b200 import ModelRunner, StepEntry
+    from kappai_b200.sampling.sampler import argmax
+
+    B, T = a.batch, a.prompt_len
+    runner = ModelRunner(model_dir, dtype="bfloat16", max_tokens=B * CONTEXT, max_requests=B, page_size=64,
+                         max_model_len=CONTEXT, cuda_graphs=False)
+    V = runner.vocab_size
+    if a.probe == "prefill":
+        for i in range(a.steps):
+            runner.step([StepEntry("p", rng.integers(0, V, T).tolist(), [T - 1])])
+            runner.end("p")
+    else:
+        for i in range(B):
+            runner.step([StepEntry(i, rng.integers(0, V, T).tolist(), [])])
+        entries = [StepEntry(i, [1], [0]) for i in range(B)]
+        for _ in range(a.steps):
+            argmax(runner.step(entries))
+    torch.cuda.synchronize()
+    print(f"probe {a.probe} ok: batch {B}, prompt {T}, {a.steps} steps, {runner.config.num_hidden_layers} layers")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -281,6 +306,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
+                    help="run a few eager steps (no CUDA graph) of one kind and exit: the small case that a "
+                         "profiler is pointed at")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -302,6 +331,8 @@ def main() -> int:
     n_layers = a.layers or LFM2_1P2B["num_hidden_layers"]
     model_dir, cfg = model_folder(LFM2_1P2B, SEED, n_layers)
     rng = np.random.default_rng(SEED)
+    if a.probe:
+        return run_probe(model_dir, a, rng)
     runner = ModelRunner(model_dir, dtype="bfloat16", max_tokens=64 * CONTEXT, max_requests=64, page_size=64,
                          max_model_len=CONTEXT)
     wbytes = weight_bytes(runner)
