@@ -46,6 +46,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
@@ -133,7 +136,6 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const TcArgs p) {
-    kp_pdl_begin();
     constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     constexpr int N_OUT_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;       // output columns of the tile
     extern __shared__ unsigned char smem[];
@@ -141,68 +143,92 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * (A_BYTES + B_BYTES));
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;                                  // [2]: accumulator b holds a finished tile
+    uint64_t* acc_empty = acc_full + 2;                                   // [2]: accumulator b has been read out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * N_OUT_TILE;
     const int n_kb = (p.K + TC_BK - 1) / TC_BK;
+    const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+    const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (n_out + N_OUT_TILE - 1) / N_OUT_TILE;
+    const int n_tiles = tiles_m * tiles_n;
+    // the CTA is persistent: it takes tiles blockIdx.x, blockIdx.x + gridDim.x, ... ; consecutive tiles
+    // share the W tile (m runs fastest), so the CTAs that run together read the same few W tiles from L2
 
+    // set-up that depends on no earlier kernel comes before the wait on it
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b2 = 0; b2 < 2; b2++) { mbar_init(&acc_full[b2], 1); mbar_init(&acc_empty[b2], 4); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, BN);
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);                         // two accumulators of BN columns
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    kp_pdl_begin();
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < n_kb; kb++) {
-                const int s = kb % STAGES;
-                if (!mbar_wait_bounded(&empty[s], ((kb / STAGES) & 1) ^ 1)) { *abort_flag = 1; break; }
-                unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
-                unsigned char* b_dst = a_dst + A_BYTES;
-                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
-                if (EPI == EPI_SWIGLU) {
-                    tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
-                    tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
-                } else {
-                    tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
+                for (int kb = 0; kb < n_kb; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (*abort_flag || !mbar_wait_bounded(&empty[s], ((it / STAGES) & 1) ^ 1)) { *abort_flag = 1; ok = false; break; }
+                    unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
+                    unsigned char* b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
+                    if (EPI == EPI_SWIGLU) {
+                        tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
+                        tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
+                    } else {
+                        tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            int it = 0, ti = 0;
             bool ok = true;
-            for (int kb = 0; kb < n_kb && ok; kb++) {
-                const int s = kb % STAGES;
-                if (!mbar_wait_bounded(&full[s], (kb / STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
+                const int b2 = ti & 1;                                    // accumulator of this tile
+                if (*abort_flag || !mbar_wait_bounded(&acc_empty[b2], ((ti >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
-                const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + A_BYTES);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(b2 * BN);
+                for (int kb = 0; kb < n_kb; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_bounded(&full[s], (it / STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
+                    const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + A_BYTES);
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++)          // 32 bytes along K inside the swizzled row: +2 in the address field
-                    umma_bf16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                umma_commit(&empty[s]);                        // the stage is free when these MMAs have read it
+                    for (int k = 0; k < TC_BK / 16; k++)      // 32 bytes along K inside the swizzled row: +2 in the address field
+                        umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&empty[s]);                    // the stage is free when these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[b2]);            // arrives when every MMA of the tile has completed
             }
-            umma_commit(acc_ready);                            // arrives when every MMA above has completed
         }
     } else {
-        // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory = rows m0 + that
+        // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory; it works on tile i while the
+        // MMA warp already fills the other accumulator with tile i + 1
         const int q = warp & 3;
-        const bool ready = mbar_wait_bounded(acc_ready, 0);
-        tc_fence_after();
-        if (ready && !*abort_flag) {
+        int ti = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
+            const int b2 = ti & 1;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
+            if (!mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
+            tc_fence_after();
             const int m = m0 + q * 32 + lane;
-            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+            const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int c = 0; c < N_OUT_TILE; c += 32) {
                 uint32_t r[32];
@@ -211,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (EPI == EPI_SWIGLU) tmem_ld32(lane_base + BN / 2 + c, u);
                 if (m < p.M) {
                     const int n_base = n0 + c;
-                    const int n_lim = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+                    const int n_lim = n_out;
                     // the 32 values of this thread's row, finished
                     float v[32];
 #pragma unroll
@@ -268,13 +294,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                 }
             }
-        } else if (lane == 0) {
-            atomicExch(&g_tc_status, 1);
+            // this warp has read the accumulator out: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b2]);
         }
+        if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, BN);
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------------------------------ host side
@@ -310,7 +339,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 
 template <int BN, int STAGES, int EPI>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const TcArgs& a, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
     auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -320,7 +349,14 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const TcArgs& a,
     }
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-    dim3 grid((n_out + n_tile - 1) / n_tile, (a.M + TC_BM - 1) / TC_BM);
+    const int n_tiles = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    dim3 grid(n_tiles < sms ? n_tiles : sms);                  // persistent: one CTA an SM
     kp_launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, s, ta, tw, a);
     return kp_launch_status();
 }
@@ -344,8 +380,13 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
         a.ff = N / 2;
     }
     const int n_out = epi == EPI_SWIGLU ? a.ff : N;
-    // the wide tile where it still fills the GPU, else the narrow one
-    const bool wide = epi != EPI_SWIGLU && ((long long)((n_out + 255) / 256) * ((M + TC_BM - 1) / TC_BM) >= 148);
+    // Tile width by a small cost model: a CTA's main loop is bound by the bytes that it brings into shared
+    // memory for each k-block (128 rows of A and BN rows of W), so a narrow tile costs about 2/3 of a wide one
+    // and does half the work; the number of rounds over the SMs decides between them.
+    const long long m_tiles = (M + TC_BM - 1) / TC_BM;
+    const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + 147) / 148;
+    const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + 147) / 148;
+    const bool wide = epi != EPI_SWIGLU && rounds_wide * 3 <= rounds_narrow * 2;
     alignas(64) CUtensorMap ta, tw;
     int st = make_map(&ta, A, M, K, lda, TC_BM);
     if (st) return st;

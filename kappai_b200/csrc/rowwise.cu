@@ -34,6 +34,18 @@ __global__ void rmsnorm_rows_kernel(const float* __restrict__ x, const float* __
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f32<T>((src[i] * scale) * w[i]);
 }
 
+// four consecutive outputs in one store (the destination is 8- or 16-byte aligned: d % 4 == 0)
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = o;
+}
+
 // The same for rows of at most 8192 floats that are 16-byte aligned: each thread keeps its 8 float4 of the
 // row in registers, so the row is read once.
 template <typename T>
@@ -66,10 +78,8 @@ rmsnorm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ w
         const int i = threadIdx.x + j * 256;
         if (i < n4) {
             const float4 ww = __ldg(w4 + i);
-            dst[4 * i + 0] = from_f32<T>((v[j].x * scale) * ww.x);
-            dst[4 * i + 1] = from_f32<T>((v[j].y * scale) * ww.y);
-            dst[4 * i + 2] = from_f32<T>((v[j].z * scale) * ww.z);
-            dst[4 * i + 3] = from_f32<T>((v[j].w * scale) * ww.w);
+            store4(dst + 4 * i, (v[j].x * scale) * ww.x, (v[j].y * scale) * ww.y, (v[j].z * scale) * ww.z,
+                   (v[j].w * scale) * ww.w);
         }
     }
 }
@@ -113,7 +123,7 @@ int kp_embed_rows(const void* table, const int* ids, float* x, int n, int d, flo
 int kp_rmsnorm_rows(const float* x, const float* w, void* y, const int* rows, int n, int d, float eps, int dtype,
                     void* stream) {
     if (n <= 0) return 0;
-    if ((d & 3) == 0 && d <= 8192 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    if ((d & 3) == 0 && d <= 8192 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
         // which kernel runs depends on the row's size and alignment only, never on the batch
         KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
         return kp_launch_status();
