@@ -48,6 +48,8 @@ class PagePool:
         self._free: List[int] = list(range(n_pages - 1, -1, -1))      # stack: lowest page first
         self._tables: Dict[Hashable, List[int]] = {}
         self._held: Dict[Hashable, int] = {}                          # pages currently held per request
+        self._version: Dict[Hashable, int] = {}                       # stamp of the last change of a request's table
+        self._tick = 0                                                # source of the stamps: never repeats
 
     # -- queries
     @property
@@ -57,26 +59,40 @@ class PagePool:
     def table(self, req: Hashable) -> List[int]:
         return self._tables[req]
 
+    def version(self, req: Hashable) -> int:
+        """A stamp that changes whenever the request's block table does (a page added or
+        released) and is never used twice in this pool, not even by a later request of
+        the same name: a copy of the table elsewhere knows by it when it is stale."""
+        return self._version[req]
+
     def pages_needed(self, req: Hashable, new_len: int) -> int:
         have = len(self._tables.get(req, ()))
         return max(0, _ceil_div(new_len, self.page_size) - have)
 
     # -- changes
+    def _stamp(self) -> int:
+        self._tick += 1
+        return self._tick
+
     def open(self, req: Hashable) -> None:
         if req in self._tables:
             raise CacheError(f"request {req!r} already has a block table")
         self._tables[req] = []
         self._held[req] = 0
+        self._version[req] = self._stamp()
 
     def extend(self, req: Hashable, new_len: int) -> None:
         """Make the table cover tokens [0, new_len)."""
         need = self.pages_needed(req, new_len)
         if need > len(self._free):
             raise OutOfPages(f"need {need} pages, {len(self._free)} free")
+        if need == 0:
+            return
         t = self._tables[req]
         for _ in range(need):
             t.append(self._free.pop())
         self._held[req] += need
+        self._version[req] = self._stamp()
 
     def release_behind(self, req: Hashable, next_pos: int) -> int:
         """Windowed groups: give back pages whose every key lies before the
@@ -94,7 +110,9 @@ class PagePool:
                 self._free.append(t[b])
                 t[b] = RELEASED
                 n += 1
-        self._held[req] -= n
+        if n:
+            self._held[req] -= n
+            self._version[req] = self._stamp()
         return n
 
     def close(self, req: Hashable) -> None:
@@ -105,6 +123,7 @@ class PagePool:
             if p != RELEASED:
                 self._free.append(p)
         del self._held[req]
+        del self._version[req]
 
     def check(self) -> None:
         """Every page is either free or held by exactly one block table."""
@@ -205,10 +224,20 @@ class CacheManager:
         """Pages for tokens [0, new_len) in every group, or none at all."""
         if req not in self.requests:
             raise CacheError(f"request {req!r} is not live")
-        if not self.can_extend(req, new_len):
+        if not self.try_extend(req, new_len):
             raise OutOfPages(f"request {req!r}: no pages for {new_len} tokens")
-        for p in self.pools.values():
+
+    def try_extend(self, req: Hashable, new_len: int) -> bool:
+        """:meth:`extend` that answers False (and takes nothing) where it would raise OutOfPages."""
+        pools = self.pools.values()
+        needs = [p.pages_needed(req, new_len) for p in pools]
+        if not any(needs):
+            return True
+        if any(n > p.n_free for n, p in zip(needs, pools)):
+            return False
+        for p in pools:
             p.extend(req, new_len)
+        return True
 
     def advance(self, req: Hashable, new_len: int) -> None:
         """The request now holds ``new_len`` tokens; release what windows have passed."""

@@ -97,14 +97,16 @@ class Engine:
             return []
         entries = []
         for e in plan:
-            toks = e.request.tokens[e.start:e.start + e.n]
+            toks = e.request.token_slice(e.start, e.n)
             entries.append(StepEntry(e.request.id, toks, [e.n - 1] if e.sample else []))
         logits = self.runner.step(entries)
         sampled: Dict[Hashable, int] = {}
         got = [e.request for e in plan if e.sample]
         if got:
+            # the token history only where a repeat penalty reads it
+            recent = [r.tokens for r in got] if any(r.params.repeat_penalty != 1.0 for r in got) else None
             toks = sample(logits, [r.params for r in got], [r.seed for r in got], [len(r.output) for r in got],
-                          [r.tokens for r in got])
+                          recent)
             for r, t in zip(got, toks.tolist()):                    # the step's one device-to-host read
                 sampled[r.id] = t
         else:

@@ -46,13 +46,21 @@ class _DecodeGraph:
         self.size = off
         self.dev = torch.zeros(off, dtype=torch.int32, device=dev)
         self.pinned = [torch.zeros(off, dtype=torch.int32, pin_memory=True) for _ in range(N_PINNED)]
+        self.pinned_np = [p.numpy() for p in self.pinned]
         self.events = [None] * N_PINNED
         self.turn = 0
-        for p in self.pinned:                       # the pieces that never change
-            a = p.numpy()
-            a[self.off["row_seg"]:self.off["row_seg"] + n] = np.arange(n)
-            a[self.off["cu_rows"]:self.off["cu_rows"] + n + 1] = np.arange(n + 1)
-            a[self.off["logit_rows"]:self.off["logit_rows"] + n] = np.arange(n)
+        # The tables are kept in one host array and changed in place from step to step (a block-table row is
+        # rewritten only when its request or the request's table has changed); each step copies the array
+        # to the next staging buffer.
+        self.host = np.zeros(off, dtype=np.int32)
+        a = self.host                               # the pieces that never change
+        a[self.off["row_seg"]:self.off["row_seg"] + n] = np.arange(n)
+        a[self.off["cu_rows"]:self.off["cu_rows"] + n + 1] = np.arange(n + 1)
+        a[self.off["logit_rows"]:self.off["logit_rows"] + n] = np.arange(n)
+        self.host_bt = {gk: a[self.off[("block_table", gk)]:self.off[("block_table", gk)] + n * width].reshape(n, width)
+                        for gk, _ in groups}
+        self.host_sm = {gk: a[self.off[("slot_map", gk)]:self.off[("slot_map", gk)] + n] for gk, _ in groups}
+        self.row_key = {gk: [None] * n for gk, _ in groups}     # (request, table version) a row was written for
         piece = lambda name, m: self.dev[self.off[name]:self.off[name] + m]
         paged = {gk: PagedView(piece(("block_table", gk), n * width).view(n, width), piece(("slot_map", gk), n), ps)
                  for gk, ps in groups}
@@ -74,22 +82,28 @@ class _DecodeGraph:
         self.turn = (i + 1) % N_PINNED
         if self.events[i] is not None:
             self.events[i].synchronize()
-        a = self.pinned[i].numpy()
+        a = self.host
         n, o = self.n, self.off
         cache = runner.cache
-        lens = [cache.requests[r].length for r in reqs]
+        rcs = [cache.requests[r] for r in reqs]
+        lens = [rc.length for rc in rcs]
         if tokens is not None:
             a[o["token_ids"]:o["token_ids"] + n] = tokens
         a[o["positions"]:o["positions"] + n] = lens
         a[o["seg_pos"]:o["seg_pos"] + n] = lens
-        a[o["seg_slot"]:o["seg_slot"] + n] = [cache.requests[r].slot for r in reqs]
+        a[o["seg_slot"]:o["seg_slot"] + n] = [rc.slot for rc in rcs]
         for gk, ps in runner.group_page_size.items():
-            bt = a[o[("block_table", gk)]:o[("block_table", gk)] + n * self.width].reshape(n, self.width)
-            sm = a[o[("slot_map", gk)]:o[("slot_map", gk)] + n]
+            pool = cache.pools[gk]
+            bt, sm, keys = self.host_bt[gk], self.host_sm[gk], self.row_key[gk]
             for j, r in enumerate(reqs):
-                t = cache.block_table(r, gk)
-                bt[j, :len(t)] = t
+                t = pool.table(r)
+                key = (r, pool.version(r))
+                if keys[j] != key:
+                    bt[j, :len(t)] = t
+                    bt[j, len(t):] = 0
+                    keys[j] = key
                 sm[j] = t[lens[j] // ps] * ps + lens[j] % ps
+        np.copyto(self.pinned_np[i], a)
         self.dev.copy_(self.pinned[i], non_blocking=True)
         ev = self.events[i] or torch.cuda.Event()
         ev.record()

@@ -60,6 +60,15 @@ class Request:
     def n_tokens(self) -> int:
         return len(self.prompt) + len(self.output)
 
+    def token_slice(self, start: int, n: int) -> List[int]:
+        """``tokens[start:start + n]`` without joining the two lists."""
+        lp = len(self.prompt)
+        if start >= lp:
+            return self.output[start - lp:start - lp + n]
+        if start + n <= lp:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - lp]
+
 
 @dataclass
 class ScheduledEntry:
@@ -120,7 +129,7 @@ class Scheduler:
             if r.state != RUNNING or budget == 0:
                 continue
             n = min(r.n_tokens - r.n_computed, budget)
-            while not self.cache.can_extend(r.id, r.n_computed + n):
+            while not self.cache.try_extend(r.id, r.n_computed + n):
                 victim = self._victim(exclude=[e.request for e in entries])
                 if victim is None or victim is r:
                     if len(self.running) == 1:
@@ -134,7 +143,6 @@ class Scheduler:
                 preempted = True
             if r.state != RUNNING:
                 continue
-            self.cache.extend(r.id, r.n_computed + n)
             entries.append(ScheduledEntry(r, r.n_computed, n, r.n_computed + n == r.n_tokens))
             budget -= n
         # admission (not in a step that had to preempt: the freed pages are for those who run)
