@@ -217,12 +217,12 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
-                                  int window, int H, int hd) {
+                                  int chunk_keys, int window, int H, int hd) {
     kp_pdl_begin();
     const int h = blockIdx.x, row = blockIdx.y;
     int k_lo, k_hi;
     key_range(positions[row], window, k_lo, k_hi);
-    const int c_lo = k_lo / AD_CHUNK, c_hi = k_hi / AD_CHUNK;
+    const int c_lo = k_lo / chunk_keys, c_hi = k_hi / chunk_keys;
     const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
     float m = -INFINITY;
     for (int c = c_lo; c <= c_hi; c++) m = fmaxf(m, ml[2 * c]);
@@ -275,24 +275,25 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
         else if (hd == 64) AD_LAUNCH(T, 64, 0);
         else if (hd == 128) AD_LAUNCH(T, 128, 0);
         else AD_LAUNCH(T, 0, 0);
-        kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window,
-                                                        H, hd);
+        kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_chunks,
+                                                        AD_CHUNK, window, H, hd);
     });
 #undef AD_LAUNCH
     return kp_launch_status();
 }
 
-// The merge alone, for chunk partials that another kernel wrote into `scratch` in the same format.
-int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int window,
-                       int n, int H, int hd, int dtype, void* stream) {
+// The merge alone, for partials of chunks of `chunk_keys` keys that another kernel wrote into `scratch` in the
+// same format.
+int kp_attention_merge(const int* positions, void* out, int ldo, const float* scratch, int n_chunks, int chunk_keys,
+                       int window, int n, int H, int hd, int dtype, void* stream) {
     if (n <= 0) return 0;
-    if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535) return KP_ERR_UNSUPPORTED;
+    if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535 || chunk_keys < 1) return KP_ERR_UNSUPPORTED;
     const float* part_acc = scratch;
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     dim3 mgrid(H, n);
     const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
     KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, (cudaStream_t)stream, 
-        part_acc, part_ml, positions, (T*)out, ldo, n_chunks, window, H, hd)));
+        part_acc, part_ml, positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd)));
     return kp_launch_status();
 }
 

@@ -19,7 +19,7 @@
 // start at multiples of 64 of the absolute key index, chunks at multiples of
 // 256, so the order of summation does not depend on how a prompt was cut or
 // what else is in the batch.
-#include "common.cuh"
+#include "tma.cuh"
 
 #define AM_TILE 64
 #define AM_CHUNK 256
@@ -55,10 +55,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// A tile in shared memory: 64 rows (keys) of HD bf16; the 16-byte chunk c of row r lies at chunk c ^ (r & 7).
+// A tile in shared memory: 64 rows (keys) of HD bf16, as HD / 64 halves of 64 rows x 128 bytes; in a half the
+// 16-byte chunk c of row r lies at chunk c ^ (r & 7).  This is what a TMA box of 64 columns with the 128-byte
+// swizzle writes (tile on a 1024-byte boundary), so both ways of loading a tile give the same layout.
 template <int HD>
 __device__ __forceinline__ bf16* tile_chunk(bf16* tile, int r, int c) {
-    return tile + (size_t)r * HD + ((c ^ (r & 7)) << 3);
+    return tile + (size_t)(c >> 3) * (AM_TILE * 64) + (size_t)r * 64 + (((c & 7) ^ (r & 7)) << 3);
 }
 
 // Bring keys [k0, k0+64) of one kv head into a K tile and a V tile.  Keys outside [k_lo, k_hi] are zero-filled.
@@ -115,36 +117,74 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&
 }
 
 // ------------------------------------------------------------------ decode (split over chunks)
-template <int HD>
-__global__ void __launch_bounds__(128)
-attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
+// NW warps a CTA, one tile of 64 keys each: a chunk is NW * 64 keys.  Small chunks (NW = 1) give many short CTAs,
+// which fill the SMs evenly and keep many loads in flight; the merge then has more partial results to add.
+//
+// TMA = true: the tiles come by tiled TMA loads from the cache seen as one 2-D tensor (rows = page, K|V, kv
+// head, key of the page; HD columns), one box of min(page size, 64) keys x 64 columns each, issued by one
+// thread: no address arithmetic in the other threads.  Needs a page size that divides 64 or is a multiple of
+// it, and a multiple of 8.  Boxes wholly outside the row's keys are not loaded; V rows outside them are zeroed.
+__device__ int g_attn_status = 0;                // 1: a bounded wait gave up
+
+template <int HD, int NW, bool TMA>
+__global__ void __launch_bounds__(NW * 32)
+attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
                       int n_chunks, float scale, int window, int page_size, int H, int G) {
     kp_pdl_begin();
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [4][64][HD]
-    bf16* Vs = Ks + 4 * AM_TILE * HD;                             // [4][64][HD]
-    float* wO = reinterpret_cast<float*>(Vs + 4 * AM_TILE * HD);  // [4][AM_RMAX][HD]
-    float* wm = wO + 4 * AM_RMAX * HD;                            // [4][AM_RMAX]
-    float* wl = wm + 4 * AM_RMAX;                                 // [4][AM_RMAX]
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [NW][64][HD]
+    bf16* Vs = Ks + NW * AM_TILE * HD;                            // [NW][64][HD]
+    float* wO = reinterpret_cast<float*>(Vs + NW * AM_TILE * HD); // [NW][AM_RMAX][HD]
+    float* wm = wO + NW * AM_RMAX * HD;                           // [NW][AM_RMAX]
+    float* wl = wm + NW * AM_RMAX;                                // [NW][AM_RMAX]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(wl + NW * AM_RMAX);
+    constexpr int CHUNK = NW * AM_TILE;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, kvh = blockIdx.y, row = blockIdx.z;
     const int R = H / G;
     const int pos = positions[row];
     const int k_lo = window > 0 ? max(0, pos - window + 1) : 0, k_hi = pos;
-    const int c0 = chunk * AM_CHUNK;
-    if (c0 > k_hi || c0 + AM_CHUNK - 1 < k_lo) return;
+    const int c0 = chunk * CHUNK;
+    if (c0 > k_hi || c0 + CHUNK - 1 < k_lo) return;
     const int* bt = block_table + (size_t)row_seg[row] * max_blocks;
     const size_t page_stride = (size_t)2 * G * page_size * HD;
     const size_t k_off = (size_t)kvh * page_size * HD, v_off = ((size_t)G + kvh) * page_size * HD;
 
+    if (TMA) {
+        if (tid == 0) {
+            kp_mbar_init(bar, 1);
+            kp_mbar_init_fence();
+            const int box = min(page_size, AM_TILE);               // keys a box
+            uint32_t bytes = 0;
+            for (int key0 = c0; key0 < c0 + CHUNK; key0 += box)
+                if (key0 <= k_hi && key0 + box - 1 >= k_lo) bytes += 2 * box * HD * 2;
+            kp_mbar_expect_tx(bar, bytes);
+            for (int key0 = c0; key0 < c0 + CHUNK; key0 += box) {
+                if (!(key0 <= k_hi && key0 + box - 1 >= k_lo)) continue;
+                const int page = bt[key0 / page_size];
+                const int row_k = ((page * 2) * G + kvh) * page_size + key0 % page_size;   // row of the 2-D view
+                const int row_v = row_k + G * page_size;
+                const int in_chunk = key0 - c0;
+                bf16* kd = Ks + (size_t)(in_chunk / AM_TILE) * AM_TILE * HD + (size_t)(in_chunk % AM_TILE) * 64;
+                bf16* vd = Vs + (size_t)(in_chunk / AM_TILE) * AM_TILE * HD + (size_t)(in_chunk % AM_TILE) * 64;
 #pragma unroll
-    for (int w = 0; w < 4; w++)
-        load_kv_tile<HD>(Ks + w * AM_TILE * HD, Vs + w * AM_TILE * HD, cache, bt, page_stride, k_off, v_off, page_size,
-                         c0 + w * AM_TILE, k_lo, k_hi, tid, 128);
-    cp_async_commit();
+                for (int half = 0; half < HD / 64; half++) {
+                    kp_tma_load_2d(kd + half * (AM_TILE * 64), &tmC, half * 64, row_k, bar);
+                    kp_tma_load_2d(vd + half * (AM_TILE * 64), &tmC, half * 64, row_v, bar);
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int w = 0; w < NW; w++)
+            load_kv_tile<HD>(Ks + w * AM_TILE * HD, Vs + w * AM_TILE * HD, cache, bt, page_stride, k_off, v_off, page_size,
+                             c0 + w * AM_TILE, k_lo, k_hi, tid, NW * 32);
+        cp_async_commit();
+    }
 
     // Q of the R heads of this kv head as rows 0..R-1 of the m16 tile (rows 8..15 do not exist: R <= 8)
     uint32_t qf[HD / 16][4];
@@ -158,12 +198,28 @@ attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restric
             qf[ks][0] = lo; qf[ks][1] = 0; qf[ks][2] = hi; qf[ks][3] = 0;
         }
     }
-    cp_async_wait<0>();
-    __syncthreads();
-
     bf16* Kt = Ks + warp * AM_TILE * HD;
     bf16* Vt = Vs + warp * AM_TILE * HD;
     const int t0 = c0 + warp * AM_TILE;                           // first key of this warp's tile
+    if (TMA) {
+        __syncthreads();                                          // the barrier is initialised
+        if (!kp_mbar_wait_bounded(bar, 0)) {
+            if (lane == 0) atomicExch(&g_attn_status, 1);
+            return;                                                // (every thread sees the same barrier)
+        }
+        // V rows of keys that this row does not read hold whatever was there: zero them (P is 0 there, but
+        // 0 * NaN is not); K rows need nothing, their scores are masked
+        if (t0 < k_lo || t0 + AM_TILE - 1 > k_hi) {
+            for (int idx = lane; idx < AM_TILE * (HD / 8); idx += 32) {
+                const int r = idx / (HD / 8), c = idx % (HD / 8);
+                if (t0 + r < k_lo || t0 + r > k_hi) *reinterpret_cast<uint4*>(tile_chunk<HD>(Vt, r, c)) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+    } else {
+        cp_async_wait<0>();
+        __syncthreads();
+    }
     float s[8][4];
     qk_tile<HD>(s, qf, Kt, lane);
     // row g of the tile: columns 2t, 2t+1 of each n-tile are keys t0 + nt*8 + 2t (+1)
@@ -209,15 +265,15 @@ attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restric
         if (t == 0) { wm[warp * AM_RMAX + g] = m; wl[warp * AM_RMAX + g] = l; }
     }
     __syncthreads();
-    // the four warps' partial results, combined in warp order
-    for (int e = tid; e < R * HD; e += 128) {
+    // the warps' partial results, combined in warp order
+    for (int e = tid; e < R * HD; e += NW * 32) {
         const int r = e / HD, d = e % HD;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; w++) M = fmaxf(M, wm[w * AM_RMAX + r]);
+        for (int w = 0; w < NW; w++) M = fmaxf(M, wm[w * AM_RMAX + r]);
         float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; w++) {
+        for (int w = 0; w < NW; w++) {
             const float mw = wm[w * AM_RMAX + r];
             if (mw != -INFINITY) acc = fmaf(wO[((size_t)w * AM_RMAX + r) * HD + d], expf(mw - M), acc);
         }
@@ -225,8 +281,8 @@ attn_split_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restric
     }
     if (tid < R) {
         float M = -INFINITY, L = 0.f;
-        for (int w = 0; w < 4; w++) M = fmaxf(M, wm[w * AM_RMAX + tid]);
-        for (int w = 0; w < 4; w++) {
+        for (int w = 0; w < NW; w++) M = fmaxf(M, wm[w * AM_RMAX + tid]);
+        for (int w = 0; w < NW; w++) {
             const float mw = wm[w * AM_RMAX + tid];
             if (mw != -INFINITY) L = fmaf(wl[w * AM_RMAX + tid], expf(mw - M), L);
         }
@@ -367,14 +423,23 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
     }
 }
 
-template <int HD>
-static int launch_split(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                        const int* row_seg, const int* positions, float* part_acc, float* part_ml, int n_chunks,
-                        float scale, int window, int page_size, int n, int H, int G, cudaStream_t s) {
-    const size_t smem = (size_t)8 * AM_TILE * HD * 2 + sizeof(float) * (4 * AM_RMAX * HD + 8 * AM_RMAX);
-    cudaError_t e = cudaFuncSetAttribute(attn_split_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    kp_launch_pdl(attn_split_mma_kernel<HD>, dim3(dim3(n_chunks, G, n)), dim3(128), smem, s, 
+template <int HD, int NW>
+static int launch_split(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
+                        int max_blocks, const int* row_seg, const int* positions, float* part_acc, float* part_ml,
+                        int n_chunks, float scale, int window, int page_size, int n, int H, int G, cudaStream_t s) {
+    const size_t smem = 1024 + (size_t)2 * NW * AM_TILE * HD * 2 + sizeof(float) * (NW * AM_RMAX * HD + 2 * NW * AM_RMAX) + 16;
+    alignas(64) CUtensorMap tm = {};
+    // tiles by TMA where the pages allow it (and the cache is known by its size), else by cp.async
+    const bool tma = n_pages > 0 && n_pages * 2 * G * page_size < 2147483647LL && (page_size % 8 == 0) && (page_size % AM_TILE == 0 || AM_TILE % page_size == 0) &&
+                     !((uintptr_t)cache & 15) &&
+                     kp_make_map_bf16_2d(&tm, cache, (unsigned long long)n_pages * 2 * G * page_size, HD, HD, 64,
+                                         page_size < AM_TILE ? page_size : AM_TILE) == 0;
+    auto kern = tma ? attn_split_mma_kernel<HD, NW, true> : attn_split_mma_kernel<HD, NW, false>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    kp_launch_pdl(kern, dim3(dim3(n_chunks, G, n)), dim3(NW * 32), smem, s, tm,
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
         n_chunks, scale, window, page_size, H, G);
     return kp_launch_status();
@@ -395,22 +460,31 @@ static int launch_prefill(const void* q, int ldq, const void* cache, const int* 
 
 extern "C" {
 
-// The chunk partials of the split pass (bfloat16, head size 64 or 128, H/G <= 8).  The caller runs the merge
-// of attention_decode.cu afterwards (kp_attention_merge) on the same scratch.
-int kp_attention_split_mma(const void* q, int ldq, const void* cache, const int* block_table, int max_blocks,
-                           const int* row_seg, const int* positions, float* scratch, int n_chunks, float scale,
-                           int window, int page_size, int n, int H, int G, int hd, void* stream) {
+// The chunk partials of the split pass (bfloat16, head size 64 or 128, H/G <= 8); chunks of `chunk_keys` keys
+// (64, 128 or 256), n_chunks of them.  The caller runs the merge of attention_decode.cu afterwards
+// (kp_attention_merge, same chunk size) on the same scratch.
+int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table, int max_blocks,
+                           const int* row_seg, const int* positions, float* scratch, int n_chunks, int chunk_keys,
+                           float scale, int window, int page_size, int n, int H, int G, int hd, void* stream) {
     if (n <= 0) return 0;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || H / G > AM_RMAX || page_size < 1 || n_chunks < 1 || n > 65535 ||
-        G > 65535 || (ldq & 1))
+        G > 65535 || (ldq & 1) || (chunk_keys != 64 && chunk_keys != 128 && chunk_keys != 256))
         return KP_ERR_UNSUPPORTED;
     float* part_acc = scratch;
     float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     cudaStream_t s = (cudaStream_t)stream;
-    if (hd == 64) return launch_split<64>(q, ldq, cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
-                                          n_chunks, scale, window, page_size, n, H, G, s);
-    return launch_split<128>(q, ldq, cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml, n_chunks,
-                             scale, window, page_size, n, H, G, s);
+#define AM_SPLIT(HD, NW)                                                                                          \
+    return launch_split<HD, NW>(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, part_acc, part_ml, \
+                                n_chunks, scale, window, page_size, n, H, G, s)
+    if (hd == 64) {
+        if (chunk_keys == 64) AM_SPLIT(64, 1);
+        if (chunk_keys == 128) AM_SPLIT(64, 2);
+        AM_SPLIT(64, 4);
+    }
+    if (chunk_keys == 64) AM_SPLIT(128, 1);
+    if (chunk_keys == 128) AM_SPLIT(128, 2);
+    AM_SPLIT(128, 4);
+#undef AM_SPLIT
 }
 
 // tile_seg / tile_row0: for each tile of 64 rows its segment and its first row (device arrays, n_tiles long)
@@ -426,6 +500,14 @@ int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const in
                                             n_tiles, out, ldo, scale, window, page_size, H, G, s);
     return launch_prefill<128>(q, ldq, cache, block_table, max_blocks, cu_rows, seg_pos, tile_seg, tile_row0, n_tiles,
                                out, ldo, scale, window, page_size, H, G, s);
+}
+
+// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
+int kp_attention_mma_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
+    return v;
 }
 
 }  // extern "C"

@@ -160,6 +160,15 @@ def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose:
                 raise KernelBuildError(f"nvcc failed on {name}.cu (exit {proc.returncode}):\n"
                                        + outp.decode("utf-8", "replace"))
             os.replace(tmp, out)
+            # libraries of earlier versions of this source are of no use any more (a process that still has
+            # one loaded keeps its mapping)
+            prefix = f"lib{name}-"
+            for f in os.listdir(os.path.dirname(out)):
+                if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
+                    try:
+                        os.unlink(os.path.join(os.path.dirname(out), f))
+                    except OSError:
+                        pass
             if verbose:
                 print(f"[kappai_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
                       file=sys.stderr, flush=True)

@@ -265,12 +265,13 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
 
 
 SPLIT_CHUNK = 256          # keys a chunk of the split-KV attention
+SPLIT_CHUNK_MMA = 256       # keys a chunk of its tensor-core form: 64, 128 or 256 (a divisor of SPLIT_CHUNK)
 SPLIT_MAX_RATIO = 8        # query heads per kv head it takes
 
 
 def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
     """Float elements of scratch that :func:`attention_split` needs."""
-    return n_rows * H * n_chunks * (hd + 2)
+    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2)
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
@@ -288,13 +289,16 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
         raise KernelError("attention_split: scratch too small")
     lib = load_library("attention_decode")
     if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
-        # tensor-core chunk pass, then the same merge
+        # tensor-core chunk pass over smaller chunks, then the same merge
+        parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
         _check(load_library("attention_mma").kp_attention_split_mma(
-            _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(row_seg),
-            _ptr(positions), _ptr(scratch), n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
-            _stream()), "attention_split_mma")
-        _check(lib.kp_attention_merge(_ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), n_chunks,
-                                      int(window or 0), n, H, hd, dtype_code(q.dtype), _stream()), "attention_merge")
+            _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
+            _ptr(block_table), block_table.shape[1], _ptr(row_seg),
+            _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), page_size,
+            n, H, G, hd, _stream()), "attention_split_mma")
+        _check(lib.kp_attention_merge(_ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
+                                      SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), _stream()),
+               "attention_merge")
         return out
     _check(lib.kp_attention_split(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
                                   _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
@@ -304,6 +308,7 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     return out
 
 
+USE_TMA_ATTENTION = True       # its key/value tiles come by TMA where the page size allows
 USE_MMA_ATTENTION = True       # bfloat16 attention with head size 64 or 128 runs on the tensor cores
 PREFILL_TILE = 64              # query rows a CTA of the prefill attention kernel
 
