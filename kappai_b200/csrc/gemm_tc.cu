@@ -10,7 +10,9 @@
 //              (128 x BN x 16) per stage, descriptors advanced by 32 bytes inside the swizzled rows;
 //              tcgen05.commit frees the stage ("empty" mbarrier) and, after the last k-block, signals
 //              "accumulator ready".
-//   warps 2-5: epilogue.  Each reads its 32 lanes of tensor memory with tcgen05.ld (32 columns at a
+//   the rest: epilogue, two warps for each quarter of the 128 lanes of tensor memory (a warp may only read
+//              the lanes 32 * (warp % 4) ...), taking the 32-column pieces in turn: more loads and stores in
+//              flight.  Each reads its lanes with tcgen05.ld (32 columns at a
 //              time), applies bias / residual accumulation / SwiGLU and writes its rows of C.
 // Rows of A beyond M and rows of W beyond N are zero-filled by TMA (out-of-bounds fill) and masked at the
 // store; K needs no padding (the tail of the last k-block is zero-filled too) but K % 8 == 0 (16-byte rows).
@@ -33,7 +35,8 @@
 
 #define TC_BM 128
 #define TC_BK 64
-#define TC_THREADS 192                      // 6 warps
+#define TC_EPI_PER_Q 2                       // epilogue warps for each quarter of the tensor-memory lanes
+#define TC_THREADS (64 + TC_EPI_PER_Q * 128) // the producer warp, the MMA warp and the epilogue warps
 #define TC_WAIT_NS 1000000000ull            // one second: far beyond any legitimate wait
 
 __device__ int g_tc_status = 0;
@@ -126,6 +129,8 @@ struct TcArgs {
     void* C; int ldc;
     int M, N, K, ff;
     int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
+    int a_rows;                             // rows of the A box: 128, fewer (a multiple of 8) when M < 128
+    int n_stages;                           // stages of the ring
 };
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
@@ -133,15 +138,20 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmW, const TcArgs p) {
-    constexpr int A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    constexpr int B_BYTES = BN * TC_BK * 2;
     constexpr int N_OUT_TILE = (EPI == EPI_SWIGLU) ? BN / 2 : BN;       // output columns of the tile
+    const int A_BYTES = p.a_rows * TC_BK * 2;                            // the rows of A that are brought in
+    const int STAGES = p.n_stages;
     extern __shared__ unsigned char smem[];
-    // STAGES x (A tile | B tile); the swizzled tiles must start on 1024-byte boundaries
+    // STAGES x (A tile | B tile); the swizzled tiles must start on 1024-byte boundaries.  With fewer than 128
+    // rows of A a stage is smaller and the ring has more of them; the MMA still reads 128 rows from the
+    // stage's start (on into the W tile and beyond: the host leaves room after the last stage), and what it
+    // makes of the rest lands in accumulator rows that nobody reads.
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * (A_BYTES + B_BYTES));
+    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * (A_BYTES + B_BYTES) + (TC_BM * TC_BK * 2 - A_BYTES));
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;                                  // [2]: accumulator b holds a finished tile
     uint64_t* acc_empty = acc_full + 2;                                   // [2]: accumulator b has been read out
@@ -159,7 +169,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // set-up that depends on no earlier kernel comes before the wait on it
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b2 = 0; b2 < 2; b2++) { mbar_init(&acc_full[b2], 1); mbar_init(&acc_empty[b2], 4); }
+        for (int b2 = 0; b2 < 2; b2++) { mbar_init(&acc_full[b2], 1); mbar_init(&acc_empty[b2], 4 * TC_EPI_PER_Q); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -172,13 +182,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            int it = 0;
+            int s = 0;                                                    // stage, and the parity of its round
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
-                for (int kb = 0; kb < n_kb; kb++, it++) {
-                    const int s = it % STAGES;
-                    if (*abort_flag || !mbar_wait_bounded(&empty[s], ((it / STAGES) & 1) ^ 1)) { *abort_flag = 1; ok = false; break; }
+                for (int kb = 0; kb < n_kb; kb++) {
+                    if (*abort_flag || !mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
                     unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
                     unsigned char* b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
@@ -189,22 +199,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     } else {
                         tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
                     }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(TC_BM, BN);
-            int it = 0, ti = 0;
+            int s = 0, ti = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
                 const int b2 = ti & 1;                                    // accumulator of this tile
                 if (*abort_flag || !mbar_wait_bounded(&acc_empty[b2], ((ti >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b2 * BN);
-                for (int kb = 0; kb < n_kb; kb++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait_bounded(&full[s], (it / STAGES) & 1)) { *abort_flag = 1; ok = false; break; }
+                for (int kb = 0; kb < n_kb; kb++) {
+                    if (!mbar_wait_bounded(&full[s], ph)) { *abort_flag = 1; ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
                     const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + A_BYTES);
@@ -212,6 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     for (int k = 0; k < TC_BK / 16; k++)      // 32 bytes along K inside the swizzled row: +2 in the address field
                         umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
                     umma_commit(&empty[s]);                    // the stage is free when these MMAs have read it
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (ok) umma_commit(&acc_full[b2]);            // arrives when every MMA of the tile has completed
             }
@@ -220,6 +232,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory; it works on tile i while the
         // MMA warp already fills the other accumulator with tile i + 1
         const int q = warp & 3;
+        const int half = (warp - 2) >> 2;                                 // which of the quarter's warps
         int ti = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
@@ -230,7 +243,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < N_OUT_TILE; c += 32) {
+            for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
                 uint32_t r[32];
                 tmem_ld32(lane_base + c, r);
                 uint32_t u[32];
@@ -337,15 +350,23 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
     return r == CUDA_SUCCESS ? 0 : KP_ERR_BAD_ARG;
 }
 
-template <int BN, int STAGES, int EPI>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tw, const TcArgs& a, cudaStream_t s) {
-    constexpr size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
-    auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
-    static bool attr_set = false;
-    if (!attr_set) {
+static int g_tc_smem_kb = 208;              // shared memory for the ring (tunable for measurements)
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaStream_t s) {
+    const int stage = a.a_rows * TC_BK * 2 + BN * TC_BK * 2;
+    const int slack = (TC_BM - a.a_rows) * TC_BK * 2;          // the MMA's reads past a short last stage
+    int stages = (g_tc_smem_kb * 1024 - slack) / stage;
+    if (stages > 24) stages = 24;
+    if (stages < 2) stages = 2;
+    a.n_stages = stages;
+    const size_t smem = (size_t)stages * stage + slack + (size_t)(2 * stages + 4) * 8 + 16 + 1024;
+    auto kern = gemm_tc_kernel<BN, EPI>;
+    static size_t attr_smem = 0;
+    if (smem > attr_smem) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attr_set = true;
+        attr_smem = smem;
     }
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
@@ -380,27 +401,52 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
         a.ff = N / 2;
     }
     const int n_out = epi == EPI_SWIGLU ? a.ff : N;
-    // Tile width by a small cost model: a CTA's main loop is bound by the bytes that it brings into shared
-    // memory for each k-block (128 rows of A and BN rows of W), so a narrow tile costs about 2/3 of a wide one
-    // and does half the work; the number of rounds over the SMs decides between them.
+    // Tile width.  Many rows: by a small cost model: a CTA's main loop is bound by the bytes that it brings
+    // into shared memory for each k-block (128 rows of A and BN rows of W), so a narrow tile costs about 2/3
+    // of a wide one and does half the work; the number of rounds over the SMs decides between them.
+    // At most 128 rows (one row of tiles, W streamed once): the widest tile that still gives about a hundred
+    // tiles, so that enough CTAs pull on the memory.
     const long long m_tiles = (M + TC_BM - 1) / TC_BM;
-    const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + 147) / 148;
-    const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + 147) / 148;
-    const bool wide = epi != EPI_SWIGLU && rounds_wide * 3 <= rounds_narrow * 2;
+    int bn;
+    if (m_tiles > 1) {
+        const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + 147) / 148;
+        const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + 147) / 148;
+        bn = (epi == EPI_SWIGLU || rounds_wide * 3 <= rounds_narrow * 2) ? 256 : 128;
+    } else {
+        const int lowest = epi == EPI_SWIGLU ? 64 : 32;
+        bn = 256;
+        while (bn > lowest && (n_out + (epi == EPI_SWIGLU ? bn / 2 : bn) - 1) / (epi == EPI_SWIGLU ? bn / 2 : bn) < 96) bn /= 2;
+    }
+    a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;
-    int st = make_map(&ta, A, M, K, lda, TC_BM);
+    int st = make_map(&ta, A, M, K, lda, a.a_rows);
     if (st) return st;
-    st = make_map(&tw, W, N, K, ldw, epi == EPI_SWIGLU ? 128 : (wide ? 256 : 128));
+    st = make_map(&tw, W, N, K, ldw, epi == EPI_SWIGLU ? bn / 2 : bn);
     if (st) return st;
     cudaStream_t s = (cudaStream_t)stream;
+#define TC_PICK(EPI)                                               \
+    switch (bn) {                                                  \
+        case 256: return launch<256, EPI>(ta, tw, a, s);           \
+        case 128: return launch<128, EPI>(ta, tw, a, s);           \
+        case 64: return launch<64, EPI>(ta, tw, a, s);             \
+        default: return launch<32, EPI>(ta, tw, a, s);             \
+    }
     switch (epi) {
-        case EPI_STORE: return wide ? launch<256, 4, EPI_STORE>(ta, tw, a, s) : launch<128, 6, EPI_STORE>(ta, tw, a, s);
-        case EPI_STORE_F32: return wide ? launch<256, 4, EPI_STORE_F32>(ta, tw, a, s) : launch<128, 6, EPI_STORE_F32>(ta, tw, a, s);
-        case EPI_ACCUM_F32: return wide ? launch<256, 4, EPI_ACCUM_F32>(ta, tw, a, s) : launch<128, 6, EPI_ACCUM_F32>(ta, tw, a, s);
-        case EPI_SWIGLU: return launch<256, 4, EPI_SWIGLU>(ta, tw, a, s);
+        case EPI_STORE: TC_PICK(EPI_STORE)
+        case EPI_STORE_F32: TC_PICK(EPI_STORE_F32)
+        case EPI_ACCUM_F32: TC_PICK(EPI_ACCUM_F32)
+        case EPI_SWIGLU:
+            switch (bn) {
+                case 256: return launch<256, EPI_SWIGLU>(ta, tw, a, s);
+                case 128: return launch<128, EPI_SWIGLU>(ta, tw, a, s);
+                default: return launch<64, EPI_SWIGLU>(ta, tw, a, s);
+            }
         default: return KP_ERR_BAD_ARG;
     }
+#undef TC_PICK
 }
+
+void kp_gemm_tc_set_smem_kb(int kb) { g_tc_smem_kb = kb < 64 ? 64 : (kb > 216 ? 216 : kb); }
 
 // Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
 int kp_tc_status(void) {

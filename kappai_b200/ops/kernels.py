@@ -355,6 +355,18 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 USE_TC = True              # bfloat16 products of more than 64 rows run on tcgen05 tensor cores
 
 
+def tc_pays_for_few_rows(M: int, N: int, swiglu: bool) -> bool:
+    """Few-row products that the tcgen05 kernel runs faster than the weight-streaming
+    kernels (measured on B200, K = 2048): the 65536-row head from 8 rows on (46 us at
+    every M against 48 us at 8 rows and 199 us at 64), and wide products without the
+    SwiGLU epilogue from 32 rows on (6144 rows: 16 us at every M against 17 us at 32
+    rows and 28 us at 64).  Narrow products (2048 rows: few tiles) stay with the
+    streaming kernels at every M <= 64."""
+    if swiglu:
+        return False
+    return (N >= 32768 and M >= 8) or (N >= 4096 and M >= 32)
+
+
 def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
     """Can the tcgen05 kernel take this product (bfloat16, 16-byte aligned rows, K a multiple of 8)?"""
     return (USE_TC and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0

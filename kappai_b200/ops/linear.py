@@ -87,9 +87,10 @@ def linear(a: Operand, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
             tmp = K.gemm_nt_simt(a32, w, torch.empty((M, N), dtype=torch.float32, device=a.device), bias)
             return K.cast(tmp, out)
         raise K.KernelError(f"linear: operand dtypes {a.dtype} and {w.dtype} do not go together")
-    if K.skinny_ok(a, w):
+    tc = K.tc_ok(a, w) and out.stride(1) == 1
+    if K.skinny_ok(a, w) and not (tc and K.tc_pays_for_few_rows(M, N, False)):
         return K.gemm_skinny(a, w, out, bias, accumulate)
-    if K.tc_ok(a, w) and out.stride(1) == 1:
+    if tc:
         return K.gemm_tc(a, w, out, bias, accumulate)
     return K.gemm_nt_simt(a, w, out, bias, accumulate)
 

@@ -21,7 +21,9 @@ def _no_timeouts():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 8, 8), (129, 130, 72), (300, 331, 120), (2048, 2048, 2048),
-                                   (257, 6144, 2048), (130, 2048, 5632), (1000, 96, 200), (512, 1000, 4096)])
+                                   (257, 6144, 2048), (130, 2048, 5632), (1000, 96, 200), (512, 1000, 4096),
+                                   # few rows: short A boxes, and tiles of 64 columns while W has few rows
+                                   (1, 200, 72), (8, 6144, 2048), (17, 2048, 5632), (64, 331, 120), (100, 20000, 256)])
 def test_gemm_tc_against_plain(M, N, K):
     from kappai_b200.ops import kernels as Kn
     rng = np.random.default_rng(60)
@@ -53,7 +55,8 @@ def test_gemm_tc_rows_do_not_depend_on_m():
         assert torch.equal(part, full[lo:hi]), (lo, hi)
 
 
-@pytest.mark.parametrize("M,ff,K", [(128, 128, 64), (200, 100, 64), (2048, 5632, 2048), (70, 333, 96)])
+@pytest.mark.parametrize("M,ff,K", [(128, 128, 64), (200, 100, 64), (2048, 5632, 2048), (70, 333, 96), (9, 5632, 2048),
+                                    (64, 100, 64), (33, 15000, 128)])
 def test_gemm_tc_swiglu(M, ff, K):
     from kappai_b200.ops import kernels as Kn
     rng = np.random.default_rng(62)
