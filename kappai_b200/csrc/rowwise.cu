@@ -84,6 +84,87 @@ rmsnorm_rows_vec_kernel(const float* __restrict__ x, const float* __restrict__ w
     }
 }
 
+// Rows of at most 2048 elements (a multiple of 4), two kernels with ONE arithmetic, so that which of them runs
+// (it depends on the number of rows) changes no bit of the result.  The row is 16 groups of 32 float4; "lane" l
+// of "part" g (0..7) sums the squares of float4 l of group g, then of group g + 8, in element order; a lane's
+// eight parts are added in order of g; the 32 lane sums are added by the warp butterfly.
+//  * warp kernel (many rows): one warp a row, the row in registers (all loads in flight at once), no
+//    block-wide barrier, eight rows a block.
+//  * block kernel (few rows): 256 threads a row (thread = (part, lane)), so that a row's loads are spread
+//    over more threads and the rows over more SMs.
+__device__ __forceinline__ float sumsq8(const float4& a, const float4& b) {
+    float ss = 0.f;
+    ss = fmaf(a.x, a.x, ss); ss = fmaf(a.y, a.y, ss); ss = fmaf(a.z, a.z, ss); ss = fmaf(a.w, a.w, ss);
+    ss = fmaf(b.x, b.x, ss); ss = fmaf(b.y, b.y, ss); ss = fmaf(b.z, b.z, ss); ss = fmaf(b.w, b.w, ss);
+    return ss;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                         const int* __restrict__ rows, int n, int d, float eps) {
+    kp_pdl_begin();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= n) return;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+    const int n4 = d >> 2;
+    float4 v[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int i = lane + j * 32;
+        v[j] = i < n4 ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = sumsq8(v[0], v[8]);
+#pragma unroll
+    for (int g = 1; g < 8; g++) ss += sumsq8(v[g], v[g + 8]);
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    T* dst = y + (size_t)r * d;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int i = lane + j * 32;
+        if (i < n4) {
+            const float4 ww = __ldg(w4 + i);
+            store4(dst + 4 * i, (v[j].x * scale) * ww.x, (v[j].y * scale) * ww.y, (v[j].z * scale) * ww.z,
+                   (v[j].w * scale) * ww.w);
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_blk_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ y,
+                        const int* __restrict__ rows, int d, float eps) {
+    kp_pdl_begin();
+    __shared__ float part[8][32];
+    __shared__ float scale_s;
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int r = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * d);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = d >> 2;
+    const int ia = lane + 32 * g, ib = lane + 32 * (g + 8);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 a = ia < n4 ? __ldg(src + ia) : zero, b = ib < n4 ? __ldg(src + ib) : zero;
+    const float4 wa = ia < n4 ? __ldg(w4 + ia) : zero, wb = ib < n4 ? __ldg(w4 + ib) : zero;
+    part[g][lane] = sumsq8(a, b);
+    __syncthreads();
+    if (g == 0) {
+        float ss = part[0][lane];
+#pragma unroll
+        for (int k = 1; k < 8; k++) ss += part[k][lane];
+        ss = warp_sum(ss);
+        if (lane == 0) scale_s = 1.0f / sqrtf(ss / (float)d + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    T* dst = y + (size_t)r * d;
+    if (ia < n4) store4(dst + 4 * ia, (a.x * scale) * wa.x, (a.y * scale) * wa.y, (a.z * scale) * wa.z, (a.w * scale) * wa.w);
+    if (ib < n4) store4(dst + 4 * ib, (b.x * scale) * wb.x, (b.y * scale) * wb.y, (b.z * scale) * wb.z, (b.w * scale) * wb.w);
+}
+
 // act = silu(gate) * up,  silu(g) = g / (1 + exp(-g))     (src/backend/cpu/scalar/core.c:774-800)
 // gate_up rows hold [gate(ff) | up(ff)].
 template <typename T>
@@ -125,6 +206,16 @@ int kp_rmsnorm_rows(const float* x, const float* w, void* y, const int* rows, in
     if (n <= 0) return 0;
     if ((d & 3) == 0 && d <= 8192 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & 15) == 0) {
         // which kernel runs depends on the row's size and alignment only, never on the batch
+        if (d <= 2048) {
+            if (n <= 256) {
+                KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_blk_kernel<T>, dim3(n), dim3(256), 0,
+                                                           (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
+            } else {
+                KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_warp_kernel<T>, dim3((n + 7) / 8), dim3(256), 0,
+                                                           (cudaStream_t)stream, x, w, (T*)y, rows, n, d, eps)));
+            }
+            return kp_launch_status();
+        }
         KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(rmsnorm_rows_vec_kernel<T>, dim3(n), dim3(256), 0, (cudaStream_t)stream, x, w, (T*)y, rows, d, eps)));
         return kp_launch_status();
     }

@@ -184,6 +184,94 @@ shortconv_fwd_vec_kernel(const T* __restrict__ p, int ldp, const float* __restri
     store_vec(out + (size_t)row * ldo + c0, o);
 }
 
+// Many rows (prompt portions), conv length KK <= 4: a thread takes its V channels through CONV_ROWS consecutive
+// rows, keeping the last KK-1 products B*X and the channel weights in registers, so every input is read once
+// (the kernel above reads each row KK times).  The history of a chunk's first rows comes from the rows before
+// it or, at the head of a segment, from the state; the order of summation is that of the kernels above.
+#define CONV_ROWS 8
+template <typename T, int KK>
+__global__ void __launch_bounds__(128)
+shortconv_fwd_rows_kernel(const T* __restrict__ p, int ldp, const float* __restrict__ w,
+                          const float* __restrict__ bias, const float* __restrict__ state,
+                          const int* __restrict__ row_seg, const int* __restrict__ cu_rows,
+                          const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
+                          T* __restrict__ out, int ldo, int n, int d) {
+    kp_pdl_begin();
+    constexpr int V = ConvVec<T>::N;
+    const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    const int row_lo = blockIdx.y * CONV_ROWS;
+    if (c0 >= d || row_lo >= n) return;
+    const int row_hi = min(n, row_lo + CONV_ROWS);
+    float wk[KK][V], bs[V];
+#pragma unroll
+    for (int i = 0; i < V; i++) {
+#pragma unroll
+        for (int k = 0; k < KK; k++) wk[k][i] = w[(size_t)(c0 + i) * KK + k];
+        bs[i] = bias ? bias[c0 + i] : 0.f;
+    }
+    float hist[KK - 1][V];                              // B*X of the KK-1 rows before the current one (oldest first)
+#pragma unroll
+    for (int k = 0; k < KK - 1; k++) {
+        const int r = row_lo - (KK - 1) + k;
+        if (r >= 0) {
+            float hb[V], hx[V];
+            load_vec<T>(p + (size_t)r * ldp + c0, hb);
+            load_vec<T>(p + (size_t)r * ldp + 2 * (size_t)d + c0, hx);
+#pragma unroll
+            for (int i = 0; i < V; i++) hist[k][i] = hb[i] * hx[i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; i++) hist[k][i] = 0.f;
+        }
+    }
+#pragma unroll 2
+    for (int row = row_lo; row < row_hi; row++) {
+        const int seg = row_seg[row];
+        const int t = row - cu_rows[seg];
+        const T* pr = p + (size_t)row * ldp;
+        float bv[V], cv[V], xv[V], bx[V], sum[V];
+        load_vec<T>(pr + c0, bv);
+        load_vec<T>(pr + d + c0, cv);
+        load_vec<T>(pr + 2 * (size_t)d + c0, xv);
+#pragma unroll
+        for (int i = 0; i < V; i++) bx[i] = bv[i] * xv[i];
+        if (t < KK - 1) {
+            // the head of a segment: rows before it belong to another request; the history is the state (or zero)
+            const bool fresh = seg_pos[seg] == 0;
+            const float* st = state + (size_t)seg_slot[seg] * (KK - 1) * d;
+#pragma unroll
+            for (int k = 0; k < KK - 1; k++) {
+                const int st_t = t - (KK - 1) + k;
+                if (st_t < 0) {
+#pragma unroll
+                    for (int i = 0; i < V; i++) hist[k][i] = fresh ? 0.f : st[(size_t)(KK - 1 + st_t) * d + c0 + i];
+                }
+            }
+        }
+        if (KK != 3) {
+#pragma unroll
+            for (int i = 0; i < V; i++) sum[i] = bx[i] * wk[KK - 1][i];
+#pragma unroll
+            for (int k = 0; k < KK - 1; k++)
+#pragma unroll
+                for (int i = 0; i < V; i++) sum[i] += hist[k][i] * wk[k][i];
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; i++) sum[i] = (hist[0][i] * wk[0][i] + hist[1][i] * wk[1][i]) + bx[i] * wk[2][i];
+        }
+        float o[V];
+#pragma unroll
+        for (int i = 0; i < V; i++) o[i] = cv[i] * (bias ? sum[i] + bs[i] : sum[i]);
+        store_vec(out + (size_t)row * ldo + c0, o);
+#pragma unroll
+        for (int k = 0; k + 1 < KK - 1; k++)
+#pragma unroll
+            for (int i = 0; i < V; i++) hist[k][i] = hist[k + 1][i];
+#pragma unroll
+        for (int i = 0; i < V; i++) hist[KK - 2][i] = bx[i];
+    }
+}
+
 // Every segment is one row (a decode step): output and new state by the same
 // thread, so one launch does both.  Row r belongs to segment r.
 template <typename T>
@@ -238,6 +326,16 @@ int kp_shortconv_forward(const void* p, int ldp, const float* w, const float* bi
         const int vec = dtype == KP_DTYPE_BF16 ? 8 : 4;
         const size_t esz = dtype == KP_DTYPE_BF16 ? 2 : 4;
         if (d % vec == 0 && ldp % vec == 0 && ldo % vec == 0 && (((uintptr_t)p | (uintptr_t)out) & 15) == 0 && esz) {
+            if (K <= 4) {
+                // which kernel runs depends on the layer's sizes and alignment only, never on the batch
+                dim3 rgrid((d / vec + 127) / 128, (n + CONV_ROWS - 1) / CONV_ROWS);
+#define CONV_ROWS_LAUNCH(KK)                                                                                       \
+    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(shortconv_fwd_rows_kernel<T, KK>, dim3(rgrid), dim3(128), 0,         \
+        (cudaStream_t)stream, (const T*)p, ldp, w, bias, state, row_seg, cu_rows, seg_pos, seg_slot, (T*)out, ldo, n, d)))
+                if (K == 2) { CONV_ROWS_LAUNCH(2); } else if (K == 3) { CONV_ROWS_LAUNCH(3); } else { CONV_ROWS_LAUNCH(4); }
+#undef CONV_ROWS_LAUNCH
+                return kp_launch_status();
+            }
             dim3 vgrid((d / vec + 127) / 128, n);
             KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(shortconv_fwd_vec_kernel<T>, dim3(vgrid), dim3(128), 0, (cudaStream_t)stream,
                 (const T*)p, ldp, w, bias, state, row_seg, cu_rows, seg_pos, seg_slot, (T*)out, ldo, n, d, K)));

@@ -67,6 +67,24 @@ def test_rmsnorm_rows(dtype, n, d, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d", [2048, 1000, 64])
+def test_rmsnorm_rows_same_bits_for_few_and_many_rows(dtype, d):
+    """Few rows and many rows run different kernels (a block or a warp a row) with the
+    same arithmetic: a row's result must not depend on how many rows there are."""
+    from kappai_b200.ops import kernels as K
+    rng = np.random.default_rng(11)
+    n = 600
+    x = (rng.standard_normal((n, d)) * rng.uniform(0.01, 30, (n, 1))).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(d)).astype(np.float32)
+    many = K.rmsnorm_rows(dev(x), dev(w), 1e-5, torch.empty((n, d), dtype=dtype, device="cuda"))
+    ref = P.rmsnorm(x.astype(np.float64), w.astype(np.float64), 1e-5)
+    np.testing.assert_allclose(many.cpu().double().numpy(), ref, rtol=tol(dtype), atol=tol(dtype))
+    for lo, hi in ((0, 1), (7, 15), (100, 356), (599, 600)):
+        few = K.rmsnorm_rows(dev(x[lo:hi]), dev(w), 1e-5, torch.empty((hi - lo, d), dtype=dtype, device="cuda"))
+        assert torch.equal(few, many[lo:hi]), (lo, hi)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     from kappai_b200.ops import kernels as K
     rng = np.random.default_rng(2)
