@@ -1,0 +1,365 @@
+// Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores
+// (bfloat16, head size 64).
+//
+// One CTA: 128 consecutive rows of a segment x one head, looping over tiles of 128 keys up to the causal
+// limit.  Per tile (formulas as in attention.cu; src/backend/cpu/scalar/core.c:383-433):
+//   S  = Q K^T        tcgen05.mma, 128 x 128 x 64, Q and the K tile K-major in shared memory (TMA, 128-byte
+//                     swizzle), S in tensor memory (128 columns);
+//   P  = exp(S*scale - m), row statistics in float32 by 128 threads (one a row) that read S from tensor
+//        memory, mask keys outside [pos - window + 1, pos], and write P as bfloat16 into shared memory in the
+//        K-major swizzled layout of an MMA operand;
+//   PV = P V          tcgen05.mma, 128 x 64 x 128, V tile as it lies in the cache (keys x head size: the
+//                     MN-major B operand), into 64 more columns of tensor memory, not accumulated there:
+//   O  = O*corr + PV  in registers of the row's thread, so a change of the row maximum needs no pass over
+//                     tensor memory.
+// Roles by warp: 0 TMA producer (Q once; K double-buffered, V single: the next K tile is requested as soon as
+// S has been computed from the buffer, the next V tile as soon as PV has), 1 tensor-memory owner and MMA
+// issuer, 2-5 the rows.  The MMA warp issues the next tile's S right behind PV, so it overlaps the rows'
+// update of O.  Two CTAs fit an SM (96 KB of shared memory, 256 columns of tensor memory each) and fill each
+// other's waits.
+//
+// K/V tiles come from the cache seen as one 2-D tensor (rows = page, K|V, kv head, key of the page), one box
+// of min(page size, 128) keys each; boxes wholly outside the CTA's keys are not loaded (V starts zeroed, so
+// what an unloaded part holds is finite and meets P = 0).  Tiles start at multiples of 128 of the absolute
+// key index.  The CTAs are those of the 64-row tile list whose tile starts a 128-row stretch of its segment.
+// Every mbarrier wait is bounded; a wait that gives up sets the status word, and the CTA frees its tensor
+// memory and returns.
+#include "tma.cuh"
+
+#define AT_BM 128
+#define AT_BN 128
+#define AT_HD 64
+#define AT_THREADS 192
+#define AT_TILE_BYTES (128 * 64 * 2)         // a 128 x 64 bf16 tile: 16 KB
+
+__device__ int g_attn_tc_status = 0;
+
+__device__ __forceinline__ void at_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(kp_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void at_tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(kp_smem_u32(dst_smem)), "r"(ncols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void at_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(kp_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void at_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// Descriptor of a tile whose rows are 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.  For a
+// K-major operand the rows are the M/N index and a step of 16 along K is +32 bytes; for the MN-major V tile
+// the rows are the K index (keys) and a step of 16 keys is +2048 bytes.
+__device__ __forceinline__ uint64_t at_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// float32 accumulator, bfloat16 operands; b_mn: the B operand is MN-major (bit 16)
+__host__ __device__ constexpr uint32_t at_idesc(int M, int N, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(N >> 3) << 17) |
+           ((uint32_t)(M >> 4) << 24);
+}
+
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct AtArgs {
+    const int* block_table; int max_blocks;
+    const int* cu_rows; const int* seg_pos; const int* tile_seg; const int* tile_row0;
+    bf16* out; int ldo;
+    float scale; int window; int page_size; int H, G; int n_tiles;
+};
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmC, const AtArgs p) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    unsigned char* Qs = sm;                                     // 16 KB
+    unsigned char* Ks = Qs + AT_TILE_BYTES;                     // 2 x 16 KB
+    unsigned char* Vs = Ks + 2 * AT_TILE_BYTES;                 // 16 KB
+    unsigned char* Ps = Vs + AT_TILE_BYTES;                     // 2 x 16 KB: keys 0..63 | keys 64..127
+    uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + 2 * AT_TILE_BYTES);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;                                // [2]
+    uint64_t* k_empty = bars + 3;                               // [2]
+    uint64_t* v_full = bars + 5;
+    uint64_t* v_empty = bars + 6;
+    uint64_t* s_full = bars + 7;
+    uint64_t* p_full = bars + 8;
+    uint64_t* pv_full = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h = blockIdx.y, kvh = h / (p.H / p.G);
+    const int tile = p.n_tiles - 1 - (int)blockIdx.x;            // the last (longest) tiles start first
+    const int seg = p.tile_seg[tile];
+    const int row0 = p.tile_row0[tile];
+    const int seg_begin = p.cu_rows[seg], seg_end = p.cu_rows[seg + 1];
+    if ((row0 - seg_begin) % AT_BM != 0) return;                 // the second half of a 128-row stretch
+    const int n_rows = min(AT_BM, seg_end - row0);
+    const int pos0 = p.seg_pos[seg] + (row0 - seg_begin);        // position of the first row
+    const int k_hi_all = pos0 + n_rows - 1;
+    const int k_lo_all = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int kt_lo = k_lo_all / AT_BN, kt_hi = k_hi_all / AT_BN;
+    const int* bt = p.block_table + (size_t)seg * p.max_blocks;
+
+    if (threadIdx.x == 0) {
+        kp_mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) { kp_mbar_init(&k_full[i], 1); kp_mbar_init(&k_empty[i], 1); }
+        kp_mbar_init(v_full, 1); kp_mbar_init(v_empty, 1);
+        kp_mbar_init(s_full, 1); kp_mbar_init(p_full, 128); kp_mbar_init(pv_full, 1);
+        *abort_flag = 0;
+        kp_mbar_init_fence();
+    }
+    // V starts zeroed: a part of a tile that is never loaded then holds something finite
+    for (int i = threadIdx.x; i < AT_TILE_BYTES / 16; i += AT_THREADS) reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == 1) at_tmem_alloc(tmem_slot, 256);
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+    kp_pdl_begin();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            kp_mbar_expect_tx(q_full, AT_TILE_BYTES);
+            kp_tma_load_2d(Qs, &tmQ, h * AT_HD, row0, q_full);
+            const int box = min(p.page_size, AT_BN);
+            // the boxes of a tile that hold keys of this CTA; `dst` a K or V buffer, kv 0 or 1
+            auto load_tile = [&](unsigned char* dst, int kt, int kv, uint64_t* bar) {
+                uint32_t bytes = 0;
+                for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box)
+                    if (key0 <= k_hi_all && key0 + box - 1 >= k_lo_all) bytes += box * AT_HD * 2;
+                kp_mbar_expect_tx(bar, bytes);
+                for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box) {
+                    if (!(key0 <= k_hi_all && key0 + box - 1 >= k_lo_all)) continue;
+                    const int page = bt[key0 / p.page_size];
+                    const int row = ((page * 2 + kv) * p.G + kvh) * p.page_size + key0 % p.page_size;
+                    kp_tma_load_2d(dst + (size_t)(key0 - kt * AT_BN) * 128, &tmC, 0, row, bar);
+                }
+            };
+            int i = 0;
+            for (int kt = kt_lo; kt <= kt_hi; kt++, i++) {
+                const int kb = i & 1;
+                if (*abort_flag || !kp_mbar_wait_bounded(&k_empty[kb], ((i >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
+                load_tile(Ks + kb * AT_TILE_BYTES, kt, 0, &k_full[kb]);
+                if (!kp_mbar_wait_bounded(v_empty, (i & 1) ^ 1)) { *abort_flag = 1; break; }
+                load_tile(Vs, kt, 1, v_full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = at_idesc(AT_BM, AT_BN, false);
+            constexpr uint32_t idesc_pv = at_idesc(AT_BM, AT_HD, true);
+            bool ok = kp_mbar_wait_bounded(q_full, 0);
+            const uint64_t qdesc = at_desc(kp_smem_u32(Qs));
+            auto issue_s = [&](int i) {                               // S of the i-th tile of the loop
+                const int kb = i & 1;
+                if (!kp_mbar_wait_bounded(&k_full[kb], (i >> 1) & 1)) return false;
+                // S is free once the rows have read the tile before (they say so with p_full)
+                if (i > 0 && !kp_mbar_wait_bounded(p_full, (i - 1) & 1)) return false;
+                at_fence_after();
+                const uint64_t kdesc = at_desc(kp_smem_u32(Ks + kb * AT_TILE_BYTES));
+#pragma unroll
+                for (int k = 0; k < AT_HD / 16; k++) at_umma(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k ? 1u : 0u);
+                at_commit(s_full);
+                at_commit(&k_empty[kb]);
+                return true;
+            };
+            const int n_kt = kt_hi - kt_lo + 1;
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_kt && ok; i++) {
+                // PV of tile i: P is in shared memory (p_full), V has come
+                if (!kp_mbar_wait_bounded(p_full, i & 1) || !kp_mbar_wait_bounded(v_full, i & 1)) { ok = false; break; }
+                at_fence_after();
+                const uint32_t pa = kp_smem_u32(Ps), va = kp_smem_u32(Vs);
+#pragma unroll
+                for (int kk = 0; kk < AT_BN / 16; kk++)
+                    at_umma(tmem_pv, at_desc(pa + (kk >> 2) * AT_TILE_BYTES) + 2 * (kk & 3), at_desc(va + kk * 2048), idesc_pv,
+                            kk ? 1u : 0u);
+                at_commit(pv_full);
+                at_commit(v_empty);
+                if (i + 1 < n_kt) ok = issue_s(i + 1);
+            }
+            if (!ok) { *abort_flag = 1; atomicExch(&g_attn_tc_status, 1); }
+        }
+    } else {
+        // ---- the rows: thread r of the four warps owns row r (lane r of tensor memory)
+        const int q4 = warp & 3;
+        const int r = q4 * 32 + lane;
+        const int pos = pos0 + r;                                     // this row's position (rows >= n_rows: masked)
+        const bool live = r < n_rows;
+        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
+        const int lo_max = p.window > 0 ? max(0, pos0 + n_rows - 1 - p.window + 1) : 0;    // the last row's first key
+        const float sl2 = p.scale * 1.4426950408889634f;              // scale * log2(e)
+        float o[AT_HD];
+#pragma unroll
+        for (int d = 0; d < AT_HD; d++) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        int i = 0;
+        for (int kt = kt_lo; kt <= kt_hi && ok; kt++, i++) {
+            if (!kp_mbar_wait_bounded(s_full, i & 1) || *abort_flag) { ok = false; break; }
+            at_fence_after();
+            // Most tiles lie wholly inside every row's keys; only the tile on the diagonal, a window's edge and
+            // rows past the end of the segment need the mask.  Scores are taken in base 2: exp(x) = 2^(x log2 e).
+            const bool masked = !(kt * AT_BN + AT_BN - 1 <= pos0 && kt * AT_BN >= lo_max && n_rows == AT_BM);
+            // pass 1: the row maximum of this tile
+            float tmax = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < AT_BN; c += 32) {
+                uint32_t s[32];
+                at_tmem_ld32(tmem_s + lane_off + c, s);
+                if (masked) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int key = kt * AT_BN + c + j;
+                        if (live && key >= lo && key <= pos) tmax = fmaxf(tmax, __uint_as_float(s[j]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) tmax = fmaxf(tmax, __uint_as_float(s[j]));
+                }
+            }
+            const float m_new = fmaxf(m, tmax * sl2);                       // in units of log2
+            const float corr = (m_new == -INFINITY) ? 0.f : exp2f(m - m_new);       // m = -inf: 2^(-inf) = 0
+            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;
+            // pass 2: P = 2^(S*scale*log2e - m_new), rounded to bfloat16 as it enters the product; its row sum
+            float lsum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < AT_BN; c += 32) {
+                uint32_t s[32];
+                at_tmem_ld32(tmem_s + lane_off + c, s);
+                unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
+#pragma unroll
+                for (int j8 = 0; j8 < 4; j8++) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j2 = 0; j2 < 4; j2++) {
+                        float pv[2];
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int j = j8 * 8 + j2 * 2 + e;
+                            float pe = at_exp2(fmaf(__uint_as_float(s[j]), sl2, -m_sub));
+                            if (masked) {
+                                const int key = kt * AT_BN + c + j;
+                                if (!(live && key >= lo && key <= pos)) pe = 0.f;
+                            }
+                            pv[e] = pe;
+                        }
+                        lsum += pv[0] + pv[1];
+                        const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
+                        w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                    }
+                    const int chunk = ((c & 63) >> 3) + j8;               // 16-byte piece of the 128-byte row
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            l = l * corr + lsum;
+            m = m_new;
+            at_fence_before();                                           // the reads of S are done
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+            at_mbar_arrive(p_full);
+            // O = O * corr + P V
+            if (!kp_mbar_wait_bounded(pv_full, i & 1)) { ok = false; break; }
+            at_fence_after();
+#pragma unroll
+            for (int c = 0; c < AT_HD; c += 32) {
+                uint32_t v[32];
+                at_tmem_ld32(tmem_pv + lane_off + c, v);
+#pragma unroll
+                for (int j = 0; j < 32; j++) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
+            }
+            at_fence_before();
+        }
+        if (ok && live) {
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            bf16* dst = p.out + (size_t)(row0 + r) * p.ldo + (size_t)h * AT_HD;
+#pragma unroll
+            for (int d = 0; d < AT_HD; d += 8) {
+                uint4 w;
+                __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                for (int e = 0; e < 4; e++) w2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                *reinterpret_cast<uint4*>(dst + d) = w;
+            }
+        }
+        if (!ok && lane == 0) atomicExch(&g_attn_tc_status, 1);
+    }
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) at_tmem_dealloc(tmem_base, 256);
+}
+
+extern "C" {
+
+// tile_seg / tile_row0: the 64-row tiles of the step (device arrays, n_tiles long); n_rows_total: rows of q.
+int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void* cache, long long n_pages,
+                            const int* block_table, int max_blocks, const int* cu_rows, const int* seg_pos,
+                            const int* tile_seg, const int* tile_row0, int n_tiles, void* out, int ldo, float scale,
+                            int window, int page_size, int H, int G, int hd, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (hd != AT_HD || G < 1 || H % G || H > 65535 || (ldq & 7) || (ldo & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15) ||
+        ((uintptr_t)cache & 15) || page_size < 8 || (page_size % 8) || !(page_size % AT_BN == 0 || AT_BN % page_size == 0) ||
+        n_pages <= 0 || n_pages * 2 * G * page_size >= 2147483647LL)
+        return KP_ERR_UNSUPPORTED;
+    alignas(64) CUtensorMap tq, tc;
+    int st = kp_make_map_bf16_2d(&tq, q, (unsigned long long)n_rows_total, H * hd, ldq, AT_HD, AT_BM);
+    if (st) return st;
+    st = kp_make_map_bf16_2d(&tc, cache, (unsigned long long)n_pages * 2 * G * page_size, hd, hd, AT_HD,
+                             page_size < AT_BN ? page_size : AT_BN);
+    if (st) return st;
+    AtArgs a = {};
+    a.block_table = block_table; a.max_blocks = max_blocks; a.cu_rows = cu_rows; a.seg_pos = seg_pos;
+    a.tile_seg = tile_seg; a.tile_row0 = tile_row0; a.out = (bf16*)out; a.ldo = ldo; a.scale = scale; a.window = window;
+    a.page_size = page_size; a.H = H; a.G = G; a.n_tiles = n_tiles;
+    const size_t smem = 1024 + 6 * AT_TILE_BYTES + 10 * 8 + 16;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set = true;
+    }
+    kp_launch_pdl(attn_prefill_tc_kernel, dim3(n_tiles, H), dim3(AT_THREADS), smem, (cudaStream_t)stream, tq, tc, a);
+    return kp_launch_status();
+}
+
+// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
+int kp_attention_tc_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_attn_tc_status, &zero, sizeof(int));
+    return v;
+}
+
+}  // extern "C"

@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 ]
 
 # the kernel libraries of this package, in csrc/
-LIBRARIES = ["rowwise", "gemm_simt", "gemm_skinny", "gemm_stream", "gemm_tc", "shortconv", "qkrope", "attention", "attention_decode", "attention_mma", "attention_noalloc", "sampling"]
+LIBRARIES = ["rowwise", "gemm_simt", "gemm_skinny", "gemm_stream", "gemm_tc", "shortconv", "qkrope", "attention", "attention_decode", "attention_mma", "attention_tc", "attention_noalloc", "sampling"]
 
 
 class KernelBuildError(RuntimeError):

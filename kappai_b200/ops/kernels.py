@@ -313,6 +313,23 @@ USE_MMA_ATTENTION = True       # bfloat16 attention with head size 64 or 128 run
 PREFILL_TILE = 64              # query rows a CTA of the prefill attention kernel
 
 
+USE_TC_ATTENTION = True        # prompt portions with head size 64 run on the tcgen05 tensor cores
+
+
+def attention_prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, page_size: int, hd: int) -> bool:
+    """Can the tcgen05 prefill attention take this call (head size 64, 16-byte aligned rows, a page size
+    that is a multiple of 8 and divides 128 or is a multiple of it)?"""
+    return (USE_TC_ATTENTION and hd == 64 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
+            and page_size % 8 == 0 and (page_size % 128 == 0 or 128 % page_size == 0)
+            and cache.shape[0] * cache.shape[1] * cache.shape[2] * page_size < 2 ** 31 - 1)
+
+
+def attention_tc_status() -> int:
+    """0, or 1 if a bounded wait of the tcgen05 attention kernel gave up since the last call (synchronises)."""
+    return int(load_library("attention_tc").kp_attention_tc_status())
+
+
 def attention_prefill_ok(q: torch.Tensor, hd: int) -> bool:
     return USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0
 
@@ -332,6 +349,13 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         raise KernelError("attention_prefill: shape mismatch")
     if tile_seg.numel() != tile_row0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
+    if attention_prefill_tc_ok(q, out, cache, page_size, hd):
+        _check(load_library("attention_tc").kp_attention_prefill_tc(
+            _ptr(q), _rows_2d(q, "q"), n, _ptr(cache), ctypes.c_longlong(cache.shape[0]), _ptr(block_table),
+            block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos), _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(),
+            _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), page_size, H, G, hd, _stream()),
+            "attention_prefill_tc")
+        return out
     _check(load_library("attention_mma").kp_attention_prefill_mma(
         _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
         _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),

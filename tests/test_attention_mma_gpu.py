@@ -1,6 +1,7 @@
-"""The tensor-core prefill attention kernel alone, against whole-sequence
-attention: segments that start anywhere in a sequence, tiles that end inside a
-page, windows, one far key, and a batch that mixes long and short segments."""
+"""The tensor-core prefill attention kernels alone (the tcgen05 kernel where it
+takes the sizes, and the mma.sync kernel), against whole-sequence attention:
+segments that start anywhere in a sequence, tiles that end inside a page,
+windows, one far key, and a batch that mixes long and short segments."""
 import math
 
 import numpy as np
@@ -13,6 +14,17 @@ from test_kernels_gpu import dev, i32, paged_setup, rt
 pytestmark = pytest.mark.gpu
 DT = torch.bfloat16
 TOL = 1.5e-2
+
+
+@pytest.fixture(autouse=True, params=["tcgen05", "mma.sync"])
+def _both_kernels(request):
+    """Every test runs twice: with the tcgen05 kernel allowed, and with the mma.sync kernel only."""
+    from kappai_b200.ops import kernels as Kn
+    old = Kn.USE_TC_ATTENTION
+    Kn.USE_TC_ATTENTION = request.param == "tcgen05"
+    yield
+    Kn.USE_TC_ATTENTION = old
+    assert Kn.attention_tc_status() == 0, "a bounded wait of the tcgen05 attention kernel gave up"
 
 
 def run_prefill(qs, q_from, seq_lens, cache, bt, scale, window, page, H, G, hd):
