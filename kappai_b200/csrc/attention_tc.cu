@@ -21,7 +21,8 @@
 // K/V tiles come from the cache seen as one 2-D tensor (rows = page, K|V, kv head, key of the page), one box
 // of min(page size, 128) keys each; boxes wholly outside the CTA's keys are not loaded (V starts zeroed, so
 // what an unloaded part holds is finite and meets P = 0).  Tiles start at multiples of 128 of the absolute
-// key index.  The CTAs are those of the 64-row tile list whose tile starts a 128-row stretch of its segment.
+// key index.  The caller lists the 128-row tiles from the one that reads the most keys to the one that reads
+// the fewest; a CTA takes the i-th and the i-th last, so every CTA has about the same work.
 // Every mbarrier wait is bounded; a wait that gives up sets the status word, and the CTA frees its tensor
 // memory and returns.
 #include "tma.cuh"
@@ -96,6 +97,26 @@ struct AtArgs {
     float scale; int window; int page_size; int H, G; int n_tiles;
 };
 
+// One piece of work: 128 rows (or the segment's last few) of one segment
+struct AtItem {
+    int row0, n_rows, pos0, k_hi_all, k_lo_all, kt_lo, kt_hi;
+    const int* bt;
+};
+__device__ __forceinline__ AtItem at_item(const AtArgs& p, int tile) {
+    AtItem it;
+    const int seg = p.tile_seg[tile];
+    it.row0 = p.tile_row0[tile];
+    const int seg_begin = p.cu_rows[seg], seg_end = p.cu_rows[seg + 1];
+    it.n_rows = min(AT_BM, seg_end - it.row0);
+    it.pos0 = p.seg_pos[seg] + (it.row0 - seg_begin);            // position of the first row
+    it.k_hi_all = it.pos0 + it.n_rows - 1;
+    it.k_lo_all = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    it.kt_lo = it.k_lo_all / AT_BN;
+    it.kt_hi = it.k_hi_all / AT_BN;
+    it.bt = p.block_table + (size_t)seg * p.max_blocks;
+    return it;
+}
+
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmC, const AtArgs p) {
     extern __shared__ unsigned char smem_dyn[];
@@ -118,17 +139,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y, kvh = h / (p.H / p.G);
-    const int tile = p.n_tiles - 1 - (int)blockIdx.x;            // the last (longest) tiles start first
-    const int seg = p.tile_seg[tile];
-    const int row0 = p.tile_row0[tile];
-    const int seg_begin = p.cu_rows[seg], seg_end = p.cu_rows[seg + 1];
-    if ((row0 - seg_begin) % AT_BM != 0) return;                 // the second half of a 128-row stretch
-    const int n_rows = min(AT_BM, seg_end - row0);
-    const int pos0 = p.seg_pos[seg] + (row0 - seg_begin);        // position of the first row
-    const int k_hi_all = pos0 + n_rows - 1;
-    const int k_lo_all = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-    const int kt_lo = k_lo_all / AT_BN, kt_hi = k_hi_all / AT_BN;
-    const int* bt = p.block_table + (size_t)seg * p.max_blocks;
+    // The tiles are listed from the one that reads the most keys to the one that reads the fewest; this CTA
+    // takes the blockIdx.x-th and the blockIdx.x-th last, so every CTA has about the same work.
+    const int n_items = ((int)blockIdx.x < p.n_tiles - 1 - (int)blockIdx.x) ? 2 : 1;
+    auto item_tile = [&](int idx) { return idx == 0 ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x; };
 
     if (threadIdx.x == 0) {
         kp_mbar_init(q_full, 1);
@@ -149,66 +163,85 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
     kp_pdl_begin();
 
+    // The three roles walk the same items and key tiles; `i` counts the key tiles over both items, and the
+    // mbarrier parities follow from it (buffer uses: K buffer i & 1 for the (i >> 1)-th time, V, S, P, PV for
+    // the i-th time).
     if (warp == 0) {
         if (lane == 0) {
-            kp_mbar_expect_tx(q_full, AT_TILE_BYTES);
-            kp_tma_load_2d(Qs, &tmQ, h * AT_HD, row0, q_full);
             const int box = min(p.page_size, AT_BN);
-            // the boxes of a tile that hold keys of this CTA; `dst` a K or V buffer, kv 0 or 1
-            auto load_tile = [&](unsigned char* dst, int kt, int kv, uint64_t* bar) {
-                uint32_t bytes = 0;
-                for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box)
-                    if (key0 <= k_hi_all && key0 + box - 1 >= k_lo_all) bytes += box * AT_HD * 2;
-                kp_mbar_expect_tx(bar, bytes);
-                for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box) {
-                    if (!(key0 <= k_hi_all && key0 + box - 1 >= k_lo_all)) continue;
-                    const int page = bt[key0 / p.page_size];
-                    const int row = ((page * 2 + kv) * p.G + kvh) * p.page_size + key0 % p.page_size;
-                    kp_tma_load_2d(dst + (size_t)(key0 - kt * AT_BN) * 128, &tmC, 0, row, bar);
-                }
-            };
             int i = 0;
-            for (int kt = kt_lo; kt <= kt_hi; kt++, i++) {
-                const int kb = i & 1;
-                if (*abort_flag || !kp_mbar_wait_bounded(&k_empty[kb], ((i >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
-                load_tile(Ks + kb * AT_TILE_BYTES, kt, 0, &k_full[kb]);
-                if (!kp_mbar_wait_bounded(v_empty, (i & 1) ^ 1)) { *abort_flag = 1; break; }
-                load_tile(Vs, kt, 1, v_full);
+            bool ok = true;
+            for (int idx = 0; idx < n_items && ok; idx++) {
+                const AtItem it = at_item(p, item_tile(idx));
+                if (idx > 0) {
+                    // Q is read by the S products; the last of the item before has freed its K buffer when done
+                    const int last = i - 1;
+                    if (!kp_mbar_wait_bounded(&k_empty[last & 1], (last >> 1) & 1)) { *abort_flag = 1; break; }
+                }
+                kp_mbar_expect_tx(q_full, AT_TILE_BYTES);
+                kp_tma_load_2d(Qs, &tmQ, h * AT_HD, it.row0, q_full);
+                // the boxes of a tile that hold keys of this item; `dst` a K or V buffer, kv 0 or 1
+                auto load_tile = [&](unsigned char* dst, int kt, int kv, uint64_t* bar) {
+                    uint32_t bytes = 0;
+                    for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box)
+                        if (key0 <= it.k_hi_all && key0 + box - 1 >= it.k_lo_all) bytes += box * AT_HD * 2;
+                    kp_mbar_expect_tx(bar, bytes);
+                    for (int key0 = kt * AT_BN; key0 < (kt + 1) * AT_BN; key0 += box) {
+                        if (!(key0 <= it.k_hi_all && key0 + box - 1 >= it.k_lo_all)) continue;
+                        const int page = it.bt[key0 / p.page_size];
+                        const int row = ((page * 2 + kv) * p.G + kvh) * p.page_size + key0 % p.page_size;
+                        kp_tma_load_2d(dst + (size_t)(key0 - kt * AT_BN) * 128, &tmC, 0, row, bar);
+                    }
+                };
+                for (int kt = it.kt_lo; kt <= it.kt_hi; kt++, i++) {
+                    const int kb = i & 1;
+                    if (*abort_flag || !kp_mbar_wait_bounded(&k_empty[kb], ((i >> 1) & 1) ^ 1)) { *abort_flag = 1; ok = false; break; }
+                    load_tile(Ks + kb * AT_TILE_BYTES, kt, 0, &k_full[kb]);
+                    if (!kp_mbar_wait_bounded(v_empty, (i & 1) ^ 1)) { *abort_flag = 1; ok = false; break; }
+                    load_tile(Vs, kt, 1, v_full);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = at_idesc(AT_BM, AT_BN, false);
             constexpr uint32_t idesc_pv = at_idesc(AT_BM, AT_HD, true);
-            bool ok = kp_mbar_wait_bounded(q_full, 0);
             const uint64_t qdesc = at_desc(kp_smem_u32(Qs));
-            auto issue_s = [&](int i) {                               // S of the i-th tile of the loop
-                const int kb = i & 1;
-                if (!kp_mbar_wait_bounded(&k_full[kb], (i >> 1) & 1)) return false;
-                // S is free once the rows have read the tile before (they say so with p_full)
-                if (i > 0 && !kp_mbar_wait_bounded(p_full, (i - 1) & 1)) return false;
-                at_fence_after();
-                const uint64_t kdesc = at_desc(kp_smem_u32(Ks + kb * AT_TILE_BYTES));
+            bool ok = true;
+            int base = 0;                                                // key tiles of the items before
+            for (int idx = 0; idx < n_items && ok; idx++) {
+                const AtItem it = at_item(p, item_tile(idx));
+                const int n_kt = it.kt_hi - it.kt_lo + 1;
+                ok = kp_mbar_wait_bounded(q_full, idx & 1);
+                auto issue_s = [&](int i) {                               // S of key tile i (counted over the items)
+                    const int kb = i & 1;
+                    if (!kp_mbar_wait_bounded(&k_full[kb], (i >> 1) & 1)) return false;
+                    // S is free once the rows have read the tile before (they say so with p_full)
+                    if (i > 0 && !kp_mbar_wait_bounded(p_full, (i - 1) & 1)) return false;
+                    at_fence_after();
+                    const uint64_t kdesc = at_desc(kp_smem_u32(Ks + kb * AT_TILE_BYTES));
 #pragma unroll
-                for (int k = 0; k < AT_HD / 16; k++) at_umma(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k ? 1u : 0u);
-                at_commit(s_full);
-                at_commit(&k_empty[kb]);
-                return true;
-            };
-            const int n_kt = kt_hi - kt_lo + 1;
-            if (ok) ok = issue_s(0);
-            for (int i = 0; i < n_kt && ok; i++) {
-                // PV of tile i: P is in shared memory (p_full), V has come
-                if (!kp_mbar_wait_bounded(p_full, i & 1) || !kp_mbar_wait_bounded(v_full, i & 1)) { ok = false; break; }
-                at_fence_after();
-                const uint32_t pa = kp_smem_u32(Ps), va = kp_smem_u32(Vs);
+                    for (int k = 0; k < AT_HD / 16; k++) at_umma(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k ? 1u : 0u);
+                    at_commit(s_full);
+                    at_commit(&k_empty[kb]);
+                    return true;
+                };
+                if (ok) ok = issue_s(base);
+                for (int j = 0; j < n_kt && ok; j++) {
+                    const int i = base + j;
+                    // PV of tile i: P is in shared memory (p_full), V has come
+                    if (!kp_mbar_wait_bounded(p_full, i & 1) || !kp_mbar_wait_bounded(v_full, i & 1)) { ok = false; break; }
+                    at_fence_after();
+                    const uint32_t pa = kp_smem_u32(Ps), va = kp_smem_u32(Vs);
 #pragma unroll
-                for (int kk = 0; kk < AT_BN / 16; kk++)
-                    at_umma(tmem_pv, at_desc(pa + (kk >> 2) * AT_TILE_BYTES) + 2 * (kk & 3), at_desc(va + kk * 2048), idesc_pv,
-                            kk ? 1u : 0u);
-                at_commit(pv_full);
-                at_commit(v_empty);
-                if (i + 1 < n_kt) ok = issue_s(i + 1);
+                    for (int kk = 0; kk < AT_BN / 16; kk++)
+                        at_umma(tmem_pv, at_desc(pa + (kk >> 2) * AT_TILE_BYTES) + 2 * (kk & 3), at_desc(va + kk * 2048),
+                                idesc_pv, kk ? 1u : 0u);
+                    at_commit(pv_full);
+                    at_commit(v_empty);
+                    if (j + 1 < n_kt) ok = issue_s(i + 1);
+                }
+                base += n_kt;
             }
             if (!ok) { *abort_flag = 1; atomicExch(&g_attn_tc_status, 1); }
         }
@@ -216,102 +249,106 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         // ---- the rows: thread r of the four warps owns row r (lane r of tensor memory)
         const int q4 = warp & 3;
         const int r = q4 * 32 + lane;
-        const int pos = pos0 + r;                                     // this row's position (rows >= n_rows: masked)
-        const bool live = r < n_rows;
-        const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
         const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
-        const int lo_max = p.window > 0 ? max(0, pos0 + n_rows - 1 - p.window + 1) : 0;    // the last row's first key
         const float sl2 = p.scale * 1.4426950408889634f;              // scale * log2(e)
-        float o[AT_HD];
-#pragma unroll
-        for (int d = 0; d < AT_HD; d++) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
         bool ok = true;
         int i = 0;
-        for (int kt = kt_lo; kt <= kt_hi && ok; kt++, i++) {
-            if (!kp_mbar_wait_bounded(s_full, i & 1) || *abort_flag) { ok = false; break; }
-            at_fence_after();
-            // Most tiles lie wholly inside every row's keys; only the tile on the diagonal, a window's edge and
-            // rows past the end of the segment need the mask.  Scores are taken in base 2: exp(x) = 2^(x log2 e).
-            const bool masked = !(kt * AT_BN + AT_BN - 1 <= pos0 && kt * AT_BN >= lo_max && n_rows == AT_BM);
-            // pass 1: the row maximum of this tile
-            float tmax = -INFINITY;
+        for (int idx = 0; idx < n_items && ok; idx++) {
+            const AtItem it = at_item(p, item_tile(idx));
+            const int pos = it.pos0 + r;                                  // this row's position (rows >= n_rows: masked)
+            const bool live = r < it.n_rows;
+            const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+            const int lo_max = p.window > 0 ? max(0, it.k_hi_all - p.window + 1) : 0;    // the last row's first key
+            float o[AT_HD];
+#pragma unroll
+            for (int d = 0; d < AT_HD; d++) o[d] = 0.f;
+            float m = -INFINITY, l = 0.f;
+            for (int kt = it.kt_lo; kt <= it.kt_hi && ok; kt++, i++) {
+                if (!kp_mbar_wait_bounded(s_full, i & 1) || *abort_flag) { ok = false; break; }
+                at_fence_after();
+                // Most tiles lie wholly inside every row's keys; only the tile on the diagonal, a window's edge
+                // and rows past the end of the segment need the mask.  Scores are taken in base 2:
+                // exp(x) = 2^(x log2 e).
+                const bool masked = !(kt * AT_BN + AT_BN - 1 <= it.pos0 && kt * AT_BN >= lo_max && it.n_rows == AT_BM);
+                // pass 1: the row maximum of this tile
+                float tmax = -INFINITY;
 #pragma unroll 1
-            for (int c = 0; c < AT_BN; c += 32) {
-                uint32_t s[32];
-                at_tmem_ld32(tmem_s + lane_off + c, s);
-                if (masked) {
+                for (int c = 0; c < AT_BN; c += 32) {
+                    uint32_t s[32];
+                    at_tmem_ld32(tmem_s + lane_off + c, s);
+                    if (masked) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int key = kt * AT_BN + c + j;
-                        if (live && key >= lo && key <= pos) tmax = fmaxf(tmax, __uint_as_float(s[j]));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) tmax = fmaxf(tmax, __uint_as_float(s[j]));
-                }
-            }
-            const float m_new = fmaxf(m, tmax * sl2);                       // in units of log2
-            const float corr = (m_new == -INFINITY) ? 0.f : exp2f(m - m_new);       // m = -inf: 2^(-inf) = 0
-            const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;
-            // pass 2: P = 2^(S*scale*log2e - m_new), rounded to bfloat16 as it enters the product; its row sum
-            float lsum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < AT_BN; c += 32) {
-                uint32_t s[32];
-                at_tmem_ld32(tmem_s + lane_off + c, s);
-                unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
-#pragma unroll
-                for (int j8 = 0; j8 < 4; j8++) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int j2 = 0; j2 < 4; j2++) {
-                        float pv[2];
-#pragma unroll
-                        for (int e = 0; e < 2; e++) {
-                            const int j = j8 * 8 + j2 * 2 + e;
-                            float pe = at_exp2(fmaf(__uint_as_float(s[j]), sl2, -m_sub));
-                            if (masked) {
-                                const int key = kt * AT_BN + c + j;
-                                if (!(live && key >= lo && key <= pos)) pe = 0.f;
-                            }
-                            pv[e] = pe;
+                        for (int j = 0; j < 32; j++) {
+                            const int key = kt * AT_BN + c + j;
+                            if (live && key >= lo && key <= pos) tmax = fmaxf(tmax, __uint_as_float(s[j]));
                         }
-                        lsum += pv[0] + pv[1];
-                        const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
-                        w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) tmax = fmaxf(tmax, __uint_as_float(s[j]));
                     }
-                    const int chunk = ((c & 63) >> 3) + j8;               // 16-byte piece of the 128-byte row
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                const float m_new = fmaxf(m, tmax * sl2);                       // in units of log2
+                const float corr = (m_new == -INFINITY) ? 0.f : exp2f(m - m_new);       // m = -inf: 2^(-inf) = 0
+                const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;
+                // pass 2: P = 2^(S*scale*log2e - m_new), rounded to bfloat16 as it enters the product; its row sum
+                float lsum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < AT_BN; c += 32) {
+                    uint32_t s[32];
+                    at_tmem_ld32(tmem_s + lane_off + c, s);
+                    unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
+#pragma unroll
+                    for (int j8 = 0; j8 < 4; j8++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j2 = 0; j2 < 4; j2++) {
+                            float pv[2];
+#pragma unroll
+                            for (int e = 0; e < 2; e++) {
+                                const int j = j8 * 8 + j2 * 2 + e;
+                                float pe = at_exp2(fmaf(__uint_as_float(s[j]), sl2, -m_sub));
+                                if (masked) {
+                                    const int key = kt * AT_BN + c + j;
+                                    if (!(live && key >= lo && key <= pos)) pe = 0.f;
+                                }
+                                pv[e] = pe;
+                            }
+                            lsum += pv[0] + pv[1];
+                            const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
+                            w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                        }
+                        const int chunk = ((c & 63) >> 3) + j8;               // 16-byte piece of the 128-byte row
+                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+                l = l * corr + lsum;
+                m = m_new;
+                at_fence_before();                                           // the reads of S are done
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+                at_mbar_arrive(p_full);
+                // O = O * corr + P V
+                if (!kp_mbar_wait_bounded(pv_full, i & 1)) { ok = false; break; }
+                at_fence_after();
+#pragma unroll
+                for (int c = 0; c < AT_HD; c += 32) {
+                    uint32_t v[32];
+                    at_tmem_ld32(tmem_pv + lane_off + c, v);
+#pragma unroll
+                    for (int j = 0; j < 32; j++) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
+                }
+                at_fence_before();
             }
-            l = l * corr + lsum;
-            m = m_new;
-            at_fence_before();                                           // the reads of S are done
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-            at_mbar_arrive(p_full);
-            // O = O * corr + P V
-            if (!kp_mbar_wait_bounded(pv_full, i & 1)) { ok = false; break; }
-            at_fence_after();
+            if (ok && live) {
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                bf16* dst = p.out + (size_t)(it.row0 + r) * p.ldo + (size_t)h * AT_HD;
 #pragma unroll
-            for (int c = 0; c < AT_HD; c += 32) {
-                uint32_t v[32];
-                at_tmem_ld32(tmem_pv + lane_off + c, v);
+                for (int d = 0; d < AT_HD; d += 8) {
+                    uint4 w;
+                    __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-                for (int j = 0; j < 32; j++) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
-            }
-            at_fence_before();
-        }
-        if (ok && live) {
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            bf16* dst = p.out + (size_t)(row0 + r) * p.ldo + (size_t)h * AT_HD;
-#pragma unroll
-            for (int d = 0; d < AT_HD; d += 8) {
-                uint4 w;
-                __nv_bfloat162* w2 = reinterpret_cast<__nv_bfloat162*>(&w);
-#pragma unroll
-                for (int e = 0; e < 4; e++) w2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                *reinterpret_cast<uint4*>(dst + d) = w;
+                    for (int e = 0; e < 4; e++) w2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                    *reinterpret_cast<uint4*>(dst + d) = w;
+                }
             }
         }
         if (!ok && lane == 0) atomicExch(&g_attn_tc_status, 1);
@@ -323,7 +360,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 
 extern "C" {
 
-// tile_seg / tile_row0: the 64-row tiles of the step (device arrays, n_tiles long); n_rows_total: rows of q.
+// tile_seg / tile_row0: the 128-row tiles of the step, most keys first (device arrays, n_tiles long);
+// n_rows_total: rows of q.
 int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void* cache, long long n_pages,
                             const int* block_table, int max_blocks, const int* cu_rows, const int* seg_pos,
                             const int* tile_seg, const int* tile_row0, int n_tiles, void* out, int ldo, float scale,
@@ -350,7 +388,7 @@ int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void
         if (e != cudaSuccess) return (int)e;
         attr_set = true;
     }
-    kp_launch_pdl(attn_prefill_tc_kernel, dim3(n_tiles, H), dim3(AT_THREADS), smem, (cudaStream_t)stream, tq, tc, a);
+    kp_launch_pdl(attn_prefill_tc_kernel, dim3((n_tiles + 1) / 2, H), dim3(AT_THREADS), smem, (cudaStream_t)stream, tq, tc, a);
     return kp_launch_status();
 }
 

@@ -68,8 +68,14 @@ class StepContext:
     tile_seg: Optional[torch.Tensor] = None    # int32 [n_tiles]: segment of each tile of ROW_TILE consecutive rows
     tile_row0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first row of each tile
     n_tiles: int = 0
+    # the same in stretches of BIG_TILE rows, those that read the most keys first (a kernel that gives a CTA the
+    # i-th and the i-th last of them gives every CTA about the same work)
+    big_tile_seg: Optional[torch.Tensor] = None
+    big_tile_row0: Optional[torch.Tensor] = None
+    n_big_tiles: int = 0
 
 
+BIG_TILE = 128                     # rows of the larger tiles
 ROW_TILE = 64                      # rows of one segment that a tiled kernel (prefill attention) takes at a time
 
 
@@ -128,9 +134,16 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), ROW_TILE):
             tile_seg.append(i)
             tile_row0.append(r0)
+    big = []
+    for i in range(n_seg):
+        for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), BIG_TILE):
+            last_pos = int(seg_pos[i]) + min(r0 + BIG_TILE, int(cu_rows[i + 1])) - int(cu_rows[i]) - 1
+            big.append((-last_pos, i, r0))                # the further on, the more keys
+    big.sort()
     parts = [token_ids, positions, row_seg, cu_rows, seg_pos, seg_slot,
              np.asarray(logit_rows, dtype=np.int32), np.asarray(tile_seg, dtype=np.int32),
-             np.asarray(tile_row0, dtype=np.int32)]
+             np.asarray(tile_row0, dtype=np.int32), np.asarray([b[1] for b in big], dtype=np.int32),
+             np.asarray([b[2] for b in big], dtype=np.int32)]
     n_fixed = len(parts)
     paged_host = {}
     for gk, page_size in groups.items():
@@ -173,7 +186,8 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         max_seg_len=max(len(s.tokens) for s in segments),
         max_context=max(s.pos_start + len(s.tokens) for s in segments),
         decode_only=all(len(s.tokens) == 1 for s in segments),
-        tile_seg=piece(7), tile_row0=piece(8), n_tiles=len(tile_seg))
+        tile_seg=piece(7), tile_row0=piece(8), n_tiles=len(tile_seg),
+        big_tile_seg=piece(9), big_tile_row0=piece(10), n_big_tiles=len(big))
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
     ctx.h2d_bytes = flat.numel() * 4
     return ctx

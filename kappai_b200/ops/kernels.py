@@ -336,9 +336,13 @@ def attention_prefill_ok(q: torch.Tensor, hd: int) -> bool:
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, cu_rows: torch.Tensor,
                       seg_pos: torch.Tensor, tile_seg: torch.Tensor, tile_row0: torch.Tensor, out: torch.Tensor,
-                      scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+                      scale: float, window: Optional[int], page_size: int, H: int, G: int, hd: int,
+                      big_tile_seg: Optional[torch.Tensor] = None, big_tile_row0: Optional[torch.Tensor] = None
+                      ) -> torch.Tensor:
     """Tensor-core causal attention for segments of many rows.  ``tile_seg`` / ``tile_row0`` list, for every
-    tile of 64 consecutive rows of a segment, its segment and its first row."""
+    tile of 64 consecutive rows of a segment, its segment and its first row; ``big_tile_seg`` /
+    ``big_tile_row0`` the same for tiles of 128 rows, the tile that reads the most keys first (with them the
+    tcgen05 kernel runs where it takes the sizes)."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(cache, "cache", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
     for t_, nm in ((block_table, "block_table"), (cu_rows, "cu_rows"), (seg_pos, "seg_pos"), (tile_seg, "tile_seg"),
@@ -349,10 +353,14 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         raise KernelError("attention_prefill: shape mismatch")
     if tile_seg.numel() != tile_row0.numel():
         raise KernelError("attention_prefill: tile lists differ in length")
-    if attention_prefill_tc_ok(q, out, cache, page_size, hd):
+    if big_tile_seg is not None and attention_prefill_tc_ok(q, out, cache, page_size, hd):
+        _need(big_tile_seg, "big_tile_seg", torch.int32); _need(big_tile_row0, "big_tile_row0", torch.int32)
+        if big_tile_seg.numel() != big_tile_row0.numel():
+            raise KernelError("attention_prefill: tile lists differ in length")
         _check(load_library("attention_tc").kp_attention_prefill_tc(
             _ptr(q), _rows_2d(q, "q"), n, _ptr(cache), ctypes.c_longlong(cache.shape[0]), _ptr(block_table),
-            block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos), _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(),
+            block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos), _ptr(big_tile_seg), _ptr(big_tile_row0),
+            big_tile_seg.numel(),
             _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), page_size, H, G, hd, _stream()),
             "attention_prefill_tc")
         return out

@@ -116,7 +116,8 @@ class Attention(Part):
                               self.scale, self.window, view.page_size, H, G, hd)
         elif K.attention_prefill_ok(q, hd) and ctx.tile_seg is not None:
             K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, ctx.tile_seg,
-                                ctx.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd)
+                                ctx.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd,
+                                getattr(ctx, "big_tile_seg", None), getattr(ctx, "big_tile_row0", None))
         else:
             K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
                              self.window, view.page_size, H, G, hd)

@@ -29,19 +29,22 @@ def _both_kernels(request):
 
 def run_prefill(qs, q_from, seq_lens, cache, bt, scale, window, page, H, G, hd):
     from kappai_b200.ops import kernels as Kn
-    rows, cu, seg_pos, tile_seg, tile_row0 = [], [0], [], [], []
+    rows, cu, seg_pos, tile_seg, tile_row0, big = [], [0], [], [], [], []
     for i, (L, a) in enumerate(zip(seq_lens, q_from)):
         rows.append(qs[i][a:])
         for r0 in range(cu[-1], cu[-1] + L - a, Kn.PREFILL_TILE):
             tile_seg.append(i)
             tile_row0.append(r0)
+        for r0 in range(cu[-1], cu[-1] + L - a, 128):
+            big.append((-(a + min(r0 + 128, cu[-1] + L - a) - cu[-1] - 1), i, r0))     # most keys first
         cu.append(cu[-1] + L - a)
         seg_pos.append(a)
+    big.sort()
     q_rows = np.concatenate(rows, 0).reshape(cu[-1], H * hd)
     out = torch.empty((cu[-1], H * hd), dtype=DT, device="cuda")
     assert Kn.attention_prefill_ok(dev(q_rows, DT), hd)
     Kn.attention_prefill(dev(q_rows, DT), dev(cache, DT), i32(bt), i32(cu), i32(seg_pos), i32(tile_seg), i32(tile_row0),
-                         out, scale, window, page, H, G, hd)
+                         out, scale, window, page, H, G, hd, i32([x[1] for x in big]), i32([x[2] for x in big]))
     return out.cpu().double().numpy().reshape(cu[-1], H, hd), cu
 
 
