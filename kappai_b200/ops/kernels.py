@@ -384,7 +384,7 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-USE_TC = True              # bfloat16 products of more than 64 rows run on tcgen05 tensor cores
+USE_TC = True              # bfloat16 products of more than 64 rows (and some of fewer) run on tcgen05 tensor cores
 
 
 def tc_pays_for_few_rows(M: int, N: int, swiglu: bool) -> bool:
@@ -435,8 +435,6 @@ def tc_status() -> int:
 
 STREAM_MAX_M = 64          # rows up to which the bulk-copy kernel is preferred
 USE_STREAM = True         # few-row products go to the bulk-copy kernel where their shape fits it
-STREAM_CHUNK = 256
-STREAM_MAX_SLAB = 96 * 1024
 
 
 def stream_fits(K: int, swiglu: bool) -> bool:
@@ -445,11 +443,11 @@ def stream_fits(K: int, swiglu: bool) -> bool:
 
 
 def stream_pays(N: int, K: int) -> bool:
-    """Measured on B200 (8 rows, back to back in a graph): the bulk-copy kernel wins or ties for the layer
-    products (6144 x 2048: 6.4 against 8.1 us; gate/up 11264 x 2048: 12.3 against 16.0; 2048 x 5632: 9.1
-    against 8.9; 2048 x 2048: 3.8 against 4.4) and, because it fetches its whole slab before it waits for
-    the kernel before it, overlaps that kernel's tail inside a model step.  It loses on the huge grid of
-    the 65536-row head (65 against 48 us), which keeps the register-streaming kernel."""
+    """Measured on B200 (8 rows, back to back in a graph): the bulk-copy kernel wins or ties with the
+    register-streaming kernel for the layer products (6144 x 2048: 8.0 against 8.1 us; gate/up 11264 x 2048:
+    9.5 against 16.0; 2048 x 5632: 10.2 against 8.9; 2048 x 2048: 4.6 against 4.4) and, because its producer
+    fills the ring before it waits for the kernel before it, overlaps that kernel's tail inside a model step.
+    It loses on the huge grid of a 65536-row head (65 against 48 us)."""
     return N <= 16384
 
 

@@ -11,7 +11,7 @@ with state, attention over its fp16 cache (online-softmax and plain), SwiGLU,
 argmax and the sampler.  Inputs and outputs are saved; the test
 tests/test_plain_vs_golden.py compares the plain implementation with them.
 
-    python tests/golden/make_golden.py [REF]        (REF defaults to /root/reference)
+    python tests/golden/make_golden.py REF          (REF: a checkout of the reference; or $KAPPAI_REFERENCE)
 """
 import ctypes
 import os
@@ -48,7 +48,9 @@ def fp(a):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KAPPAI_REFERENCE")
+    if not ref:
+        sys.exit("usage: make_golden.py REF   (a checkout of the reference)")
     lib = build(ref)
     rng = np.random.default_rng(1234)
     f32 = lambda *s: rng.standard_normal(s).astype(np.float32)
