@@ -4,16 +4,16 @@
 // The work is reading W once from HBM, and a decode step is a chain of such products, each only a few
 // microseconds long.  So the kernel is built to keep HBM busy across kernel boundaries:
 //
-//  * Persistent CTAs, two an SM.  A CTA walks the 8-row tiles of W it owns (tile t, t + grid, ...); for the
+//  * Persistent CTAs, two or three an SM.  A CTA walks the 8-row tiles of W it owns (tile t, t + grid, ...); for the
 //    SwiGLU epilogue a tile is 8 gate rows and the 8 matching up rows.
 //  * A producer warp streams the tiles' rows in chunks of 512 columns (one cp.async.bulk of 1 KB a row and
 //    chunk) into a ring of stages in shared memory; each stage has a "full" mbarrier (armed with the byte
 //    count) and an "empty" mbarrier (the consumer warps arrive when they have read it).  The producer
 //    runs ahead of the consumers, also across tile boundaries, so the stream never drains inside a kernel.
-//  * The ring is about 52 KB a CTA, under half an SM's shared memory, and the kernel is launched with
-//    programmatic dependent launch: the next product's CTAs become resident while this one still runs and
-//    their producers fill their rings before griddepcontrol.wait (weights depend on no earlier kernel).  The
-//    stream therefore does not drain between kernels either.
+//  * The ring is 64 KB a CTA with three CTAs an SM, 88 KB with two (products of few tiles), and the kernel
+//    is launched with programmatic dependent launch: the next product's CTAs become resident as soon as this
+//    one's leave and their producers fill their rings before griddepcontrol.wait (weights depend on no
+//    earlier kernel).
 //  * Eight consumer warps take the k-blocks of 32 of a stage (block b to warp b % 8), read W fragments from
 //    shared memory (rows padded: 16-byte reads of 8 rows hit all banks) and activation fragments from
 //    global memory (L1 serves them), and issue mma.m16n8k16 with the batch rows on the m side.  At a tile's
@@ -38,7 +38,8 @@
 #define ST_THREADS ((ST_CONSUMERS + 1) * 32) // plus the producer warp
 #define ST_COLS 512                          // columns of a stage: 16 k-blocks of 32, 2 a consumer warp
 #define ST_ROW_BYTES (ST_COLS * 2 + 64)      // a stage row in shared memory: 1 KB of data, pitch = 64 mod 128
-#define ST_RING_BYTES (53 * 1024)            // 6 stages of 8 rows or 3 stages of 2 x 8 rows
+#define ST_RING_BYTES (64 * 1024)            // the ring with three CTAs an SM: 7 stages of 8 rows, 3 of 2 x 8
+#define ST_RING_BYTES_FEW (88 * 1024)        // with two CTAs an SM (products with few tiles): 10 stages of 8 rows
 #define ST_WAIT_NS 1000000000ull             // one second: far beyond any legitimate wait
 
 __device__ int g_stream_status = 0;          // 0 ok; 1: a bounded wait gave up
@@ -320,8 +321,8 @@ static int n_sm() {
     return n;
 }
 
-static int g_ctas_per_sm = 3;                // persistent CTAs an SM (tunable for measurements)
-static int g_ring_bytes = ST_RING_BYTES;     // bytes of the ring (tunable for measurements)
+static int g_ctas_per_sm = 0;                // persistent CTAs an SM; 0: chosen by the product's tiles (see launch_epi)
+static int g_ring_bytes = 0;                 // bytes of the ring; 0: likewise (both can be set for measurements)
 
 template <typename Kern>
 static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const StreamArgs& a) {
@@ -337,9 +338,15 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     const int NW = epi == EPI_SWIGLU ? 2 : 1;
     const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
     const int n_tiles = (n_out + 7) / 8;
-    a.n_stages = g_ring_bytes / (NW * 8 * ST_ROW_BYTES);
-    if (a.n_stages < 2) a.n_stages = 2;             // 6 stages, or 3 with the SwiGLU epilogue
-    int g = n_sm() * g_ctas_per_sm;
+    // Measured on B200 (8 and 16 rows): three CTAs an SM with a 64 KB ring is best or tied for products with
+    // many tiles (6144 x 2048: 6.9 us against 8.1 with 53 KB); a product with at most two tiles an SM (2048
+    // rows) does better with two CTAs an SM and more of its long rows in flight (2048 x 5632: 8.3 against 10.3).
+    const bool few = n_tiles <= 2 * n_sm();
+    const int per_sm = g_ctas_per_sm ? g_ctas_per_sm : (few ? 2 : 3);
+    const int ring = g_ring_bytes ? g_ring_bytes : (few ? ST_RING_BYTES_FEW : ST_RING_BYTES);
+    a.n_stages = ring / (NW * 8 * ST_ROW_BYTES);
+    if (a.n_stages < 2) a.n_stages = 2;
+    int g = n_sm() * per_sm;
     if (g > n_tiles) g = n_tiles;
     dim3 grid(g);
     const size_t sm = smem_bytes(NW, MT, a.n_stages);
@@ -375,8 +382,8 @@ static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void*
 extern "C" {
 
 // Persistent CTAs an SM (1..4), for measurements.
-void kp_gemm_stream_set_ctas_per_sm(int n) { g_ctas_per_sm = n < 1 ? 1 : (n > 8 ? 8 : n); }
-void kp_gemm_stream_set_ring_kb(int kb) { g_ring_bytes = (kb < 18 ? 18 : (kb > 96 ? 96 : kb)) * 1024; }
+void kp_gemm_stream_set_ctas_per_sm(int n) { g_ctas_per_sm = n < 0 ? 0 : (n > 8 ? 8 : n); }
+void kp_gemm_stream_set_ring_kb(int kb) { g_ring_bytes = kb <= 0 ? 0 : (kb < 18 ? 18 : (kb > 96 ? 96 : kb)) * 1024; }
 
 int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                    int K, int epi, void* stream) {
