@@ -253,7 +253,9 @@ def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
     eng = Engine(EngineArgs(model=model_dir, dtype="bfloat16", ctx_size=CONTEXT, max_batch=max(batch, 1),
                             max_step_tokens=PROMPT_LEN, page_size=64, kv_tokens=batch * CONTEXT))
     V = eng.vocab_size
-    sp = SamplingParams(temperature=0.0, n_predict=warmup + steps + 8)
+    # room beyond the timed steps: the requests whose prompts ran first decode while the others' prompts run,
+    # and nobody may finish (and change the batch) inside the timed region
+    sp = SamplingParams(temperature=0.0, n_predict=warmup + steps + 2 * batch + 64)
     for _ in range(batch):
         eng.add_request(rng.integers(0, V, prompt_len).tolist(), sp)
     while any(len(r.output) == 0 for r in eng.requests.values()):
