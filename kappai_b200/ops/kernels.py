@@ -271,14 +271,19 @@ SPLIT_MAX_RATIO = 8        # query heads per kv head it takes
 
 def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
     """Float elements of scratch that :func:`attention_split` needs."""
-    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2)
+    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2) + n_rows * H
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
-                    window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
+                    window: Optional[int], page_size: int, H: int, G: int, hd: int,
+                    fused_merge: bool = False) -> torch.Tensor:
     """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
-    must cover the largest position of the batch; ``scratch`` is float32."""
+    must cover the largest position of the batch; ``scratch`` is float32.
+    ``fused_merge``: the tensor-core chunk kernel merges too (one launch
+    less); the caller vouches that ``scratch`` was zero when it was made and
+    has been used by nothing but calls of this function with it since (its
+    tail holds counters that every call leaves zero)."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
@@ -295,7 +300,11 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), page_size,
-            n, H, G, hd, _stream()), "attention_split_mma")
+            n, H, G, hd, _ptr(out) if fused_merge else ctypes.c_void_p(0), _rows_2d(out, "out"),
+            ctypes.c_longlong(scratch.numel()), _stream()),
+            "attention_split_mma")
+        if fused_merge:
+            return out
         _check(lib.kp_attention_merge(_ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
                                       SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), _stream()),
                "attention_merge")

@@ -110,8 +110,10 @@ class Attention(Part):
             need = K.attention_split_scratch(ctx.n_rows, H, hd, n_chunks)
             ws = self.env.shared.get("attn_scratch")
             if ws is None or ws.numel() < need:
-                ws = torch.empty(max(need, 1 << 16), dtype=torch.float32, device=q.device)
+                ws = torch.zeros(max(need, 1 << 16), dtype=torch.float32, device=q.device)
                 self.env.shared["attn_scratch"] = ws
+            # (the chunk kernel can merge too, fused_merge=True: measured slower in the decode step, 714 against
+            # 697 us, since the last CTA's fence, counter and dependent loads cost more than the launch they save)
             K.attention_split(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, ws, n_chunks,
                               self.scale, self.window, view.page_size, H, G, hd)
         elif K.attention_prefill_ok(q, hd) and ctx.tile_seg is not None:
