@@ -404,8 +404,7 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     // Tile width.  Many rows: by a small cost model: a CTA's main loop is bound by the bytes that it brings
     // into shared memory for each k-block (128 rows of A and BN rows of W), so a narrow tile costs about 2/3
     // of a wide one and does half the work; the number of rounds over the SMs decides between them.
-    // At most 128 rows (one row of tiles, W streamed once): the widest tile that still gives about a hundred
-    // tiles, so that enough CTAs pull on the memory.
+    // At most 128 rows (one row of tiles, W streamed once): see below.
     const long long m_tiles = (M + TC_BM - 1) / TC_BM;
     int bn;
     if (m_tiles > 1) {
@@ -413,9 +412,12 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
         const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + 147) / 148;
         bn = (epi == EPI_SWIGLU || rounds_wide * 3 <= rounds_narrow * 2) ? 256 : 128;
     } else {
+        // the narrowest tile that still runs in one round over the SMs (as many CTAs as possible pull on the
+        // memory, none waits for a second round); products too wide for that take the widest tile
         const int lowest = epi == EPI_SWIGLU ? 64 : 32;
+        auto tiles_at = [&](int w) { const int cols = epi == EPI_SWIGLU ? w / 2 : w; return (n_out + cols - 1) / cols; };
         bn = 256;
-        while (bn > lowest && (n_out + (epi == EPI_SWIGLU ? bn / 2 : bn) - 1) / (epi == EPI_SWIGLU ? bn / 2 : bn) < 96) bn /= 2;
+        while (bn > lowest && tiles_at(bn / 2) <= 148) bn /= 2;
     }
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;

@@ -399,12 +399,11 @@ USE_TC = True              # bfloat16 products of more than 64 rows (and some of
 def tc_pays_for_few_rows(M: int, N: int, swiglu: bool) -> bool:
     """Few-row products that the tcgen05 kernel runs faster than the weight-streaming
     kernels (measured on B200, K = 2048): the 65536-row head from 8 rows on (46 us at
-    every M against 48 us at 8 rows and 199 us at 64), and wide products without the
-    SwiGLU epilogue from 32 rows on (6144 rows: 16 us at every M against 17 us at 32
-    rows and 28 us at 64).  Narrow products (2048 rows: few tiles) stay with the
-    streaming kernels at every M <= 64."""
+    every M against 48 us at 8 rows and 199 us at 64), and wide products from 32 rows
+    on (6144 rows: 13 us at every M against 17 us at 32 rows and 28 us at 64).  Narrow
+    products (2048 rows: few tiles) stay with the streaming kernels at every M <= 64."""
     if swiglu:
-        return False
+        return N >= 8192 and M >= 32        # gate/up 11264 x 2048: 19.9 us against 22.9 at 32 rows, 19.8 against 32.1 at 64
     return (N >= 32768 and M >= 8) or (N >= 4096 and M >= 32)
 
 

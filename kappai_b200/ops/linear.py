@@ -105,9 +105,10 @@ def linear_swiglu(a: Operand, w_gate_up: torch.Tensor, bias: Optional[torch.Tens
     if _fusable(a, w_gate_up):
         return K.gemm_skinny_norm(a.x, a.weight, a.eps, a.rows, w_gate_up, act, bias, swiglu=True)
     a = as_tensor(a)
-    if K.skinny_ok(a, w_gate_up):
+    tc = K.tc_ok(a, w_gate_up)
+    if K.skinny_ok(a, w_gate_up) and not (tc and K.tc_pays_for_few_rows(a.shape[0], w_gate_up.shape[0], True)):
         return K.gemm_skinny(a, w_gate_up, act, bias, swiglu=True)
-    if K.tc_ok(a, w_gate_up):
+    if tc:
         return K.gemm_tc(a, w_gate_up, act, bias, swiglu=True)
     gu = linear(a, w_gate_up, bias)
     return K.swiglu(gu, act)
