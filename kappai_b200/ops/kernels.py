@@ -32,7 +32,15 @@ def dtype_code(dt: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dt}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream of the current device (asked of torch's C layer directly where it offers that:
+    this runs once per kernel launch)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
