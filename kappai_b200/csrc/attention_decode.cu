@@ -271,10 +271,12 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
                                                                 n_chunks, scale, window, page_size, H, G, hd)
     KP_DISPATCH_DTYPE(dtype, T, {
-        if (hd == 64 && R == 4) AD_LAUNCH(T, 64, 4);
-        else if (hd == 64) AD_LAUNCH(T, 64, 0);
-        else if (hd == 128) AD_LAUNCH(T, 128, 0);
-        else AD_LAUNCH(T, 0, 0);
+        cudaError_t e0;
+        if (hd == 64 && R == 4) e0 = AD_LAUNCH(T, 64, 4);
+        else if (hd == 64) e0 = AD_LAUNCH(T, 64, 0);
+        else if (hd == 128) e0 = AD_LAUNCH(T, 128, 0);
+        else e0 = AD_LAUNCH(T, 0, 0);
+        if (e0 != cudaSuccess) { cudaGetLastError(); return (int)e0; }      // the first launch that failed
         kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_chunks,
                                                         AD_CHUNK, window, H, hd);
     });

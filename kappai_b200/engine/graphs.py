@@ -13,6 +13,7 @@ model code runs under capture.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -170,8 +171,18 @@ class DecodeGraphs:
         torch.cuda.current_stream().synchronize()
         graph = torch.cuda.CUDAGraph()
         before = K.LAUNCHES[0]
-        with torch.cuda.graph(graph):
-            g.logits = r.model.forward(g.ctx, r.storage.views)
+        # Python's cycle collector must not run inside the capture: a dead cycle may hold captured graphs of
+        # an engine that is gone, and destroying a CUDA graph while a stream captures invalidates the capture.
+        # So the dead cycles are collected now and the collector rests until the capture has ended.
+        gc.collect()
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                g.logits = r.model.forward(g.ctx, r.storage.views)
+        finally:
+            if gc_was_on:
+                gc.enable()
         g.n_kernels = K.LAUNCHES[0] - before       # kernel launchers a replay stands for
         for t, s in zip(states, saved):
             t.copy_(s)
