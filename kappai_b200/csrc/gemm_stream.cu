@@ -119,11 +119,14 @@ struct StreamArgs {
 };
 
 // shared memory: [ring: n_stages x NW*8 rows x ST_ROW_BYTES][full[n_stages]][empty[n_stages]][red][scales]
-template <int MT, bool HALF, int EPI, bool NORM>
+// WIDE (more than 16 batch rows, no SwiGLU): a tile is 16 rows of W, so that an activation fragment, whose
+// loads weigh more than the weights' once there are several m-tiles, serves two n-tiles.
+template <int MT, bool HALF, int EPI, bool NORM, bool WIDE>
 __global__ void __launch_bounds__(ST_THREADS)
 gemm_stream_kernel(const StreamArgs p) {
-    constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int NW = (EPI == EPI_SWIGLU || WIDE) ? 2 : 1;
     constexpr int ROWS = NW * 8;
+    constexpr int TROWS = WIDE ? 16 : 8;                                 // output columns a tile
     constexpr int STAGE_BYTES = ROWS * ST_ROW_BYTES;
     extern __shared__ __align__(128) unsigned char smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,7 +137,7 @@ gemm_stream_kernel(const StreamArgs p) {
     float* red = reinterpret_cast<float*>(empty + S);                    // [ST_CONSUMERS][NW][MT][4][32]
     float* scales = red + ST_CONSUMERS * NW * MT * 128;                  // [16]
     const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
-    const int n_tiles = (n_out + 7) >> 3;
+    const int n_tiles = (n_out + TROWS - 1) / TROWS;
     const int n_chunks = K / ST_COLS;
 
     if (threadIdx.x == 0) {
@@ -149,10 +152,10 @@ gemm_stream_kernel(const StreamArgs p) {
         int it = 0;
         bool alive = true;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
-            const int n0 = tile * 8;
+            const int n0 = tile * TROWS;
             const bf16* src = nullptr;
             if (lane < ROWS) {
-                const int wrow = (lane < 8 ? 0 : p.ff) + min(n0 + (lane & 7), n_out - 1);
+                const int wrow = WIDE ? min(n0 + lane, n_out - 1) : (lane < 8 ? 0 : p.ff) + min(n0 + (lane & 7), n_out - 1);
                 src = p.W + (size_t)wrow * p.ldw;
             }
             for (int c = 0; c < n_chunks; c++, it++) {
@@ -220,7 +223,7 @@ gemm_stream_kernel(const StreamArgs p) {
     bool alive = true;
     const int nkb = K >> 5;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int n0 = tile * 8;
+        const int n0 = tile * TROWS;
         float acc[NW][MT][4];
 #pragma unroll
         for (int w = 0; w < NW; w++)
@@ -275,14 +278,14 @@ gemm_stream_kernel(const StreamArgs p) {
 #pragma unroll
                 for (int i = 0; i < 4; i++) red[(((warp * NW + w) * MT + mt) * 4 + i) * 32 + lane] = acc[w][mt][i];
         consumer_sync();
-        for (int e = threadIdx.x; e < MT * 4 * 32; e += ST_CONSUMERS * 32) {
-            const int l = e & 31, i = (e >> 5) & 3, mt = e >> 7;
+        for (int e = threadIdx.x; e < (WIDE ? 2 : 1) * MT * 4 * 32; e += ST_CONSUMERS * 32) {
+            const int l = e & 31, i = (e >> 5) & 3, mt = (e >> 7) % MT, wsel = WIDE ? e / (MT * 128) : 0;
             const int m = mt * 16 + (l >> 2) + ((i & 2) ? 8 : 0);
-            const int n = n0 + (l & 3) * 2 + (i & 1);
+            const int n = n0 + wsel * 8 + (l & 3) * 2 + (i & 1);
             if (m >= M || n >= n_out) continue;
             float v = 0.f;
 #pragma unroll
-            for (int w4 = 0; w4 < ST_CONSUMERS; w4++) v += red[(((w4 * NW + 0) * MT + mt) * 4 + i) * 32 + l];
+            for (int w4 = 0; w4 < ST_CONSUMERS; w4++) v += red[(((w4 * NW + wsel) * MT + mt) * 4 + i) * 32 + l];
             if (p.bias) v += p.bias[n];
             const size_t o = (size_t)m * p.ldc + n;
             if (EPI == EPI_SWIGLU) {
@@ -335,9 +338,12 @@ static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const S
 
 template <int MT, bool HALF, bool NORM>
 static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
-    const int NW = epi == EPI_SWIGLU ? 2 : 1;
+    // tiles of 16 rows of W from three m-tiles on (see the kernel; measured at 64 batch rows: 2048 x 5632 15.5 us
+    // against 23.7, 2048 x 2048 8.0 against 12.2; at 32 rows the narrow tile is as fast or faster)
+    constexpr bool WIDE = MT >= 3;
+    const int NW = (epi == EPI_SWIGLU || WIDE) ? 2 : 1;
     const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
-    const int n_tiles = (n_out + 7) / 8;
+    const int n_tiles = (n_out + (WIDE && epi != EPI_SWIGLU ? 15 : 7)) / (WIDE && epi != EPI_SWIGLU ? 16 : 8);
     // Measured on B200 (8 and 16 rows): three CTAs an SM with a 64 KB ring is best or tied for products with
     // many tiles (6144 x 2048: 6.9 us against 8.1 with 53 KB); a product with at most two tiles an SM (2048
     // rows) does better with two CTAs an SM and more of its long rows in flight (2048 x 5632: 8.3 against 10.3).
@@ -351,10 +357,10 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     dim3 grid(g);
     const size_t sm = smem_bytes(NW, MT, a.n_stages);
     switch (epi) {
-        case EPI_STORE: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE, NORM>, grid, sm, s, a);
-        case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, NORM>, grid, sm, s, a);
-        case EPI_ACCUM_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_ACCUM_F32, NORM>, grid, sm, s, a);
-        case EPI_SWIGLU: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_SWIGLU, NORM>, grid, sm, s, a);
+        case EPI_STORE: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE, NORM, WIDE>, grid, sm, s, a);
+        case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, NORM, WIDE>, grid, sm, s, a);
+        case EPI_ACCUM_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_ACCUM_F32, NORM, WIDE>, grid, sm, s, a);
+        case EPI_SWIGLU: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_SWIGLU, NORM, false>, grid, sm, s, a);
         default: return KP_ERR_BAD_ARG;
     }
 }
