@@ -1,26 +1,30 @@
 // C[M,N] = A[M,K] * W[N,K]^T (bfloat16 in, float32 accumulation) on the 5th-generation tensor cores:
 // tcgen05.mma with the accumulator in tensor memory, operands brought to shared memory by TMA.
-// The product of prompt portions (M > 64 rows).
+// The product of prompt portions, and of few-row steps where it was measured faster than weight streaming.
 //
-// One CTA computes a 128 x BN tile of C (BN = 128 or 256).  Roles by warp:
+// Persistent CTAs, one an SM; a CTA computes tiles of 128 x BN of C (tile b, b + grid, ...; m runs fastest so
+// that the CTAs that run together share W tiles in L2).  BN is 256 or 128 for products of many rows (chosen by
+// a cost model of rounds over the SMs), and for at most 128 rows the narrowest of 256..32 that still runs in
+// one round, so that as many CTAs as possible pull on the memory.  Roles by warp:
 //   warp 0   : TMA producer.  For every k-block of 64 it waits for a free stage, arms the stage's "full"
-//              mbarrier with the byte count and issues the tiled loads of the A box (128 rows x 64) and the
-//              W box (BN rows x 64), both with the 128-byte swizzle, no multicast.
-//   warp 1   : allocates BN columns of tensor memory, then one lane issues the MMAs: four tcgen05.mma
-//              (128 x BN x 16) per stage, descriptors advanced by 32 bytes inside the swizzled rows;
-//              tcgen05.commit frees the stage ("empty" mbarrier) and, after the last k-block, signals
-//              "accumulator ready".
-//   the rest: epilogue, two warps for each quarter of the 128 lanes of tensor memory (a warp may only read
-//              the lanes 32 * (warp % 4) ...), taking the 32-column pieces in turn: more loads and stores in
-//              flight.  Each reads its lanes with tcgen05.ld (32 columns at a
-//              time), applies bias / residual accumulation / SwiGLU and writes its rows of C.
+//              mbarrier with the byte count and issues the tiled loads of the A box (128 rows x 64, or only
+//              the rows there are, rounded up to 8, when M < 128) and the W box (BN rows x 64), both with
+//              the 128-byte swizzle, no multicast.  The ring has as many stages as fit shared memory.
+//   warp 1   : allocates 2 x BN columns of tensor memory (two accumulators: the epilogue of a tile runs under
+//              the main loop of the next), then one lane issues the MMAs: four tcgen05.mma (128 x BN x 16) per
+//              stage, descriptors advanced by 32 bytes inside the swizzled rows; tcgen05.commit frees the
+//              stage ("empty" mbarrier) and, after the last k-block, signals "accumulator full".
+//   the rest : epilogue, two warps for each quarter of the 128 lanes of tensor memory (a warp may only read
+//              the lanes 32 * (warp % 4) ...), taking the 32-column pieces in turn so that more loads and
+//              stores are in flight.  Each reads its lanes with tcgen05.ld (32 columns at a time), applies
+//              bias / residual accumulation / SwiGLU, writes its rows of C and hands the accumulator back.
 // Rows of A beyond M and rows of W beyond N are zero-filled by TMA (out-of-bounds fill) and masked at the
 // store; K needs no padding (the tail of the last k-block is zero-filled too) but K % 8 == 0 (16-byte rows).
 // Each output row sums its k-blocks in order, so a row's result does not depend on M.
 //
-// SwiGLU epilogue: W holds gate rows then up rows (ff apart).  The CTA's W tile is 128 gate rows and the
-// matching 128 up rows (two TMA boxes into one 256-row tile), so accumulator columns c and 128 + c are the
-// gate and up of one output column: the epilogue writes silu(gate) * up.
+// SwiGLU epilogue: W holds gate rows then up rows (ff apart).  The CTA's W tile is BN/2 gate rows and the
+// matching BN/2 up rows (two TMA boxes into one tile), so accumulator columns c and BN/2 + c are the gate and
+// up of one output column: the epilogue writes silu(gate) * up.
 //
 // Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
 // stops issuing work, still frees its tensor memory and returns.
