@@ -25,7 +25,7 @@
 // the fewest; a CTA takes the i-th and the i-th last, so every CTA has about the same work.
 // Every mbarrier wait is bounded; a wait that gives up sets the status word, and the CTA frees its tensor
 // memory and returns.
-#include "tma.cuh"
+#include "tcgen05.cuh"
 
 #define AT_BM 128
 #define AT_BN 128
@@ -34,55 +34,6 @@
 #define AT_TILE_BYTES (128 * 64 * 2)         // a 128 x 64 bf16 tile: 16 KB
 
 __device__ int g_attn_tc_status = 0;
-
-__device__ __forceinline__ void at_mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(kp_smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void at_tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(kp_smem_u32(dst_smem)), "r"(ncols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void at_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
-}
-__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void at_umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void at_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(kp_smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void at_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-// Descriptor of a tile whose rows are 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.  For a
-// K-major operand the rows are the M/N index and a step of 16 along K is +32 bytes; for the MN-major V tile
-// the rows are the K index (keys) and a step of 16 keys is +2048 bytes.
-__device__ __forceinline__ uint64_t at_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// float32 accumulator, bfloat16 operands; b_mn: the B operand is MN-major (bit 16)
-__host__ __device__ constexpr uint32_t at_idesc(int M, int N, bool b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(N >> 3) << 17) |
-           ((uint32_t)(M >> 4) << 24);
-}
 
 __device__ __forceinline__ float at_exp2(float x) {
     float y;
@@ -155,10 +106,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // V starts zeroed: a part of a tile that is never loaded then holds something finite
     for (int i = threadIdx.x; i < AT_TILE_BYTES / 16; i += AT_THREADS) reinterpret_cast<uint4*>(Vs)[i] = make_uint4(0, 0, 0, 0);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    if (warp == 1) at_tmem_alloc(tmem_slot, 256);
-    at_fence_before();
+    if (warp == 1) kp_tmem_alloc(tmem_slot, 256);
+    kp_tc_fence_before();
     __syncthreads();
-    at_fence_after();
+    kp_tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
     kp_pdl_begin();
@@ -204,9 +155,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = at_idesc(AT_BM, AT_BN, false);
-            constexpr uint32_t idesc_pv = at_idesc(AT_BM, AT_HD, true);
-            const uint64_t qdesc = at_desc(kp_smem_u32(Qs));
+            constexpr uint32_t idesc_s = kp_umma_idesc(AT_BM, AT_BN, false);
+            constexpr uint32_t idesc_pv = kp_umma_idesc(AT_BM, AT_HD, true);
+            const uint64_t qdesc = kp_umma_desc(kp_smem_u32(Qs));
             bool ok = true;
             int base = 0;                                                // key tiles of the items before
             for (int idx = 0; idx < n_items && ok; idx++) {
@@ -218,12 +169,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     if (!kp_mbar_wait_bounded(&k_full[kb], (i >> 1) & 1)) return false;
                     // S is free once the rows have read the tile before (they say so with p_full)
                     if (i > 0 && !kp_mbar_wait_bounded(p_full, (i - 1) & 1)) return false;
-                    at_fence_after();
-                    const uint64_t kdesc = at_desc(kp_smem_u32(Ks + kb * AT_TILE_BYTES));
+                    kp_tc_fence_after();
+                    const uint64_t kdesc = kp_umma_desc(kp_smem_u32(Ks + kb * AT_TILE_BYTES));
 #pragma unroll
-                    for (int k = 0; k < AT_HD / 16; k++) at_umma(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k ? 1u : 0u);
-                    at_commit(s_full);
-                    at_commit(&k_empty[kb]);
+                    for (int k = 0; k < AT_HD / 16; k++) kp_umma_bf16(tmem_s, qdesc + 2 * k, kdesc + 2 * k, idesc_s, k ? 1u : 0u);
+                    kp_umma_commit(s_full);
+                    kp_umma_commit(&k_empty[kb]);
                     return true;
                 };
                 if (ok) ok = issue_s(base);
@@ -231,14 +182,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                     const int i = base + j;
                     // PV of tile i: P is in shared memory (p_full), V has come
                     if (!kp_mbar_wait_bounded(p_full, i & 1) || !kp_mbar_wait_bounded(v_full, i & 1)) { ok = false; break; }
-                    at_fence_after();
+                    kp_tc_fence_after();
                     const uint32_t pa = kp_smem_u32(Ps), va = kp_smem_u32(Vs);
 #pragma unroll
                     for (int kk = 0; kk < AT_BN / 16; kk++)
-                        at_umma(tmem_pv, at_desc(pa + (kk >> 2) * AT_TILE_BYTES) + 2 * (kk & 3), at_desc(va + kk * 2048),
+                        kp_umma_bf16(tmem_pv, kp_umma_desc(pa + (kk >> 2) * AT_TILE_BYTES) + 2 * (kk & 3), kp_umma_desc(va + kk * 2048),
                                 idesc_pv, kk ? 1u : 0u);
-                    at_commit(pv_full);
-                    at_commit(v_empty);
+                    kp_umma_commit(pv_full);
+                    kp_umma_commit(v_empty);
                     if (j + 1 < n_kt) ok = issue_s(i + 1);
                 }
                 base += n_kt;
@@ -265,7 +216,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             float m = -INFINITY, l = 0.f;
             for (int kt = it.kt_lo; kt <= it.kt_hi && ok; kt++, i++) {
                 if (!kp_mbar_wait_bounded(s_full, i & 1) || *abort_flag) { ok = false; break; }
-                at_fence_after();
+                kp_tc_fence_after();
                 // Most tiles lie wholly inside every row's keys; only the tile on the diagonal, a window's edge
                 // and rows past the end of the segment need the mask.  Scores are taken in base 2:
                 // exp(x) = 2^(x log2 e).
@@ -275,7 +226,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll 1
                 for (int c = 0; c < AT_BN; c += 32) {
                     uint32_t s[32];
-                    at_tmem_ld32(tmem_s + lane_off + c, s);
+                    kp_tmem_ld32(tmem_s + lane_off + c, s);
                     if (masked) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
@@ -295,7 +246,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 #pragma unroll 1
                 for (int c = 0; c < AT_BN; c += 32) {
                     uint32_t s[32];
-                    at_tmem_ld32(tmem_s + lane_off + c, s);
+                    kp_tmem_ld32(tmem_s + lane_off + c, s);
                     unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
 #pragma unroll
                     for (int j8 = 0; j8 < 4; j8++) {
@@ -323,20 +274,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 }
                 l = l * corr + lsum;
                 m = m_new;
-                at_fence_before();                                           // the reads of S are done
+                kp_tc_fence_before();                                           // the reads of S are done
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-                at_mbar_arrive(p_full);
+                kp_mbar_arrive(p_full);
                 // O = O * corr + P V
                 if (!kp_mbar_wait_bounded(pv_full, i & 1)) { ok = false; break; }
-                at_fence_after();
+                kp_tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < AT_HD; c += 32) {
                     uint32_t v[32];
-                    at_tmem_ld32(tmem_pv + lane_off + c, v);
+                    kp_tmem_ld32(tmem_pv + lane_off + c, v);
 #pragma unroll
                     for (int j = 0; j < 32; j++) o[c + j] = o[c + j] * corr + __uint_as_float(v[j]);
                 }
-                at_fence_before();
+                kp_tc_fence_before();
             }
             if (ok && live) {
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -353,9 +304,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         if (!ok && lane == 0) atomicExch(&g_attn_tc_status, 1);
     }
-    at_fence_before();
+    kp_tc_fence_before();
     __syncthreads();
-    if (warp == 1) at_tmem_dealloc(tmem_base, 256);
+    if (warp == 1) kp_tmem_dealloc(tmem_base, 256);
 }
 
 extern "C" {

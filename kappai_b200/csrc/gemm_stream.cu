@@ -27,7 +27,7 @@
 // Limits: K a multiple of 512.  Other shapes take the register-streaming kernel.
 #include <type_traits>
 
-#include "common.cuh"
+#include "tma.cuh"
 
 #define EPI_STORE 0
 #define EPI_STORE_F32 1
@@ -40,46 +40,12 @@
 #define ST_ROW_BYTES (ST_COLS * 2 + 64)      // a stage row in shared memory: 1 KB of data, pitch = 64 mod 128
 #define ST_RING_BYTES (64 * 1024)            // the ring with three CTAs an SM: 7 stages of 8 rows, 3 of 2 x 8
 #define ST_RING_BYTES_FEW (88 * 1024)        // with two CTAs an SM (products with few tiles): 10 stages of 8 rows
-#define ST_WAIT_NS 1000000000ull             // one second: far beyond any legitimate wait
 
 __device__ int g_stream_status = 0;          // 0 ok; 1: a bounded wait gave up
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// false if the barrier did not flip within ST_WAIT_NS
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = now_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (now_ns() - t0 > ST_WAIT_NS) return false;
-    }
-}
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+                 ::"r"(kp_smem_u32(dst)), "l"(src), "r"(bytes), "r"(kp_smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS * 32) : "memory"); }
 
@@ -141,8 +107,8 @@ gemm_stream_kernel(const StreamArgs p) {
     const int n_chunks = K / ST_COLS;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < S; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], ST_CONSUMERS); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int s = 0; s < S; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], ST_CONSUMERS); }
+        kp_mbar_init_fence();
     }
     __syncthreads();
 
@@ -162,8 +128,8 @@ gemm_stream_kernel(const StreamArgs p) {
                 const int s = it % S;
                 int ok = 1;
                 if (lane == 0) {
-                    ok = mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1) ? 1 : 0;
-                    if (ok) mbar_expect_tx(&full[s], ROWS * ST_COLS * 2);
+                    ok = kp_mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1) ? 1 : 0;
+                    if (ok) kp_mbar_expect_tx(&full[s], ROWS * ST_COLS * 2);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { alive = false; break; }
@@ -241,7 +207,7 @@ gemm_stream_kernel(const StreamArgs p) {
         auto run_stage = [&](int c, auto slot0) {
             constexpr int SLOT0 = decltype(slot0)::value;
             const int s = it % S;
-            if (alive && !mbar_wait_bounded(&full[s], (it / S) & 1)) alive = false;
+            if (alive && !kp_mbar_wait_bounded(&full[s], (it / S) & 1)) alive = false;
             const unsigned char* stage = ring + (size_t)s * STAGE_BYTES + 16 * t;
 #pragma unroll
             for (int j = 0; j < 2; j++) {
@@ -263,7 +229,7 @@ gemm_stream_kernel(const StreamArgs p) {
                 if (kb + PF * ST_CONSUMERS < nkb) load_acts(lo[sl], hi[sl], kb + PF * ST_CONSUMERS);
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);                       // this warp has read the stage
+            if (lane == 0) kp_mbar_arrive(&empty[s]);                       // this warp has read the stage
             it++;
         };
         for (int c = 0; c < n_chunks; c += PF / 2) {

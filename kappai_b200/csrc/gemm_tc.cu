@@ -28,9 +28,7 @@
 //
 // Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
 // stops issuing work, still frees its tensor memory and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #define EPI_STORE 0
 #define EPI_STORE_F32 1
@@ -41,92 +39,8 @@
 #define TC_BK 64
 #define TC_EPI_PER_Q 2                       // epilogue warps for each quarter of the tensor-memory lanes
 #define TC_THREADS (64 + TC_EPI_PER_Q * 128) // the producer warp, the MMA warp and the epilogue warps
-#define TC_WAIT_NS 1000000000ull            // one second: far beyond any legitimate wait
 
 __device__ int g_tc_status = 0;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// false if the barrier did not flip within TC_WAIT_NS
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = now_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (now_ns() - t0 > TC_WAIT_NS) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-                 " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major operand tile whose rows are 128 bytes (64 bf16), stored with
-// the 128-byte swizzle in atoms of 8 rows (1024 bytes): start address, leading offset 1 (16 bytes; unused by
-// swizzled K-major layouts), stride offset 1024 bytes between 8-row groups, version 1, layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, N and M of the MMA.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
 
 struct TcArgs {
     const float* bias;
@@ -172,15 +86,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     // set-up that depends on no earlier kernel comes before the wait on it
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b2 = 0; b2 < 2; b2++) { mbar_init(&acc_full[b2], 1); mbar_init(&acc_empty[b2], 4 * TC_EPI_PER_Q); }
+        for (int s = 0; s < STAGES; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], 1); }
+        for (int b2 = 0; b2 < 2; b2++) { kp_mbar_init(&acc_full[b2], 1); kp_mbar_init(&acc_empty[b2], 4 * TC_EPI_PER_Q); }
         *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        kp_mbar_init_fence();
     }
-    if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);                         // two accumulators of BN columns
-    tc_fence_before();
+    if (warp == 1) kp_tmem_alloc(tmem_slot, 2 * BN);                         // two accumulators of BN columns
+    kp_tc_fence_before();
     __syncthreads();
-    tc_fence_after();
+    kp_tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     kp_pdl_begin();
 
@@ -192,16 +106,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
                 for (int kb = 0; kb < n_kb; kb++) {
-                    if (*abort_flag || !mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
+                    if (*abort_flag || !kp_mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
                     unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
                     unsigned char* b_dst = a_dst + A_BYTES;
-                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
+                    kp_mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    kp_tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
                     if (EPI == EPI_SWIGLU) {
-                        tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
-                        tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
+                        kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
+                        kp_tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
                     } else {
-                        tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+                        kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -209,27 +123,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+            constexpr uint32_t idesc = kp_umma_idesc(TC_BM, BN);
             int s = 0, ti = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
                 const int b2 = ti & 1;                                    // accumulator of this tile
-                if (*abort_flag || !mbar_wait_bounded(&acc_empty[b2], ((ti >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
-                tc_fence_after();
+                if (*abort_flag || !kp_mbar_wait_bounded(&acc_empty[b2], ((ti >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
+                kp_tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b2 * BN);
                 for (int kb = 0; kb < n_kb; kb++) {
-                    if (!mbar_wait_bounded(&full[s], ph)) { *abort_flag = 1; ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
-                    const uint64_t adesc = make_desc(a_addr), bdesc = make_desc(a_addr + A_BYTES);
+                    if (!kp_mbar_wait_bounded(&full[s], ph)) { *abort_flag = 1; ok = false; break; }
+                    kp_tc_fence_after();
+                    const uint32_t a_addr = kp_smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
+                    const uint64_t adesc = kp_umma_desc(a_addr), bdesc = kp_umma_desc(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; k++)      // 32 bytes along K inside the swizzled row: +2 in the address field
-                        umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
-                    umma_commit(&empty[s]);                    // the stage is free when these MMAs have read it
+                        kp_umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    kp_umma_commit(&empty[s]);                    // the stage is free when these MMAs have read it
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
-                if (ok) umma_commit(&acc_full[b2]);            // arrives when every MMA of the tile has completed
+                if (ok) kp_umma_commit(&acc_full[b2]);            // arrives when every MMA of the tile has completed
             }
         }
     } else {
@@ -242,16 +156,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
             const int b2 = ti & 1;
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
-            if (!mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
-            tc_fence_after();
+            if (!kp_mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
+            kp_tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
                 uint32_t r[32];
-                tmem_ld32(lane_base + c, r);
+                kp_tmem_ld32(lane_base + c, r);
                 uint32_t u[32];
-                if (EPI == EPI_SWIGLU) tmem_ld32(lane_base + BN / 2 + c, u);
+                if (EPI == EPI_SWIGLU) kp_tmem_ld32(lane_base + BN / 2 + c, u);
                 if (m < p.M) {
                     const int n_base = n0 + c;
                     const int n_lim = n_out;
@@ -312,48 +226,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
             // this warp has read the accumulator out: hand it back to the MMA warp
-            tc_fence_before();
+            kp_tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[b2]);
+            if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
         }
         if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
     }
-    tc_fence_before();
+    kp_tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+    if (warp == 1) kp_tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// rows x K bf16, row stride ld elements; box 64 (K) x box_rows, 128-byte swizzle, zero fill out of bounds
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return KP_ERR_UNSUPPORTED;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : KP_ERR_BAD_ARG;
-}
-
 static int g_tc_smem_kb = 208;              // shared memory for the ring (tunable for measurements)
 
 template <int BN, int EPI>
@@ -425,9 +309,9 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     }
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;
-    int st = make_map(&ta, A, M, K, lda, a.a_rows);
+    int st = kp_make_map_bf16_2d(&ta, A, (unsigned long long)M, K, lda, TC_BK, a.a_rows);
     if (st) return st;
-    st = make_map(&tw, W, N, K, ldw, epi == EPI_SWIGLU ? bn / 2 : bn);
+    st = kp_make_map_bf16_2d(&tw, W, (unsigned long long)N, K, ldw, TC_BK, epi == EPI_SWIGLU ? bn / 2 : bn);
     if (st) return st;
     cudaStream_t s = (cudaStream_t)stream;
 #define TC_PICK(EPI)                                               \

@@ -19,6 +19,9 @@ __device__ __forceinline__ void kp_mbar_init_fence() { asm volatile("fence.mbarr
 __device__ __forceinline__ void kp_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(kp_smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void kp_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(kp_smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool kp_mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
