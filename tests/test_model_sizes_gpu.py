@@ -1,0 +1,87 @@
+"""Whole models at sizes that the tiny configurations do not reach, so that the kernels chosen for real
+widths run inside the model and are checked against the plain implementation: head size 64 with a few
+thousand tokens (tcgen05 attention for prompt portions, the TMA-fed split kernel for decoded tokens), and
+width 512 with decode batches of up to 64 requests (the weight-streaming products in all their forms)."""
+import numpy as np
+import pytest
+
+from tolerances import tol_for
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {'architectures': ['Lfm2ForCausalLM'], 'vocab_size': 384, 'hidden_size': 256, 'num_hidden_layers': 3,
+          'num_attention_heads': 4, 'num_key_value_heads': 2, 'layer_types': ['conv', 'full_attention', 'full_attention'],
+          'max_position_embeddings': 8192, 'norm_eps': 1e-05, 'conv_L_cache': 3, 'conv_bias': False,
+          'block_ff_dim': 320, 'block_auto_adjust_ff_dim': False, 'rope_theta': 1000000.0, 'tie_embedding': True}
+
+
+@pytest.fixture(scope="module")
+def model(tmp_path_factory):
+    from kappai_b200 import write_random_model
+    from plain_lfm2 import PlainLfm2
+    d = str(tmp_path_factory.mktemp("long") / "m")
+    write_random_model(CONFIG, d, 11)
+    return d, PlainLfm2(d)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompt_in_odd_portions_then_decoding(dtype, model):
+    from kappai_b200 import ModelRunner, StepEntry
+    from kappai_b200.ops import kernels as K
+    d, plain = model
+    rng = np.random.default_rng(3)
+    T, n_dec = 3000, 6
+    toks = rng.integers(0, CONFIG["vocab_size"], T + n_dec).tolist()
+    ref = plain.logits(toks)
+    r = ModelRunner(d, dtype=dtype, max_tokens=4096, max_requests=2, page_size=64, max_model_len=4096)
+    cuts = [0, 129, 700, 701, 1500, 2047, 2048, 2900, T]                 # portions of 129, 571, 1, 799, ... tokens
+    tol = tol_for(dtype, ref)
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        want = sorted({0, (b - a) // 2, b - a - 1})
+        lg = r.step([StepEntry("a", toks[a:b], want)]).float().cpu().numpy()
+        for j, w in enumerate(want):
+            assert np.abs(lg[j] - ref[a + w]).max() <= tol, (dtype, a, b, w)
+    for i in range(n_dec):
+        lg = r.step([StepEntry("a", [toks[T + i]], [0])]).float().cpu().numpy()
+        assert np.abs(lg[0] - ref[T + i]).max() <= tol, (dtype, "decode", i)
+    assert K.tc_status() == 0 and K.stream_status() == 0 and K.attention_tc_status() == 0
+
+
+WIDE_CONFIG = {'architectures': ['Lfm2ForCausalLM'], 'vocab_size': 640, 'hidden_size': 512, 'num_hidden_layers': 2,
+               'num_attention_heads': 8, 'num_key_value_heads': 2, 'layer_types': ['conv', 'full_attention'],
+               'max_position_embeddings': 1024, 'norm_eps': 1e-06, 'conv_L_cache': 3, 'conv_bias': False,
+               'block_ff_dim': 1024, 'block_auto_adjust_ff_dim': False, 'rope_theta': 10000.0, 'tie_embedding': False}
+
+
+@pytest.fixture(scope="module")
+def wide_model(tmp_path_factory):
+    from kappai_b200 import write_random_model
+    from plain_lfm2 import PlainLfm2
+    d = str(tmp_path_factory.mktemp("wide") / "m")
+    write_random_model(WIDE_CONFIG, d, 12)
+    return d, PlainLfm2(d)
+
+
+@pytest.mark.parametrize("n_req", [3, 20, 40, 64])
+def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model):
+    """Width 512 (a multiple of the bulk-copy kernel's 512-column chunks): decode steps of 3, 20, 40 and 64
+    requests run the weight-streaming products in all their forms (half tile, two, three and four m-tiles,
+    16-row weight tiles) inside the model, from captured graphs; every request's logits against the plain model."""
+    from kappai_b200 import ModelRunner, StepEntry
+    from kappai_b200.ops import kernels as K
+    d, plain = wide_model
+    rng = np.random.default_rng(100 + n_req)
+    V = WIDE_CONFIG["vocab_size"]
+    lens = rng.integers(3, 70, n_req).tolist()
+    seqs = [rng.integers(0, V, L + 3).tolist() for L in lens]
+    refs = [plain.logits(s) for s in seqs]
+    r = ModelRunner(d, dtype="bfloat16", max_tokens=n_req * 128, max_requests=n_req, page_size=64, max_model_len=1024)
+    for i, (s, L) in enumerate(zip(seqs, lens)):
+        r.step([StepEntry(i, s[:L], [])])
+    for step in range(3):
+        entries = [StepEntry(i, [s[L + step]], [0]) for i, (s, L) in enumerate(zip(seqs, lens))]
+        lg = r.step(entries).float().cpu().numpy()
+        for i, L in enumerate(lens):
+            assert np.abs(lg[i] - refs[i][L + step]).max() <= tol_for("bfloat16", refs[i]), (n_req, step, i)
+    assert r.graphs.n_replays >= 2
+    assert K.tc_status() == 0 and K.stream_status() == 0
