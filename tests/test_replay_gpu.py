@@ -8,8 +8,10 @@ from tolerances import tol_for
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [21, 33, 49, 127, 2, 70], "B": [25, 33, 88, 154, 250, 3], "C": [40, 130, 77, 300]}
-PROMPTS = {"A": [5, 17, 33, 100, 1, 40], "B": [1, 9, 64, 130, 200, 2], "C": [8, 100, 70, 260]}
+LENGTHS = {"A": [21, 33, 49, 127, 2, 70], "B": [25, 33, 88, 154, 250, 3], "C": [40, 130, 77, 300],
+           "D": [300, 700, 130, 520]}
+PROMPTS = {"A": [5, 17, 33, 100, 1, 40], "B": [1, 9, 64, 130, 200, 2], "C": [8, 100, 70, 260],
+           "D": [260, 600, 100, 500]}
 
 
 def requests_of(name, vocab, seed):
@@ -20,7 +22,7 @@ def requests_of(name, vocab, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("A", None), ("B", None), ("B", 16), ("C", 32)])
+@pytest.mark.parametrize("name,page_size", [("A", None), ("B", None), ("B", 16), ("C", 32), ("D", None), ("D", 16)])
 def test_all_cuts_agree_with_plain(name, page_size, dtype, model_dirs, plain_models, tmp_path):
     plain = plain_models[name]
     reqs, prompt_len = requests_of(name, plain.cfg["vocab_size"], seed=11)

@@ -1,4 +1,4 @@
-"""Two tiny LFM2 configurations that differ in every size and option, and
+"""Tiny LFM2 configurations that differ in every size and option, and
 helpers that write them as model folders with random weights."""
 import os
 import tempfile
@@ -30,7 +30,18 @@ TINY_C = dict(
     block_ff_dim=200, block_auto_adjust_ff_dim=False, rope_theta=50000.0, tie_embedding=True)
 TINY_C_SEED = 7
 
-CONFIGS = {"A": (TINY_A, TINY_A_SEED), "B": (TINY_B, TINY_B_SEED), "C": (TINY_C, TINY_C_SEED)}
+# a fourth shape with head size 64, where the tensor-core attention kernels run (tcgen05 for prompt portions,
+# the TMA-fed split kernel for decoded tokens); two query heads share the one kv head
+TINY_D = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=300, hidden_size=128, num_hidden_layers=3,
+    num_attention_heads=2, num_key_value_heads=1,
+    layer_types=["full_attention", "conv", "full_attention"],
+    max_position_embeddings=1024, norm_eps=1e-5, conv_L_cache=3, conv_bias=True,
+    block_ff_dim=256, block_auto_adjust_ff_dim=False, rope_theta=10000.0, tie_embedding=True)
+TINY_D_SEED = 9
+
+CONFIGS = {"A": (TINY_A, TINY_A_SEED), "B": (TINY_B, TINY_B_SEED), "C": (TINY_C, TINY_C_SEED),
+           "D": (TINY_D, TINY_D_SEED)}
 
 
 def make_model_dir(name, root=None):
