@@ -246,7 +246,10 @@ def run_prefill(runner, T, warmup, rng):
 
 
 def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
-    """Decode through Engine.step: host tokens in, host tokens out, every step."""
+    """Decode through Engine.step, the loop a user of the Python entry point runs: every step copies its
+    tables (positions, slots, block tables) from pinned host memory and brings the sampled tokens back to the
+    host, where the scheduler records them.  (The engine launches the next decode step before it waits for the
+    last one's tokens; the token ids themselves go from the sampler to the next step on the device.)"""
     import torch
     from kappai_b200 import Engine, EngineArgs, SamplingParams
 
@@ -269,7 +272,7 @@ def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
         n += len(eng.step())
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    h2d = eng.runner.last_h2d_bytes + batch * 5 * 4 + batch * 4
+    h2d = eng.runner.last_h2d_bytes               # the step's table buffer; greedy sampling copies nothing more
     d2h = batch * 4
     eng.shutdown()
     return n / dt, h2d, d2h

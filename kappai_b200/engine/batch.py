@@ -73,9 +73,16 @@ class StepContext:
     big_tile_seg: Optional[torch.Tensor] = None
     big_tile_row0: Optional[torch.Tensor] = None
     n_big_tiles: int = 0
+    # A step that mixes decoded tokens with prompt portions: the leading segments of at most SHORT_SEG rows
+    # (the scheduler puts decodes first) can go to a kernel made for single rows with long caches and the rest
+    # to a tiled one.  n_short_rows / n_short_tiles: rows and ROW_TILE tiles of that lead (0 if the step is not
+    # mixed in this way); the big tiles then list the other segments only.
+    n_short_rows: int = 0
+    n_short_tiles: int = 0
 
 
 BIG_TILE = 128                     # rows of the larger tiles
+SHORT_SEG = 4                      # rows up to which a segment counts as short (decoded tokens)
 ROW_TILE = 64                      # rows of one segment that a tiled kernel (prefill attention) takes at a time
 
 
@@ -134,8 +141,14 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), ROW_TILE):
             tile_seg.append(i)
             tile_row0.append(r0)
+    n_short_seg = 0
+    while n_short_seg < n_seg and len(segments[n_short_seg].tokens) <= SHORT_SEG:
+        n_short_seg += 1
+    if n_short_seg == n_seg or all(len(s.tokens) > SHORT_SEG for s in segments):
+        n_short_seg = 0                                   # all short or none: one kernel takes the whole step
+    n_short_rows = int(cu_rows[n_short_seg])
     big = []
-    for i in range(n_seg):
+    for i in range(n_short_seg, n_seg):
         for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), BIG_TILE):
             last_pos = int(seg_pos[i]) + min(r0 + BIG_TILE, int(cu_rows[i + 1])) - int(cu_rows[i]) - 1
             big.append((-last_pos, i, r0))                # the further on, the more keys
@@ -187,7 +200,8 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         max_context=max(s.pos_start + len(s.tokens) for s in segments),
         decode_only=all(len(s.tokens) == 1 for s in segments),
         tile_seg=piece(7), tile_row0=piece(8), n_tiles=len(tile_seg),
-        big_tile_seg=piece(9), big_tile_row0=piece(10), n_big_tiles=len(big))
+        big_tile_seg=piece(9), big_tile_row0=piece(10), n_big_tiles=len(big),
+        n_short_rows=n_short_rows, n_short_tiles=n_short_seg)
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
     ctx.h2d_bytes = flat.numel() * 4
     return ctx

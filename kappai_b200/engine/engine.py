@@ -19,7 +19,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.rng import resolve_seed
 from ..sampling.sampler import sample
 from .runner import ModelRunner, StepEntry
-from .scheduler import Request, ScheduledEntry, Scheduler
+from .scheduler import RUNNING, Request, ScheduledEntry, Scheduler
 
 
 @dataclass
@@ -36,6 +36,7 @@ class EngineArgs:
     page_size: int = 64
     kv_tokens: int = 0                 # tokens the page pools hold (0: max_batch * ctx_size, capped by memory)
     device: str = "cuda:0"
+    look_ahead: bool = True            # launch the next decode step before the last one's tokens are read
 
 
 @dataclass
@@ -48,7 +49,28 @@ class StepStats:
     first_token_seconds: Optional[float] = None
 
 
+@dataclass
+class _Launched:
+    """A step that runs (or has run) on the device and whose sampled tokens are on their way to the host."""
+
+    plan: List[ScheduledEntry]
+    got: List[Request]                         # the requests that sample in it, in the order of ``tokens``
+    tokens: Optional[torch.Tensor]             # their new tokens on the device (int32)
+    host: Optional[torch.Tensor]               # the pinned buffer the tokens are copied to
+    done: torch.cuda.Event                     # recorded behind that copy
+
+
 class Engine:
+    """``step`` keeps the device busy while the host does its bookkeeping: once a step's sampled tokens
+    are on their way to the host, and the next step can only be "every running request decodes one more
+    token", that next step is launched at once, fed by the sampled tokens where they lie on the device; only
+    then does the host wait for the first step's tokens, record them and return them.  The next call finds its
+    step already running.  A request that ended meanwhile (end-of-sequence token, abort) had one row too many
+    computed; the row is dropped, and rows of a batch do not depend on one another.  A step is launched ahead
+    only if no request waits, every running request decodes, none reaches its length limits with the token
+    under way, none has a repeat penalty (which reads the token history on the host), and pages for the next
+    token are there without preempting anyone."""
+
     def __init__(self, args: EngineArgs):
         from ..config.registry import load_config
 
@@ -64,6 +86,12 @@ class Engine:
         self.requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
         self.stats = StepStats()
+        self._launched: Optional[_Launched] = None          # a step launched ahead by the last call of step()
+        # two pinned buffers for sampled tokens: one is read while the step ahead fills the other
+        self._token_staging = [torch.empty(max(args.max_batch, 1), dtype=torch.int32, pin_memory=True)
+                               for _ in range(2)]
+        self._staging_turn = 0
+        self.n_launched_ahead = 0
 
     @property
     def vocab_size(self) -> int:
@@ -89,34 +117,74 @@ class Engine:
         return self.scheduler.has_work()
 
     # -- one turn of the loop
-    def step(self) -> List[Request]:
-        """Schedule, run and sample one step; returns the requests that got a new token."""
-        t0 = time.perf_counter()
-        plan = self.scheduler.schedule()
-        if not plan:
-            return []
+    def _launch(self, plan: List[ScheduledEntry], device_tokens: Optional[torch.Tensor] = None,
+                ahead: int = 0) -> _Launched:
+        """Run the step for ``plan``, sample, and start the copy of the new tokens to the host; nothing
+        waits.  With ``device_tokens`` every entry is one decoded token whose id lies on the device (the
+        tokens sampled by the step before, which the host has not seen yet: ``ahead`` = 1)."""
         entries = []
         for e in plan:
-            toks = e.request.token_slice(e.start, e.n)
+            toks = [0] if device_tokens is not None else e.request.token_slice(e.start, e.n)
             entries.append(StepEntry(e.request.id, toks, [e.n - 1] if e.sample else []))
-        logits = self.runner.step(entries)
-        sampled: Dict[Hashable, int] = {}
+        logits = self.runner.step(entries, device_tokens=device_tokens)
         got = [e.request for e in plan if e.sample]
+        toks = host = None
         if got:
             # the token history only where a repeat penalty reads it
             recent = [r.tokens for r in got] if any(r.params.repeat_penalty != 1.0 for r in got) else None
-            toks = sample(logits, [r.params for r in got], [r.seed for r in got], [len(r.output) for r in got],
-                          recent)
-            for r, t in zip(got, toks.tolist()):                    # the step's one device-to-host read
-                sampled[r.id] = t
-        else:
-            torch.cuda.current_stream().synchronize()
+            toks = sample(logits, [r.params for r in got], [r.seed for r in got],
+                          [len(r.output) + ahead for r in got], recent)
+            host = self._token_staging[self._staging_turn]
+            self._staging_turn ^= 1
+            host[:len(got)].copy_(toks, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return _Launched(plan, got, toks, host, done)
+
+    def _launch_ahead(self, cur: _Launched) -> Optional[_Launched]:
+        """The step after ``cur``, if it can only be one more token for every request of ``cur``."""
+        sch = self.scheduler
+        if (not self.args.look_ahead or sch.waiting or not cur.got or len(cur.got) != len(cur.plan)
+                or len(cur.plan) != len(sch.running)):
+            return None
+        for r in cur.got:
+            n_pred = r.params.n_predict
+            if (r.state != RUNNING or r.params.repeat_penalty != 1.0
+                    or (n_pred >= 0 and len(r.output) + 1 >= n_pred)
+                    or r.n_tokens + 1 >= self.runner.max_model_len):
+                return None
+        for r in cur.got:
+            if not self.runner.cache.try_extend(r.id, r.n_tokens + 1):
+                return None                 # (pages taken for the others stay theirs: they need them anyway)
+        plan = [ScheduledEntry(r, r.n_tokens, 1, True) for r in cur.got]
+        self.n_launched_ahead += 1
+        return self._launch(plan, device_tokens=cur.tokens, ahead=1)
+
+    def step(self) -> List[Request]:
+        """Schedule, run and sample one step; returns the requests that got a new token."""
+        t0 = time.perf_counter()
+        cur, self._launched = self._launched, None
+        if cur is not None and not any(e.request.state == RUNNING for e in cur.plan):
+            cur.done.synchronize()                                   # everyone in it has ended meanwhile
+            cur = None
+        if cur is None:
+            plan = self.scheduler.schedule()
+            if not plan:
+                return []
+            cur = self._launch(plan)
+        ahead = self._launch_ahead(cur)
+        cur.done.synchronize()                                       # the step's one device-to-host read
+        new = cur.host[:len(cur.got)].tolist() if cur.got else []
+        plan = [e for e in cur.plan if e.request.state == RUNNING]   # without those that ended meanwhile
+        sampled = {r.id: t for r, t in zip(cur.got, new)}
+        n_prompt = sum(e.n for e in plan if e.n > 1 or not e.request.output)
+        n_decode = sum(1 for e in plan if e.n == 1 and e.request.output and e.sample)
         self.scheduler.update(plan, sampled)
+        self._launched = ahead
+        got = [e.request for e in plan if e.sample]
         dt = time.perf_counter() - t0
         st = self.stats
         st.n_steps += 1
-        n_prompt = sum(e.n for e in plan if e.n > 1 or not e.request.output)
-        n_decode = sum(1 for e in plan if e.n == 1 and e.request.output and e.sample)
         if n_prompt >= n_decode:
             st.prompt_seconds += dt
         else:
@@ -144,5 +212,8 @@ class Engine:
         return self.requests[request_id].finish_reason
 
     def shutdown(self) -> None:
+        if self._launched is not None:
+            self._launched.done.synchronize()
+            self._launched = None
         self.runner = None
         self.scheduler = None

@@ -199,7 +199,8 @@ class Scheduler:
         for e in entries:
             r = e.request
             r.n_computed = e.start + e.n
-            self.cache.advance(r.id, r.n_computed)
+            if self.cache.requests[r.id].length < r.n_computed:       # (a step function may have done it)
+                self.cache.advance(r.id, r.n_computed)
             if not e.sample:
                 continue
             tok = int(sampled[r.id])

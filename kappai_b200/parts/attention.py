@@ -104,26 +104,45 @@ class Attention(Part):
             K.qk_norm_rope_kv(qkv, None, None, 0.0, None, None, 0, False, ctx.positions, view.slot_map, q, kv_out,
                               view.page_size, H, G, hd)
         o = torch.empty_like(q)
-        if ctx.max_seg_len <= SPLIT_MAX_SEG_LEN and H // G <= K.SPLIT_MAX_RATIO:
+        split_ok = H // G <= K.SPLIT_MAX_RATIO
+        if ctx.max_seg_len <= SPLIT_MAX_SEG_LEN and split_ok:
             # rows that each read a long cache (decode): split the keys over many CTAs
-            n_chunks = ctx.attn_chunks if getattr(ctx, "attn_chunks", None) else -(-ctx.max_context // K.SPLIT_CHUNK)
-            need = K.attention_split_scratch(ctx.n_rows, H, hd, n_chunks)
-            ws = self.env.shared.get("attn_scratch")
-            if ws is None or ws.numel() < need:
-                ws = torch.zeros(max(need, 1 << 16), dtype=torch.float32, device=q.device)
-                self.env.shared["attn_scratch"] = ws
-            # (the chunk kernel can merge too, fused_merge=True: measured slower in the decode step, 714 against
-            # 697 us, since the last CTA's fence, counter and dependent loads cost more than the launch they save)
-            K.attention_split(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, ws, n_chunks,
-                              self.scale, self.window, view.page_size, H, G, hd)
+            self._split(q, o, ctx, view, cache, ctx.n_rows)
         elif K.attention_prefill_ok(q, hd) and ctx.tile_seg is not None:
-            K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, ctx.tile_seg,
-                                ctx.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd,
-                                getattr(ctx, "big_tile_seg", None), getattr(ctx, "big_tile_row0", None))
+            lead = getattr(ctx, "n_short_rows", 0)
+            if lead and split_ok:
+                # decoded tokens beside prompt portions: the decoded rows lead the batch and go to the split
+                # kernel (in a row tile each would walk its whole cache alone), the portions to the tiled one
+                self._split(q, o, ctx, view, cache, lead)
+                t0 = ctx.n_short_tiles
+                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, ctx.tile_seg[t0:],
+                                    ctx.tile_row0[t0:], o, self.scale, self.window, view.page_size, H, G, hd,
+                                    ctx.big_tile_seg, ctx.big_tile_row0)
+            else:
+                # (with a lead that the split kernel cannot take, the big tiles leave it out: small tiles only)
+                big = (None, None) if lead else (getattr(ctx, "big_tile_seg", None),
+                                                 getattr(ctx, "big_tile_row0", None))
+                K.attention_prefill(q, cache.tensor, view.block_table, ctx.cu_rows, ctx.seg_pos, ctx.tile_seg,
+                                    ctx.tile_row0, o, self.scale, self.window, view.page_size, H, G, hd, *big)
         else:
             K.attention_rows(q, cache.tensor, view.block_table, ctx.row_seg, ctx.positions, o, self.scale,
                              self.window, view.page_size, H, G, hd)
         linear(o, self.w_o, self.b_o, out=residual, accumulate=True)
+
+
+    def _split(self, q, o, ctx, view, cache, n_rows):
+        """Split-key attention for the first ``n_rows`` rows of the step."""
+        H, G, hd = self.H, self.G, self.hd
+        n_chunks = ctx.attn_chunks if getattr(ctx, "attn_chunks", None) else -(-ctx.max_context // K.SPLIT_CHUNK)
+        need = K.attention_split_scratch(n_rows, H, hd, n_chunks)
+        ws = self.env.shared.get("attn_scratch")
+        if ws is None or ws.numel() < need:
+            ws = torch.zeros(max(need, 1 << 16), dtype=torch.float32, device=q.device)
+            self.env.shared["attn_scratch"] = ws
+        # (the chunk kernel can merge too, fused_merge=True: measured slower in the decode step, 714 against
+        # 697 us, since the last CTA's fence, counter and dependent loads cost more than the launch they save)
+        K.attention_split(q[:n_rows], cache.tensor, view.block_table, ctx.row_seg[:n_rows], ctx.positions[:n_rows],
+                          o[:n_rows], ws, n_chunks, self.scale, self.window, view.page_size, H, G, hd)
 
 
 register_part("mixer", "attention", Attention)

@@ -50,6 +50,23 @@ def test_tile_lists_cover_every_row_once_and_big_tiles_come_longest_first():
     assert last[0] == 900
 
 
+def test_decoded_tokens_that_lead_a_mixed_step_are_set_apart():
+    segs = [seg("a", 1, 900, 0), seg("b", 2, 40, 1), seg("c", 300, 0, 2), seg("d", 1, 77, 3)]
+    ctx = build_step_context(segs, {"g": 16}, CPU, 1000, 4096)
+    assert ctx.n_short_rows == 3 and ctx.n_short_tiles == 2
+    assert ctx.tile_seg.tolist()[:2] == [0, 1]                        # the lead's small tiles come first
+    assert sorted(set(ctx.big_tile_seg.tolist())) == [2, 3]           # big tiles: the other segments only
+    covered = np.zeros(ctx.n_rows, int)
+    cu = ctx.cu_rows.tolist()
+    for s, r0 in zip(ctx.big_tile_seg.tolist(), ctx.big_tile_row0.tolist()):
+        covered[r0:min(r0 + BIG_TILE, cu[s + 1])] += 1
+    assert covered.tolist() == [0] * 3 + [1] * 301
+    # all short, or no short lead: one kernel takes the step, nothing is set apart
+    for other in ([seg("a", 1, 9, 0), seg("b", 3, 4, 1)], [seg("a", 9, 9, 0), seg("b", 1, 4, 1)]):
+        c2 = build_step_context(other, {"g": 16}, CPU, 1000, 4096)
+        assert c2.n_short_rows == 0 and c2.n_short_tiles == 0 and c2.n_big_tiles == 2
+
+
 def test_refusals():
     with pytest.raises(BatchError):
         build_step_context([], {"g": 16}, CPU, 10, 64)

@@ -153,6 +153,45 @@ def test_seeded_sampling_does_not_depend_on_the_batch(model_dirs):
     assert greedy != alone[0] or True
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_change_nothing(dtype, model_dirs):
+    """The engine launches the next decode step before it has read the last one's tokens.  The same workload
+    with and without that: requests that end by an end-of-sequence token while a step with them is under way,
+    by their length, a request that arrives in the middle, one that is aborted, seeded sampling; the tokens,
+    the reasons and the state of the cache at the end are the same."""
+    from kappai_b200 import SamplingParams
+    rng = np.random.default_rng(31)
+    prompts = [rng.integers(0, 512, n).tolist() for n in (9, 40, 3, 25)]
+    late = rng.integers(0, 512, 12).tolist()
+    sps = [SamplingParams(temperature=0.0, n_predict=30), SamplingParams(temperature=0.0, n_predict=17),
+           SamplingParams(temperature=0.9, top_k=50, seed=4, n_predict=26), SamplingParams(temperature=0.0, n_predict=60)]
+
+    def run(look_ahead, eos):
+        eng = engine(model_dirs["B"], dtype, look_ahead=look_ahead, max_step_tokens=64)
+        eng.scheduler.eos_token_id = eos
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        n = 0
+        while eng.has_work():
+            eng.step()
+            n += 1
+            if n == 8:
+                ids.append(eng.add_request(late, SamplingParams(temperature=0.0, n_predict=9)))
+            if n == 22:
+                eng.scheduler.abort(ids[3])
+        eng.runner.cache.check()
+        assert eng.runner.cache.slots.n_free == 4
+        outs = [eng.requests[i].output for i in ids]
+        return outs, [eng.finish_reason(i) for i in ids], eng.n_launched_ahead
+
+    plain_outs, _, _ = run(False, None)
+    eos = plain_outs[0][11]                                  # a token the first request meets on its way
+    want = run(False, eos)
+    got = run(True, eos)
+    assert want[2] == 0 and got[2] > 10
+    assert got[:2] == want[:2]
+    assert "eos" in want[1] and "length" in want[1] and "aborted" in want[1]
+
+
 def test_context_full_and_bad_requests(model_dirs):
     from kappai_b200 import SamplingParams
     eng = engine(model_dirs["A"], "float32", ctx_size=40)

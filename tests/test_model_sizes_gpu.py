@@ -47,6 +47,38 @@ def test_long_prompt_in_odd_portions_then_decoding(dtype, model):
     assert K.tc_status() == 0 and K.stream_status() == 0 and K.attention_tc_status() == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoded_tokens_beside_prompt_portions(dtype, model):
+    """Three requests with caches of different lengths each bring one decoded token while a fourth brings
+    portions of its prompt: the decoded rows lead the step (split-key kernel) and the portion follows (tiled
+    kernel); then the same with the portion first, where one kernel takes all.  Every row against the plain model."""
+    from kappai_b200 import ModelRunner, StepEntry
+    from kappai_b200.ops import kernels as K
+    d, plain = model
+    rng = np.random.default_rng(5)
+    V = CONFIG["vocab_size"]
+    lens = [1500, 70, 640]
+    seqs = [rng.integers(0, V, L + 4).tolist() for L in lens]
+    long = rng.integers(0, V, 900).tolist()
+    refs = [plain.logits(s) for s in seqs]
+    ref_long = plain.logits(long)
+    r = ModelRunner(d, dtype=dtype, max_tokens=4096, max_requests=4, page_size=64, max_model_len=4096)
+    for i, (s, L) in enumerate(zip(seqs, lens)):
+        r.step([StepEntry(i, s[:L], [])])
+    cuts = [0, 300, 301, 640, 900]
+    for k, (a, b) in enumerate(zip(cuts[:-1], cuts[1:])):
+        dec = [StepEntry(i, [s[L + k]], [0]) for i, (s, L) in enumerate(zip(seqs, lens))]
+        want = sorted({0, b - a - 1})
+        portion = StepEntry("p", long[a:b], want)
+        entries = dec + [portion] if k != 2 else [portion] + dec
+        lg = r.step(entries).float().cpu().numpy()
+        rows = [(refs[i][L + k], (i, k)) for i, L in enumerate(lens)]
+        prows = [(ref_long[a + w], ("p", a, w)) for w in want]
+        for j, (want_row, what) in enumerate(rows + prows if k != 2 else prows + rows):
+            assert np.abs(lg[j] - want_row).max() <= tol_for(dtype, want_row), (dtype, what)
+    assert K.tc_status() == 0 and K.stream_status() == 0 and K.attention_tc_status() == 0
+
+
 WIDE_CONFIG = {'architectures': ['Lfm2ForCausalLM'], 'vocab_size': 640, 'hidden_size': 512, 'num_hidden_layers': 2,
                'num_attention_heads': 8, 'num_key_value_heads': 2, 'layer_types': ['conv', 'full_attention'],
                'max_position_embeddings': 1024, 'norm_eps': 1e-06, 'conv_L_cache': 3, 'conv_bias': False,
