@@ -56,6 +56,7 @@ class Attention(Part):
         elif isinstance(pos, dict):
             pos = PartSpec(**pos)
         self.position = make_part("position", pos, env)
+        self.graph_safe = bool(self.position.graph_safe)     # a position part that reads host values keeps it eager
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         d, H, G, hd = self.d, self.H, self.G, self.hd

@@ -21,6 +21,7 @@ from .base import Part, register_part
 
 class RotaryEncoding(Part):
     category = "position"
+    graph_safe = True
 
     def __init__(self, params, env):
         super().__init__(params, env)
@@ -47,6 +48,7 @@ class RotaryEncoding(Part):
 
 class NoPosition(Part):
     category = "position"
+    graph_safe = True
 
     def fused_rotary(self):
         return None, None, 0, False

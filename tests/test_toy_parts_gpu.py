@@ -148,6 +148,184 @@ def test_toy_architecture_with_a_stateful_mixer(tmp_path):
         unregister_architecture("ToyForCausalLM")
 
 
+# ------------------------- a toy position encoding and a toy feed-forward with routing
+def make_toy_position():
+    from kappai_b200.parts import Part
+
+    class LinearRotary(Part):
+        """Pairs (2j, 2j+1) of the first ``n_rot`` dims of every head turn by ``pos * step * (j + 1)``."""
+        category = "position"
+        graph_safe = True                     # reads ctx.positions on the device only
+
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.n_rot, self.step, self.hd = params["n_rot"], params["step"], params["head_dim"]
+
+        def apply(self, q, k, ctx):
+            j = torch.arange(self.n_rot // 2, device=q.device, dtype=torch.float32)
+            ang = ctx.positions.float()[:, None] * (self.step * (j + 1))[None, :]
+            cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+            for t in (q, k):
+                v = t.unflatten(1, (-1, self.hd))
+                x0, x1 = v[..., 0:self.n_rot:2].float().clone(), v[..., 1:self.n_rot:2].float().clone()
+                v[..., 0:self.n_rot:2] = (x0 * cos - x1 * sin).to(t.dtype)
+                v[..., 1:self.n_rot:2] = (x0 * sin + x1 * cos).to(t.dtype)
+
+    return LinearRotary
+
+
+def make_toy_experts():
+    from kappai_b200.ops.linear import linear, linear_swiglu
+    from kappai_b200.parts import Part, WeightSpec
+
+    class Top1Experts(Part):
+        """Router logits h R^T, softmax in float32, the best expert's SwiGLU output times its probability."""
+        category = "feed_forward"
+
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.d, self.ff, self.E = params["hidden_size"], params["intermediate_size"], params["n_experts"]
+
+        def weight_specs(self):
+            s = {"router.weight": WeightSpec((self.E, self.d))}
+            for e in range(self.E):
+                s[f"experts.{e}.gate_proj.weight"] = WeightSpec((self.ff, self.d))
+                s[f"experts.{e}.up_proj.weight"] = WeightSpec((self.ff, self.d))
+                s[f"experts.{e}.down_proj.weight"] = WeightSpec((self.d, self.ff))
+            return s
+
+        def bind(self, w):
+            self.router = (w["router.weight"] * 8).contiguous()          # (larger logits: clear choices)
+            self.w_gu = [torch.cat([w[f"experts.{e}.gate_proj.weight"], w[f"experts.{e}.up_proj.weight"]], 0).contiguous()
+                         for e in range(self.E)]
+            self.w_down = [w[f"experts.{e}.down_proj.weight"].contiguous() for e in range(self.E)]
+
+        def forward(self, h, residual, ctx):
+            p = torch.softmax(linear(h, self.router, out_dtype=torch.float32), -1)
+            gate, top = p.max(-1)
+            for e in range(self.E):
+                rows = (top == e).nonzero().flatten()
+                if rows.numel():
+                    y = linear(linear_swiglu(h[rows].contiguous(), self.w_gu[e]), self.w_down[e], out_dtype=torch.float32)
+                    residual.index_add_(0, rows, y * gate[rows, None])
+
+    return Top1Experts
+
+
+def routed_config_cls():
+    from kappai_b200.config import TypedConfig, cfg
+
+    @dataclass
+    class RoutedConfig(TypedConfig):
+        vocab_size: int = cfg()
+        width: int = cfg()
+        depth: int = cfg()
+        heads: int = cfg()
+        kv_heads: int = cfg()
+        head_dim: int = cfg()
+        ff: int = cfg()
+        n_experts: int = cfg()
+        window: int = cfg()
+        max_len: int = cfg(128)
+
+    return RoutedConfig
+
+
+def routed_build_spec(c):
+    from kappai_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    norm = lambda p: PartSpec("rmsnorm", {"size": c.width, "eps": 1e-5}, p)
+    pos = PartSpec("toy_linear_rotary", {"n_rot": c.head_dim // 2, "step": 0.05, "head_dim": c.head_dim})
+    att = lambda i: PartSpec("attention", {"hidden_size": c.width, "num_heads": c.heads, "num_kv_heads": c.kv_heads,
+                                           "head_dim": c.head_dim, "scale": c.head_dim ** -0.5,
+                                           "window": c.window if i % 2 else None, "position": pos}, f"l.{i}.att.")
+    layers = [LayerSpec(mixer=att(i),
+                        ffn=PartSpec("toy_top1", {"hidden_size": c.width, "intermediate_size": c.ff,
+                                                  "n_experts": c.n_experts}, f"l.{i}.moe."),
+                        mixer_norm=norm(f"l.{i}.n1."), ffn_norm=norm(f"l.{i}.n2."))
+              for i in range(c.depth)]
+    return ModelSpec("RoutedToyForCausalLM", c.width, c.vocab_size, c.max_len,
+                     PartSpec("embedding", {"vocab_size": c.vocab_size, "hidden_size": c.width}, "emb."),
+                     layers, [ScheduleEntry(i) for i in range(c.depth)], norm("final."),
+                     PartSpec("lm_head", {"vocab_size": c.vocab_size, "hidden_size": c.width, "tied": True}, "head."))
+
+
+def routed_plain_logits(w, c, toks):
+    T, H, G, hd = len(toks), c["heads"], c["kv_heads"], c["head_dim"]
+    n_rot = hd // 2
+    ang = np.arange(T)[:, None] * (0.05 * (np.arange(n_rot // 2) + 1))[None, :]
+    cos, sin = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+
+    def turn(v):
+        v = v.copy()
+        x0, x1 = v[..., 0:n_rot:2].copy(), v[..., 1:n_rot:2].copy()
+        v[..., 0:n_rot:2], v[..., 1:n_rot:2] = x0 * cos - x1 * sin, x0 * sin + x1 * cos
+        return v
+
+    x = w["emb.weight"][np.asarray(toks)]
+    for i in range(c["depth"]):
+        p = f"l.{i}."
+        h = P.rmsnorm(x, w[p + "n1.weight"], 1e-5)
+        q = turn(P.linear(h, w[p + "att.q_proj.weight"]).reshape(T, H, hd))
+        k = turn(P.linear(h, w[p + "att.k_proj.weight"]).reshape(T, G, hd))
+        v = P.linear(h, w[p + "att.v_proj.weight"]).reshape(T, G, hd)
+        o = P.attention(q, k, v, hd ** -0.5, c["window"] if i % 2 else None)
+        x = x + P.linear(o.reshape(T, -1), w[p + "att.out_proj.weight"])
+        h = P.rmsnorm(x, w[p + "n2.weight"], 1e-5)
+        lg = P.linear(h, w[p + "moe.router.weight"] * 8)
+        pr = np.exp(lg - lg.max(-1, keepdims=True))
+        pr /= pr.sum(-1, keepdims=True)
+        top = pr.argmax(-1)
+        ranked = np.sort(pr, -1)
+        assert (ranked[:, -1] - ranked[:, -2]).min() > 1e-4 and len(set(top.tolist())) > 1     # clear choices, several experts
+        y = np.zeros_like(x)
+        for t in range(T):
+            e = f"{p}moe.experts.{top[t]}."
+            f = P.swiglu(P.linear(h[t:t + 1], w[e + "gate_proj.weight"]), P.linear(h[t:t + 1], w[e + "up_proj.weight"]))
+            y[t] = pr[t, top[t]] * P.linear(f, w[e + "down_proj.weight"])[0]
+        x = x + y
+    return P.linear(P.rmsnorm(x, w["final.weight"], 1e-5), w["emb.weight"])
+
+
+def test_toy_architecture_with_its_own_position_encoding_and_routed_experts(tmp_path):
+    """Attention (the framework's part and kernels, one layer with a window) with a position encoding defined
+    here, and a feed-forward that routes every row to one of three experts, also defined here: registered,
+    built from a configuration of its own, stepped in portions and decoded, against a plain computation."""
+    from kappai_b200 import ModelRunner, StepEntry, write_random_model
+    from kappai_b200.config import register_architecture, unregister_architecture
+    from kappai_b200.parts import register_part, unregister_part
+    register_part("position", "toy_linear_rotary", make_toy_position())
+    register_part("feed_forward", "toy_top1", make_toy_experts())
+    register_architecture("RoutedToyForCausalLM", routed_config_cls(), routed_build_spec)
+    try:
+        c = dict(architectures=["RoutedToyForCausalLM"], vocab_size=113, width=40, depth=3, heads=6, kv_heads=2,
+                 head_dim=16, ff=24, n_experts=3, window=9, max_len=128)
+        d = write_random_model(c, str(tmp_path / "routed"), 6)
+        w = {k: v.astype(np.float64) for k, v in P.read_safetensors(os.path.join(d, "model.safetensors")).items()}
+        rng = np.random.default_rng(2)
+        seqs = {"a": rng.integers(0, 113, 70).tolist(), "b": rng.integers(0, 113, 31).tolist()}
+        ref = {k: routed_plain_logits(w, c, t) for k, t in seqs.items()}
+        r = ModelRunner(d, dtype="float32", max_tokens=128, page_size=16)
+        assert len(r.cache.pools) == 2                     # layers that keep all keys, and the one with a window
+        assert not r.model.graph_safe                      # the routed part is not: every step runs eagerly
+        got, fed = {"a": [], "b": []}, {"a": 0, "b": 0}
+        plan = [{"a": 30}, {"a": 2, "b": 29}, {"a": 1, "b": 1}, {"b": 1}, {"a": 37}]
+        for st in plan:
+            ents = [StepEntry(k, seqs[k][fed[k]:fed[k] + n], list(range(n))) for k, n in st.items()]
+            out = r.step(ents).cpu().double().numpy()
+            o = 0
+            for k, n in st.items():
+                got[k].append(out[o:o + n]); o += n; fed[k] += n
+        for k in seqs:
+            err = np.abs(np.concatenate(got[k]) - ref[k]).max()
+            assert err <= tol_for("float32", ref[k]), (k, err)
+        r.end("a"); r.end("b")
+        r.cache.check()
+    finally:
+        unregister_part("position", "toy_linear_rotary")
+        unregister_part("feed_forward", "toy_top1")
+        unregister_architecture("RoutedToyForCausalLM")
+
+
 # ----------------------------------- the schedule is data: twice, and a borrowed cache
 def test_layer_named_twice_and_borrowed_cache(model_dirs, plain_models):
     """Schedule [0, 1, 2, 3, 1, 3*] over Tiny A's four layers: layer 1 (attention) runs twice with a
