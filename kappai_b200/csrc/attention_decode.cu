@@ -218,7 +218,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                   int chunk_keys, int window, int H, int hd) {
-    kp_pdl_begin();
+    kp_pdl_begin_early();
     const int h = blockIdx.x, row = blockIdx.y;
     int k_lo, k_hi;
     key_range(positions[row], window, k_lo, k_hi);

@@ -74,6 +74,10 @@ __device__ __forceinline__ float block_max(float v, float* smem) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void kp_pdl_begin() { pdl_wait(); pdl_launch_dependents(); }
+// The same with the kernel after this one let in first: it may then become resident, and run what it has
+// before its own wait (a product's producers fill their rings with weights), while this kernel still waits
+// for the one before it.  For the small kernels of a decode step that stand between two products.
+__device__ __forceinline__ void kp_pdl_begin_early() { pdl_launch_dependents(); pdl_wait(); }
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t kp_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,

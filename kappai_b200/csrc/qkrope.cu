@@ -89,7 +89,7 @@ qk_norm_rope_kv_vec_kernel(const bf16* __restrict__ qkv, int ld, const float* __
                            const float* __restrict__ sin_tab, const int* __restrict__ positions,
                            const int* __restrict__ slot_map, bf16* __restrict__ q_out, int ldq,
                            bf16* __restrict__ cache, int page_size, int H, int G, int write_kv) {
-    kp_pdl_begin();
+    kp_pdl_begin_early();
     constexpr int L = HD / 8;                          // lanes a head
     constexpr int HPB = 128 / L;                       // heads a block
     const int lane_in = threadIdx.x % L;
