@@ -214,27 +214,93 @@ attn_split_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
     }
 }
 
+#define MERGE_THREADS 256
+#define MERGE_BATCH 4096                                    // floats of accumulators in shared memory at a time
+
+// The chunks of a row and head put together: out = sum_c acc_c * exp(m_c - m) / sum_c l_c * exp(m_c - m), the
+// sums in chunk order.  One CTA a (head, row).  The statistics of the row's chunks and the weights
+// exp(m_c - m) are brought into shared memory once by all threads together; only the sums themselves run
+// chunk by chunk (a context of 32k tokens has 128 chunks: with every thread walking global memory three times
+// for them the merge took longer than half of the attention itself).
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                   int chunk_keys, int window, int H, int hd) {
     kp_pdl_begin_early();
-    const int h = blockIdx.x, row = blockIdx.y;
+    extern __shared__ __align__(16) float merge_sm[];       // [MERGE_BATCH], [n_chunks] l_c, [n_chunks] exp(m_c - m), [32]
+    const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
     int k_lo, k_hi;
     key_range(positions[row], window, k_lo, k_hi);
-    const int c_lo = k_lo / chunk_keys, c_hi = k_hi / chunk_keys;
-    const float* ml = part_ml + ((size_t)row * H + h) * n_chunks * 2;
+    const int c_lo = k_lo / chunk_keys, c_hi = k_hi / chunk_keys, n = c_hi - c_lo + 1;
+    float* s_acc = merge_sm;
+    float* s_l = merge_sm + MERGE_BATCH;
+    float* s_w = s_l + n_chunks;
+    float* s_red = s_w + n_chunks;
+    // the accumulators: brought in batches of MERGE_BATCH floats by all threads (every load of a batch in
+    // flight at once), then added chunk by chunk by the thread of each dimension
+    const float* pa = part_acc + (((size_t)row * H + h) * n_chunks + c_lo) * hd;
+    const int mb = MERGE_BATCH / hd;                        // chunks a batch
+    constexpr int PER = MERGE_BATCH / 4 / MERGE_THREADS;    // float4 a thread and batch
+    float4 reg[PER];
+    auto fetch = [&](int c0) {                              // the batch from chunk c0 on, into registers
+        const int nb = min(mb, n - c0);
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int i = (k * MERGE_THREADS + tid) * 4;
+            if (i < nb * hd) reg[k] = *reinterpret_cast<const float4*>(pa + (size_t)c0 * hd + i);
+        }
+    };
+    fetch(0);                                               // under way while the statistics are worked out
+    const float* ml = part_ml + (((size_t)row * H + h) * n_chunks + c_lo) * 2;
     float m = -INFINITY;
-    for (int c = c_lo; c <= c_hi; c++) m = fmaxf(m, ml[2 * c]);
-    float l = 0.f;
-    for (int c = c_lo; c <= c_hi; c++) l += ml[2 * c + 1] * expf(ml[2 * c] - m);
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    const float* pa = part_acc + ((size_t)row * H + h) * n_chunks * hd;
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float v = 0.f;
-        for (int c = c_lo; c <= c_hi; c++) v = fmaf(pa[(size_t)c * hd + d], expf(ml[2 * c] - m), v);
-        out[(size_t)row * ldo + (size_t)h * hd + d] = from_f32<T>(v * inv);
+    for (int c = tid; c < n; c += nt) {
+        const float2 v = *reinterpret_cast<const float2*>(ml + 2 * c);
+        s_w[c] = v.x;                                       // m_c for now
+        s_l[c] = v.y;
+        m = fmaxf(m, v.x);
     }
+    m = warp_max(m);
+    if ((tid & 31) == 0) s_red[tid >> 5] = m;
+    __syncthreads();
+    m = -INFINITY;
+    for (int w = 0; w < (nt + 31) / 32; w++) m = fmaxf(m, s_red[w]);
+    for (int c = tid; c < n; c += nt) s_w[c] = expf(s_w[c] - m);
+    __syncthreads();
+    float l = 0.f;
+    for (int c = 0; c < n; c++) l += s_l[c] * s_w[c];
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    float v = 0.f;
+    for (int c0 = 0; c0 < n; c0 += mb) {
+        const int nb = min(mb, n - c0);
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const int i = (k * MERGE_THREADS + tid) * 4;
+            if (i < nb * hd) *reinterpret_cast<float4*>(s_acc + i) = reg[k];
+        }
+        __syncthreads();
+        if (c0 + mb < n) fetch(c0 + mb);                    // the next batch is under way while this one is added
+        if (tid < hd)
+            for (int j = 0; j < nb; j++) v = fmaf(s_acc[j * hd + tid], s_w[c0 + j], v);
+        __syncthreads();
+    }
+    if (tid < hd) out[(size_t)row * ldo + (size_t)h * hd + tid] = from_f32<T>(v * inv);
+}
+
+static size_t merge_smem_bytes(int n_chunks) { return sizeof(float) * ((size_t)2 * n_chunks + 32 + MERGE_BATCH); }
+
+template <typename T>
+static int launch_merge(const float* part_acc, const float* part_ml, const int* positions, void* out, int ldo,
+                        int n_chunks, int chunk_keys, int window, int n, int H, int hd, cudaStream_t s) {
+    const size_t smem = merge_smem_bytes(n_chunks);
+    if (smem > 200 * 1024) return KP_ERR_UNSUPPORTED;       // (25,000 chunks: 6.5 million keys)
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_merge_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (hd > MERGE_THREADS || (hd & 3)) return KP_ERR_UNSUPPORTED;
+    kp_launch_pdl(attn_merge_kernel<T>, dim3(H, n), dim3(MERGE_THREADS), smem, s, part_acc, part_ml, positions, (T*)out, ldo,
+                  n_chunks, chunk_keys, window, H, hd);
+    return kp_launch_status();
 }
 
 static size_t split_smem_bytes(int R, int hd) {
@@ -264,8 +330,6 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
     float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_chunks, G, n);
-    dim3 mgrid(H, n);
-    const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
 #define AD_LAUNCH(T, HD, RR)                                                                                      \
     kp_launch_pdl(attn_split_kernel<T, HD, RR>, dim3(grid), dim3(AD_THREADS), smem, s, (const T*)q, ldq, (const T*)cache, block_table,       \
                                                                 max_blocks, row_seg, positions, part_acc, part_ml,    \
@@ -277,8 +341,7 @@ int kp_attention_split(const void* q, int ldq, const void* cache, const int* blo
         else if (hd == 128) e0 = AD_LAUNCH(T, 128, 0);
         else e0 = AD_LAUNCH(T, 0, 0);
         if (e0 != cudaSuccess) { cudaGetLastError(); return (int)e0; }      // the first launch that failed
-        kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, s, part_acc, part_ml, positions, (T*)out, ldo, n_chunks,
-                                                        AD_CHUNK, window, H, hd);
+        return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, AD_CHUNK, window, n, H, hd, s);
     });
 #undef AD_LAUNCH
     return kp_launch_status();
@@ -292,10 +355,8 @@ int kp_attention_merge(const int* positions, void* out, int ldo, const float* sc
     if (hd < 16 || hd > KP_MAX_HEAD_DIM || n > 65535 || chunk_keys < 1) return KP_ERR_UNSUPPORTED;
     const float* part_acc = scratch;
     const float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
-    dim3 mgrid(H, n);
-    const int mthreads = hd < 32 ? 32 : (hd > 128 ? 128 : hd);
-    KP_DISPATCH_DTYPE(dtype, T, (kp_launch_pdl(attn_merge_kernel<T>, dim3(mgrid), dim3(mthreads), 0, (cudaStream_t)stream, 
-        part_acc, part_ml, positions, (T*)out, ldo, n_chunks, chunk_keys, window, H, hd)));
+    KP_DISPATCH_DTYPE(dtype, T, return launch_merge<T>(part_acc, part_ml, positions, out, ldo, n_chunks, chunk_keys, window,
+                                                       n, H, hd, (cudaStream_t)stream));
     return kp_launch_status();
 }
 

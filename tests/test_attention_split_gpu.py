@@ -70,6 +70,30 @@ def test_split_finds_one_far_key(dtype, far):
         np.testing.assert_allclose(got[h], vs[0][far, h // (H // G)], atol=2e-2)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd,window", [(64, None), (128, None), (64, 7000), (48, None)])
+def test_split_over_many_chunks(dtype, hd, window):
+    """20,000 keys: 79 chunks, more than the merge holds in shared memory at a time (it adds them batch by
+    batch, in chunk order); with a window the first chunks are left out.  One far key stands out."""
+    rng = np.random.default_rng(43)
+    H, G, page, L = 4, 2, 64, 20000
+    cache, bt, ks, vs = paged_setup(rng, [L, 300], page, G, hd, dtype)
+    q = rt(rng.standard_normal((2, H, hd)), dtype)
+    q[0, 1] = ks[0][L - 6500, 0] * 4.0                       # head 1 looks at one key far back (inside the window)
+    scale = 1.0 / math.sqrt(hd)
+    out = run_split(q.reshape(2, -1), cache, bt, [0, 1], [L - 1, 299], scale, window, page, H, G, hd, dtype)
+    got = out.cpu().double().numpy().reshape(2, H, hd)
+    for j, (s_, p) in enumerate([(0, L - 1), (1, 299)]):
+        # the last row only: scores of one query against all keys
+        kk, vv = ks[s_][:p + 1], vs[s_][:p + 1]
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(H):
+            sc = (kk[lo:, h // (H // G)] @ q[j, h]) * scale
+            w = np.exp(sc - sc.max()); w /= w.sum()
+            np.testing.assert_allclose(got[j, h], w @ vv[lo:, h // (H // G)], rtol=tol(dtype), atol=tol(dtype),
+                                       err_msg=f"row {j} head {h}")
+
+
 def test_split_row_does_not_depend_on_the_batch():
     rng = np.random.default_rng(42)
     H, G, hd, page = 32, 8, 64, 64
