@@ -25,6 +25,8 @@
 // the fewest; a CTA takes the i-th and the i-th last, so every CTA has about the same work.
 // Every mbarrier wait is bounded; a wait that gives up sets the status word, and the CTA frees its tensor
 // memory and returns.
+#include <type_traits>
+
 #include "tcgen05.cuh"
 
 #define AT_BM 128
@@ -39,6 +41,13 @@ __device__ __forceinline__ float at_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// the largest of three (one instruction on this architecture)
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
 }
 
 struct AtArgs {
@@ -235,7 +244,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                         }
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) tmax = fmaxf(tmax, __uint_as_float(s[j]));
+                        for (int j = 0; j < 32; j += 2) tmax = at_max3(tmax, __uint_as_float(s[j]), __uint_as_float(s[j + 1]));
                     }
                 }
                 const float m_new = fmaxf(m, tmax * sl2);                       // in units of log2
@@ -243,35 +252,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
                 const float m_sub = (m_new == -INFINITY) ? 0.f : m_new;
                 // pass 2: P = 2^(S*scale*log2e - m_new), rounded to bfloat16 as it enters the product; its row sum
                 float lsum = 0.f;
+                // (the masked form is a separate instance: in the common, unmasked one no instruction looks at
+                // keys.  With one body and the test inside it the compiler predicated the mask's compares and
+                // selects instead of branching around them, and the ALU pipe, not the exponentials, set the pace.)
+                auto pass2 = [&](auto masked_c) {
+                    constexpr bool MASKED = decltype(masked_c)::value;
 #pragma unroll 1
-                for (int c = 0; c < AT_BN; c += 32) {
-                    uint32_t s[32];
-                    kp_tmem_ld32(tmem_s + lane_off + c, s);
-                    unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
+                    for (int c = 0; c < AT_BN; c += 32) {
+                        uint32_t s[32];
+                        kp_tmem_ld32(tmem_s + lane_off + c, s);
+                        unsigned char* prow = Ps + (c >> 6) * AT_TILE_BYTES + r * 128;
 #pragma unroll
-                    for (int j8 = 0; j8 < 4; j8++) {
-                        uint32_t w[4];
+                        for (int j8 = 0; j8 < 4; j8++) {
+                            uint32_t w[4];
 #pragma unroll
-                        for (int j2 = 0; j2 < 4; j2++) {
-                            float pv[2];
+                            for (int j2 = 0; j2 < 4; j2++) {
+                                float pv[2];
 #pragma unroll
-                            for (int e = 0; e < 2; e++) {
-                                const int j = j8 * 8 + j2 * 2 + e;
-                                float pe = at_exp2(fmaf(__uint_as_float(s[j]), sl2, -m_sub));
-                                if (masked) {
-                                    const int key = kt * AT_BN + c + j;
-                                    if (!(live && key >= lo && key <= pos)) pe = 0.f;
+                                for (int e = 0; e < 2; e++) {
+                                    const int j = j8 * 8 + j2 * 2 + e;
+                                    float pe = at_exp2(fmaf(__uint_as_float(s[j]), sl2, -m_sub));
+                                    if (MASKED) {
+                                        const int key = kt * AT_BN + c + j;
+                                        if (!(live && key >= lo && key <= pos)) pe = 0.f;
+                                    }
+                                    pv[e] = pe;
                                 }
-                                pv[e] = pe;
+                                lsum += pv[0] + pv[1];
+                                const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
+                                w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
                             }
-                            lsum += pv[0] + pv[1];
-                            const __nv_bfloat162 pb = __floats2bfloat162_rn(pv[0], pv[1]);
-                            w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                            const int chunk = ((c & 63) >> 3) + j8;           // 16-byte piece of the 128-byte row
+                            *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        const int chunk = ((c & 63) >> 3) + j8;               // 16-byte piece of the 128-byte row
-                        *reinterpret_cast<uint4*>(prow + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                }
+                };
+                if (masked) pass2(std::true_type{}); else pass2(std::false_type{});
                 l = l * corr + lsum;
                 m = m_new;
                 kp_tc_fence_before();                                           // the reads of S are done
