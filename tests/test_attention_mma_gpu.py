@@ -16,14 +16,18 @@ DT = torch.bfloat16
 TOL = 1.5e-2
 
 
-@pytest.fixture(autouse=True, params=["tcgen05", "mma.sync"])
+@pytest.fixture(autouse=True, params=["tcgen05 two heads a CTA", "tcgen05 one head a CTA", "mma.sync"])
 def _both_kernels(request):
-    """Every test runs twice: with the tcgen05 kernel allowed, and with the mma.sync kernel only."""
+    """Every test runs three times: with the tcgen05 kernels allowed (two heads a CTA where the head counts
+    allow it; one head a CTA always), and with the mma.sync kernel only."""
     from kappai_b200.ops import kernels as Kn
+    from kappai_b200.ops.build import load_library
     old = Kn.USE_TC_ATTENTION
-    Kn.USE_TC_ATTENTION = request.param == "tcgen05"
+    Kn.USE_TC_ATTENTION = request.param != "mma.sync"
+    load_library("attention_tc").kp_attention_tc_set_pair(1 if "two heads" in request.param else 0)
     yield
     Kn.USE_TC_ATTENTION = old
+    load_library("attention_tc").kp_attention_tc_set_pair(1)
     assert Kn.attention_tc_status() == 0, "a bounded wait of the tcgen05 attention kernel gave up"
 
 
