@@ -116,6 +116,11 @@ class Engine:
     def has_work(self) -> bool:
         return self.scheduler.has_work()
 
+    def abort(self, request_id: Hashable) -> None:
+        """End a request now (``finish_reason`` "aborted"); what it holds is given back.  A row computed for it
+        by a step that is already under way is dropped."""
+        self.scheduler.abort(request_id)
+
     # -- one turn of the loop
     def _launch(self, plan: List[ScheduledEntry], device_tokens: Optional[torch.Tensor] = None,
                 ahead: int = 0) -> _Launched:

@@ -177,7 +177,7 @@ def test_steps_launched_ahead_change_nothing(dtype, model_dirs):
             if n == 8:
                 ids.append(eng.add_request(late, SamplingParams(temperature=0.0, n_predict=9)))
             if n == 22:
-                eng.scheduler.abort(ids[3])
+                eng.abort(ids[3])
         eng.runner.cache.check()
         assert eng.runner.cache.slots.n_free == 4
         outs = [eng.requests[i].output for i in ids]
