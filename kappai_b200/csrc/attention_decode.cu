@@ -226,7 +226,7 @@ template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                   const int* __restrict__ positions, T* __restrict__ out, int ldo, int n_chunks,
                                   int chunk_keys, int window, int H, int hd) {
-    kp_pdl_begin_early();
+    kp_pdl_begin_early_if(gridDim.y > 1);
     extern __shared__ __align__(16) float merge_sm[];       // [MERGE_BATCH], [n_chunks] l_c, [n_chunks] exp(m_c - m), [32]
     const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
     int k_lo, k_hi;

@@ -133,7 +133,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
                       int n_chunks, float scale, int window, int page_size, int H, int G,
                       int* __restrict__ counters, bf16* __restrict__ out, int ldo) {
-    kp_pdl_begin_early();
+    kp_pdl_begin_early_if(gridDim.z > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);                 // [NW][64][HD]

@@ -279,7 +279,7 @@ __global__ void shortconv_decode_kernel(const T* __restrict__ p, int ldp, const 
                                         const float* __restrict__ bias, float* __restrict__ state,
                                         const int* __restrict__ seg_pos, const int* __restrict__ seg_slot,
                                         T* __restrict__ out, int ldo, int n, int d, int K) {
-    kp_pdl_begin_early();
+    kp_pdl_begin_early_if(n > 1);
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     const int row = blockIdx.y;
     if (c >= d || row >= n) return;
