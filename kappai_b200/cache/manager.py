@@ -50,6 +50,9 @@ class PagePool:
         self._held: Dict[Hashable, int] = {}                          # pages currently held per request
         self._version: Dict[Hashable, int] = {}                       # stamp of the last change of a request's table
         self._tick = 0                                                # source of the stamps: never repeats
+        self._used_before = [False] * n_pages
+        self.n_handed_out = 0                                         # pages given to requests so far
+        self.n_reused = 0                                             # of those, pages that another table held before
 
     # -- queries
     @property
@@ -90,7 +93,11 @@ class PagePool:
             return
         t = self._tables[req]
         for _ in range(need):
-            t.append(self._free.pop())
+            page = self._free.pop()
+            self.n_handed_out += 1
+            self.n_reused += self._used_before[page]
+            self._used_before[page] = True
+            t.append(page)
         self._held[req] += need
         self._version[req] = self._stamp()
 

@@ -231,7 +231,9 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc, const floa
     const int h = blockIdx.x, row = blockIdx.y, tid = threadIdx.x, nt = blockDim.x;
     int k_lo, k_hi;
     key_range(positions[row], window, k_lo, k_hi);
-    const int c_lo = k_lo / chunk_keys, c_hi = k_hi / chunk_keys, n = c_hi - c_lo + 1;
+    // (a position beyond the chunks the caller gave is the caller's fault; the clamp keeps the reads inside
+    // the scratch and the shared arrays all the same)
+    const int c_hi = min(k_hi / chunk_keys, n_chunks - 1), c_lo = min(k_lo / chunk_keys, c_hi), n = c_hi - c_lo + 1;
     float* s_acc = merge_sm;
     float* s_l = merge_sm + MERGE_BATCH;
     float* s_w = s_l + n_chunks;

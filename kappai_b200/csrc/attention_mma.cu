@@ -124,7 +124,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[HD / 8][4], const uint32_t (&
 // head, key of the page; HD columns), one box of min(page size, 64) keys x 64 columns each, issued by one
 // thread: no address arithmetic in the other threads.  Needs a page size that divides 64 or is a multiple of
 // it, and a multiple of 8.  Boxes wholly outside the row's keys are not loaded; V rows outside them are zeroed.
-__device__ int g_attn_status = 0;                // 1: a bounded wait gave up
+KP_STATUS_WORD(g_attn_status, attention_mma)          // 0 ok; 1: a bounded wait gave up
 
 template <int HD, int NW, bool TMA>
 __global__ void __launch_bounds__(NW * 32)
@@ -542,12 +542,5 @@ int kp_attention_prefill_mma(const void* q, int ldq, const void* cache, const in
                                out, ldo, scale, window, page_size, H, G, s);
 }
 
-// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
-int kp_attention_mma_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_attn_status, &zero, sizeof(int));
-    return v;
-}
 
 }  // extern "C"

@@ -20,6 +20,10 @@
  *  - n_rows * H * n_chunks * (head_dim + 2) must not exceed
  *    KP_NOALLOC_SCRATCH_FLOATS; a larger call is refused with
  *    KP_NOALLOC_TOO_LARGE and nothing is launched.
+ *  - n_chunks (chunks of 256 keys) must reach the largest position of the
+ *    batch: positions[r] < n_chunks * 256 for every row, and the block table
+ *    must cover that position.  A row beyond it is merged from the chunks
+ *    that exist (its result is then wrong, but nothing is read out of range).
  *  - The first call on a device looks up the array's device address (one
  *    cudaGetSymbolAddress, with that device current) and keeps it.  Make that
  *    first call outside any stream capture.

@@ -35,7 +35,7 @@
 #define AT_THREADS 192
 #define AT_TILE_BYTES (128 * 64 * 2)         // a 128 x 64 bf16 tile: 16 KB
 
-__device__ int g_attn_tc_status = 0;
+KP_STATUS_WORD(g_attn_tc_status, attention_tc)          // 0 ok; 1: a bounded wait gave up
 
 __device__ __forceinline__ float at_exp2(float x) {
     float y;
@@ -656,12 +656,5 @@ int kp_attention_prefill_tc(const void* q, int ldq, int n_rows_total, const void
 // 1 (default): two heads a CTA where the head counts allow it; 0: one head a CTA always.  For measurements and tests.
 void kp_attention_tc_set_pair(int on) { g_at_pair = on ? 1 : 0; }
 
-// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
-int kp_attention_tc_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_attn_tc_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_attn_tc_status, &zero, sizeof(int));
-    return v;
-}
 
 }  // extern "C"

@@ -41,7 +41,23 @@
 #define ST_RING_BYTES (64 * 1024)            // the ring with three CTAs an SM: 7 stages of 8 rows, 3 of 2 x 8
 #define ST_RING_BYTES_FEW (88 * 1024)        // with two CTAs an SM (products with few tiles): 10 stages of 8 rows
 
-__device__ int g_stream_status = 0;          // 0 ok; 1: a bounded wait gave up
+KP_STATUS_WORD(g_stream_status, stream)          // 0 ok; 1: a bounded wait gave up
+
+// Built with -DKP_TEST_HOOKS (a library of its own that only the tests load), the kernel can be told to
+// leave one stage of its ring unfilled and to give up its waits after a shorter time, so that a test sees
+// a wait run out, the kernel return and the status word rise, with nothing faulting or hanging.
+#ifdef KP_TEST_HOOKS
+__device__ int g_test_skip_stage = -1;                     // the producer of CTA 0 never fills this stage (-1: none)
+__device__ unsigned long long g_test_wait_ns = KP_TMA_WAIT_NS;
+#define ST_WAIT_NS g_test_wait_ns
+extern "C" int kp_gemm_stream_test_fault(int skip_stage, unsigned long long wait_ns) {
+    if (cudaMemcpyToSymbol(g_test_skip_stage, &skip_stage, sizeof(int)) != cudaSuccess) return -1;
+    if (wait_ns == 0) wait_ns = KP_TMA_WAIT_NS;
+    return cudaMemcpyToSymbol(g_test_wait_ns, &wait_ns, sizeof(wait_ns)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define ST_WAIT_NS KP_TMA_WAIT_NS
+#endif
 
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -128,11 +144,17 @@ gemm_stream_kernel(const StreamArgs p) {
                 const int s = it % S;
                 int ok = 1;
                 if (lane == 0) {
-                    ok = kp_mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1) ? 1 : 0;
-                    if (ok) kp_mbar_expect_tx(&full[s], ROWS * ST_COLS * 2);
+                    ok = kp_mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1, ST_WAIT_NS) ? 1 : 0;
+#ifdef KP_TEST_HOOKS
+                    if (ok && blockIdx.x == 0 && it == g_test_skip_stage) ok = 2;      // stage left unfilled
+#endif
+                    if (ok == 1) kp_mbar_expect_tx(&full[s], ROWS * ST_COLS * 2);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { alive = false; break; }
+#ifdef KP_TEST_HOOKS
+                if (ok == 2) continue;
+#endif
                 if (lane < ROWS)
                     bulk_g2s(ring + (size_t)s * STAGE_BYTES + (size_t)lane * ST_ROW_BYTES, src + (size_t)c * ST_COLS,
                              ST_COLS * 2, &full[s]);
@@ -207,7 +229,7 @@ gemm_stream_kernel(const StreamArgs p) {
         auto run_stage = [&](int c, auto slot0) {
             constexpr int SLOT0 = decltype(slot0)::value;
             const int s = it % S;
-            if (alive && !kp_mbar_wait_bounded(&full[s], (it / S) & 1)) alive = false;
+            if (alive && !kp_mbar_wait_bounded(&full[s], (it / S) & 1, ST_WAIT_NS)) alive = false;
             const unsigned char* stage = ring + (size_t)s * STAGE_BYTES + 16 * t;
 #pragma unroll
             for (int j = 0; j < 2; j++) {
@@ -272,7 +294,10 @@ gemm_stream_kernel(const StreamArgs p) {
         }
         consumer_sync();                                                 // red is free for the next tile
     }
-    if (!alive && lane == 0) atomicExch(&g_stream_status, 1);
+    if (!alive) {
+        if (lane == 0) atomicExch(&g_stream_status, 1);
+        kp_linger_after_failure();
+    }
 }
 
 static size_t smem_bytes(int NW, int MT, int n_stages) {
@@ -381,12 +406,5 @@ int kp_gemm_stream_norm(const float* X, int ldx, const float* norm_w, float eps,
     return launch_m<true>(a, epi, (cudaStream_t)stream);
 }
 
-// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
-int kp_stream_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_stream_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_stream_status, &zero, sizeof(int));
-    return v;
-}
 
 }  // extern "C"

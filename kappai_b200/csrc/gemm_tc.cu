@@ -40,7 +40,7 @@
 #define TC_EPI_PER_Q 2                       // epilogue warps for each quarter of the tensor-memory lanes
 #define TC_THREADS (64 + TC_EPI_PER_Q * 128) // the producer warp, the MMA warp and the epilogue warps
 
-__device__ int g_tc_status = 0;
+KP_STATUS_WORD(g_tc_status, tc)          // 0 ok; 1: a bounded wait gave up
 
 struct TcArgs {
     const float* bias;
@@ -338,12 +338,5 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
 
 void kp_gemm_tc_set_smem_kb(int kb) { g_tc_smem_kb = kb < 64 ? 64 : (kb > 216 ? 216 : kb); }
 
-// Reads (and clears) the status word: 0 ok, 1 if a bounded wait gave up since the last call.  Synchronises.
-int kp_tc_status(void) {
-    int v = 0, zero = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
-    return v;
-}
 
 }  // extern "C"

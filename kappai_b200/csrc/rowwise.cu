@@ -193,6 +193,18 @@ static inline int grid_for(size_t total, int block) {
     return (int)g;
 }
 
+// The status words of a step's kernels brought together: out[0] = OR of the words at the given device
+// addresses.  Launched behind a step; its one word travels to the host with the step's sampled tokens, so the
+// host learns without any further synchronisation whether a kernel's bounded wait gave up.
+__global__ void gather_status_kernel(const unsigned long long* __restrict__ addrs, int n, int* __restrict__ out) {
+    kp_pdl_begin();
+    if (threadIdx.x == 0) {
+        int v = 0;
+        for (int i = 0; i < n; i++) v |= *reinterpret_cast<const volatile int*>(addrs[i]);
+        out[0] = v;
+    }
+}
+
 extern "C" {
 
 int kp_embed_rows(const void* table, const int* ids, float* x, int n, int d, float scale, int dtype, void* stream) {
@@ -241,6 +253,12 @@ int kp_cast(const void* in, void* out, long long n, int dtype_in, int dtype_out,
         kp_launch_pdl(cast_kernel<bf16, float>, dim3(g), dim3(256), 0, s, (const bf16*)in, (float*)out, (size_t)n);
     else
         return KP_ERR_BAD_ARG;
+    return kp_launch_status();
+}
+
+int kp_gather_status(const unsigned long long* addrs, int n, int* out, void* stream) {
+    if (n < 0 || !out) return KP_ERR_BAD_ARG;
+    kp_launch_pdl(gather_status_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, addrs, n, out);
     return kp_launch_status();
 }
 

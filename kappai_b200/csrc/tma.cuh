@@ -33,17 +33,41 @@ __device__ __forceinline__ unsigned long long kp_now_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// false if the barrier did not flip within KP_TMA_WAIT_NS
-__device__ __forceinline__ bool kp_mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// false if the barrier did not flip within limit_ns
+__device__ __forceinline__ bool kp_mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                     unsigned long long limit_ns = KP_TMA_WAIT_NS) {
     if (kp_mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = kp_now_ns();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 64; i++)
             if (kp_mbar_try_wait(bar, parity)) return true;
-        if (kp_now_ns() - t0 > KP_TMA_WAIT_NS) return false;
+        if (kp_now_ns() - t0 > limit_ns) return false;
     }
 }
+// A CTA that gave up a wait must not leave while bulk copies into its shared memory may still be under way
+// (the memory could be handed to the next CTA meanwhile): it lingers for a moment that is far longer than any
+// copy takes.  Only the failure path comes here.
+__device__ __forceinline__ void kp_linger_after_failure() {
+    const unsigned long long t0 = kp_now_ns();
+    while (kp_now_ns() - t0 < 200000ull) __nanosleep(1000);
+}
+
+// The status word of a library whose kernels wait with a limit: 0, or 1 once a wait has given up.
+//   kp_<name>_status()          reads and clears it (synchronises the device);
+//   kp_<name>_status_address()  its device address, for a kernel that collects the status words of a step.
+#define KP_STATUS_WORD(var, name)                                                                     \
+    __device__ int var = 0;                                                                           \
+    extern "C" int kp_##name##_status(void) {                                                         \
+        int v = 0, zero = 0;                                                                          \
+        if (cudaMemcpyFromSymbol(&v, var, sizeof(int)) != cudaSuccess) return -1;                     \
+        if (v) cudaMemcpyToSymbol(var, &zero, sizeof(int));                                           \
+        return v;                                                                                     \
+    }                                                                                                 \
+    extern "C" void* kp_##name##_status_address(void) {                                               \
+        void* p = nullptr;                                                                            \
+        return cudaGetSymbolAddress(&p, var) == cudaSuccess ? p : nullptr;                            \
+    }
 // box of the 2-D tensor at (x, y) -> shared memory; x * element size must be a multiple of 16 bytes
 __device__ __forceinline__ void kp_tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

@@ -65,34 +65,50 @@ class StepContext:
     max_seg_len: int
     max_context: int               # largest position + 1 in the batch
     decode_only: bool              # every segment has one row
-    tile_seg: Optional[torch.Tensor] = None    # int32 [n_tiles]: segment of each tile of ROW_TILE consecutive rows
-    tile_row0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first row of each tile
-    n_tiles: int = 0
-    # the same in stretches of BIG_TILE rows, those that read the most keys first (a kernel that gives a CTA the
-    # i-th and the i-th last of them gives every CTA about the same work)
-    big_tile_seg: Optional[torch.Tensor] = None
-    big_tile_row0: Optional[torch.Tensor] = None
-    n_big_tiles: int = 0
-    # A step that mixes decoded tokens with prompt portions: the leading segments of at most SHORT_SEG rows
-    # (the scheduler puts decodes first) can go to a kernel made for single rows with long caches and the rest
-    # to a tiled one.  n_short_rows / n_short_tiles: rows and ROW_TILE tiles of that lead (0 if the step is not
-    # mixed in this way); the big tiles then list the other segments only.
-    n_short_rows: int = 0
-    n_short_tiles: int = 0
+    # tables that parts asked for through ``step_tables`` (see parts.base.Part): key -> namespace whose
+    # attributes are the part's int32 arrays on the device and its host scalars
+    tables: Dict[Hashable, object] = field(default_factory=dict)
 
 
-BIG_TILE = 128                     # rows of the larger tiles
-SHORT_SEG = 4                      # rows up to which a segment counts as short (decoded tokens)
-ROW_TILE = 64                      # rows of one segment that a tiled kernel (prefill attention) takes at a time
+@dataclass
+class StepSegments:
+    """The host's view of a step's segments, handed to the parts' ``step_tables``."""
+
+    n_rows: int
+    n_seg: int
+    cu_rows: np.ndarray            # int32 [n_seg + 1]
+    seg_pos: np.ndarray            # int32 [n_seg]
+    seg_len: List[int]
+    max_seg_len: int
+    decode_only: bool
+
+
+@dataclass
+class PartTables:
+    """What a part's ``step_tables`` returns: int32 arrays that go to the device with the step's one upload,
+    and host values (sizes, counts) that stay on the host."""
+
+    arrays: Dict[str, np.ndarray] = field(default_factory=dict)
+    scalars: Dict[str, int] = field(default_factory=dict)
+
+
+class _Tables:
+    """Attribute access to one part's tables of a step."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
 
 
 def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int], device: torch.device,
-                       vocab_size: int, max_positions: int) -> StepContext:
+                       vocab_size: int, max_positions: int, table_builders: Optional[Dict[Hashable, object]] = None
+                       ) -> StepContext:
     """Validate the segments on the host and upload their tables in one copy.
 
     ``groups`` maps each page group to its page size.  Everything that could
     make a kernel read or write out of bounds is refused here, before any
     launch (token ids: src/context.c:866-867; positions: src/context.c:998-999).
+    ``table_builders`` maps a key to a part whose ``step_tables(StepSegments)``
+    adds tables of its own to the upload (tile lists, scan boundaries, ...).
     """
     if not segments:
         raise BatchError("a step needs at least one segment")
@@ -136,28 +152,19 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
     if len(set(seg_slot.tolist())) != n_seg:
         raise BatchError("two segments of one step name the same state slot")
 
-    tile_seg, tile_row0 = [], []
-    for i in range(n_seg):
-        for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), ROW_TILE):
-            tile_seg.append(i)
-            tile_row0.append(r0)
-    n_short_seg = 0
-    while n_short_seg < n_seg and len(segments[n_short_seg].tokens) <= SHORT_SEG:
-        n_short_seg += 1
-    if n_short_seg == n_seg or all(len(s.tokens) > SHORT_SEG for s in segments):
-        n_short_seg = 0                                   # all short or none: one kernel takes the whole step
-    n_short_rows = int(cu_rows[n_short_seg])
-    big = []
-    for i in range(n_short_seg, n_seg):
-        for r0 in range(int(cu_rows[i]), int(cu_rows[i + 1]), BIG_TILE):
-            last_pos = int(seg_pos[i]) + min(r0 + BIG_TILE, int(cu_rows[i + 1])) - int(cu_rows[i]) - 1
-            big.append((-last_pos, i, r0))                # the further on, the more keys
-    big.sort()
-    parts = [token_ids, positions, row_seg, cu_rows, seg_pos, seg_slot,
-             np.asarray(logit_rows, dtype=np.int32), np.asarray(tile_seg, dtype=np.int32),
-             np.asarray(tile_row0, dtype=np.int32), np.asarray([b[1] for b in big], dtype=np.int32),
-             np.asarray([b[2] for b in big], dtype=np.int32)]
-    n_fixed = len(parts)
+    parts = [token_ids, positions, row_seg, cu_rows, seg_pos, seg_slot, np.asarray(logit_rows, dtype=np.int32)]
+    seg_len = [len(s.tokens) for s in segments]
+    host_segs = StepSegments(n_rows, n_seg, cu_rows, seg_pos, seg_len, max(seg_len), all(n == 1 for n in seg_len))
+    part_tables = []                                   # (key, [(name, index into parts)], scalars)
+    for key, builder in (table_builders or {}).items():
+        t = builder.step_tables(host_segs)
+        if t is None:
+            continue
+        names = []
+        for name, arr in t.arrays.items():
+            names.append((name, len(parts)))
+            parts.append(np.ascontiguousarray(arr, dtype=np.int32).reshape(-1))
+        part_tables.append((key, names, dict(t.scalars)))
     paged_host = {}
     for gk, page_size in groups.items():
         max_blocks = max(1, max(len(s.block_tables.get(gk, ())) for s in segments))
@@ -192,16 +199,15 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
     paged = {}
     for gk, (i, shape, page_size) in paged_host.items():
         paged[gk] = PagedView(piece(i).view(shape), piece(i + 1), page_size)
+    tables = {key: _Tables(**{name: piece(i) for name, i in names}, **scalars)
+              for key, names, scalars in part_tables}
     ctx = StepContext(
         n_rows=n_rows, n_seg=n_seg, token_ids=piece(0), positions=piece(1), row_seg=piece(2), cu_rows=piece(3),
         seg_pos=piece(4), seg_slot=piece(5), logit_rows=piece(6), n_out=len(logit_rows), paged=paged,
         host_cu_rows=cu_rows.tolist(), host_seg_pos=seg_pos.tolist(), host_seg_slot=seg_slot.tolist(),
-        max_seg_len=max(len(s.tokens) for s in segments),
+        max_seg_len=host_segs.max_seg_len,
         max_context=max(s.pos_start + len(s.tokens) for s in segments),
-        decode_only=all(len(s.tokens) == 1 for s in segments),
-        tile_seg=piece(7), tile_row0=piece(8), n_tiles=len(tile_seg),
-        big_tile_seg=piece(9), big_tile_row0=piece(10), n_big_tiles=len(big),
-        n_short_rows=n_short_rows, n_short_tiles=n_short_seg)
+        decode_only=host_segs.decode_only, tables=tables)
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
     ctx.h2d_bytes = flat.numel() * 4
     return ctx

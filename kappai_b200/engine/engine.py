@@ -18,7 +18,8 @@ import torch
 from ..sampling.params import SamplingParams
 from ..sampling.rng import resolve_seed
 from ..sampling.sampler import sample
-from .runner import ModelRunner, StepEntry
+from ..ops import kernels as K
+from .runner import EngineError, ModelRunner, StepEntry
 from .scheduler import RUNNING, Request, ScheduledEntry, Scheduler
 
 
@@ -34,7 +35,7 @@ class EngineArgs:
     max_batch: int = 64                # requests that run together (state slots)
     max_step_tokens: int = 2048        # token budget of one step
     page_size: int = 64
-    kv_tokens: int = 0                 # tokens the page pools hold (0: max_batch * ctx_size, capped by memory)
+    kv_tokens: int = 0                 # tokens the page pools hold (0: max_batch * ctx_size, or what fits beside the weights)
     device: str = "cuda:0"
     look_ahead: bool = True            # launch the next decode step before the last one's tokens are read
 
@@ -56,7 +57,7 @@ class _Launched:
     plan: List[ScheduledEntry]
     got: List[Request]                         # the requests that sample in it, in the order of ``tokens``
     tokens: Optional[torch.Tensor]             # their new tokens on the device (int32)
-    host: Optional[torch.Tensor]               # the pinned buffer the tokens are copied to
+    host: torch.Tensor                         # the pinned buffer the tokens and the status word are copied to
     done: torch.cuda.Event                     # recorded behind that copy
 
 
@@ -71,16 +72,20 @@ class Engine:
     under way, none has a repeat penalty (which reads the token history on the host), and pages for the next
     token are there without preempting anyone."""
 
-    def __init__(self, args: EngineArgs):
-        from ..config.registry import load_config
+    def __init__(self, args: EngineArgs, free_memory=None):
+        from ..ops.kernels import MAX_STEP_ROWS
+        from .runner import EngineError
 
         self.args = args
-        _, cfg = load_config(args.model)
-        arch_ctx = getattr(cfg, "max_position_embeddings", None) or 4096
-        ctx_size = min(args.ctx_size or arch_ctx, arch_ctx)         # src/context.c:465-470
-        kv_tokens = args.kv_tokens or min(args.max_batch * ctx_size, 1 << 22)
-        self.runner = ModelRunner(args.model, dtype=args.dtype, max_tokens=kv_tokens, max_requests=args.max_batch,
-                                  page_size=args.page_size, max_model_len=ctx_size, device=args.device)
+        if not (1 <= args.max_step_tokens <= MAX_STEP_ROWS):
+            raise EngineError(f"max_step_tokens={args.max_step_tokens}: a step takes 1 to {MAX_STEP_ROWS} tokens")
+        if args.max_batch < 1 or args.ctx_size < 0 or args.kv_tokens < 0:
+            raise EngineError("max_batch must be positive; ctx_size and kv_tokens must not be negative")
+        # the longest sequence is the model's own limit unless ctx_size asks for less (src/context.c:465-470);
+        # the pools hold kv_tokens, or what max_batch requests of that length need, or what fits beside the weights
+        self.runner = ModelRunner(args.model, dtype=args.dtype, max_tokens=args.kv_tokens, max_requests=args.max_batch,
+                                  page_size=args.page_size, max_model_len=args.ctx_size or None, device=args.device,
+                                  max_step_tokens=args.max_step_tokens, free_memory=free_memory)
         self.scheduler = Scheduler(self.runner.cache, args.max_step_tokens, args.max_batch,
                                    self.runner.max_model_len, self.runner.spec.eos_token_id)
         self.requests: Dict[Hashable, Request] = {}
@@ -88,10 +93,12 @@ class Engine:
         self.stats = StepStats()
         self._launched: Optional[_Launched] = None          # a step launched ahead by the last call of step()
         # two pinned buffers for sampled tokens: one is read while the step ahead fills the other
-        self._token_staging = [torch.empty(max(args.max_batch, 1), dtype=torch.int32, pin_memory=True)
+        # (one more element than tokens: the step's status word travels with them)
+        self._token_staging = [torch.empty(max(args.max_batch, 1) + 1, dtype=torch.int32, pin_memory=True)
                                for _ in range(2)]
         self._staging_turn = 0
         self.n_launched_ahead = 0
+        self.status = K.StatusGather(self.runner.device)
 
     @property
     def vocab_size(self) -> int:
@@ -133,15 +140,19 @@ class Engine:
             entries.append(StepEntry(e.request.id, toks, [e.n - 1] if e.sample else []))
         logits = self.runner.step(entries, device_tokens=device_tokens)
         got = [e.request for e in plan if e.sample]
-        toks = host = None
+        n = len(got)
+        # the new tokens and, behind them, one word that says whether a kernel of the step gave up a wait
+        buf = torch.empty(n + 1, dtype=torch.int32, device=self.runner.device)
+        toks = None
         if got:
             # the token history only where a repeat penalty reads it
             recent = [r.tokens for r in got] if any(r.params.repeat_penalty != 1.0 for r in got) else None
             toks = sample(logits, [r.params for r in got], [r.seed for r in got],
-                          [len(r.output) + ahead for r in got], recent)
-            host = self._token_staging[self._staging_turn]
-            self._staging_turn ^= 1
-            host[:len(got)].copy_(toks, non_blocking=True)
+                          [len(r.output) + ahead for r in got], recent, out=buf[:n])
+        self.status.gather(buf[n:])
+        host = self._token_staging[self._staging_turn]
+        self._staging_turn ^= 1
+        host[:n + 1].copy_(buf, non_blocking=True)
         done = torch.cuda.Event()
         done.record()
         return _Launched(plan, got, toks, host, done)
@@ -179,7 +190,9 @@ class Engine:
             cur = self._launch(plan)
         ahead = self._launch_ahead(cur)
         cur.done.synchronize()                                       # the step's one device-to-host read
-        new = cur.host[:len(cur.got)].tolist() if cur.got else []
+        new = cur.host[:len(cur.got) + 1].tolist()
+        if new.pop():
+            self._compute_failed(cur, ahead)
         plan = [e for e in cur.plan if e.request.state == RUNNING]   # without those that ended meanwhile
         sampled = {r.id: t for r, t in zip(cur.got, new)}
         n_prompt = sum(e.n for e in plan if e.n > 1 or not e.request.output)
@@ -197,6 +210,20 @@ class Engine:
         st.prompt_tokens += n_prompt
         st.decode_tokens += len(got)
         return got
+
+    def _compute_failed(self, cur: _Launched, ahead: Optional[_Launched]) -> None:
+        """A kernel of the step gave up a bounded wait (src/context.c:1580-1592: a compute failure ends the
+        session): what the step computed cannot be trusted, nor what a step launched ahead made of it.  Their
+        requests end with ``compute_failed``, pages and slots return, the status words are cleared, and the
+        caller is told.  Requests that were not in the step go on."""
+        if ahead is not None:
+            ahead.done.synchronize()
+        what = self.status.clear()
+        reqs = {id(e.request): e.request for l in (cur, ahead) if l is not None for e in l.plan}
+        self.scheduler.fail(list(reqs.values()))
+        self.stats.n_steps += 1
+        raise EngineError("a kernel's bounded wait gave up (" + ", ".join(sorted(what)) + "): the step's requests "
+                          + ", ".join(repr(r.id) for r in reqs.values()) + " ended with compute_failed")
 
     # -- whole generations
     def generate(self, prompts: Sequence[Sequence[int]], params=None,

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..ops import kernels as K
-from .batch import PagedView, StepContext
+from .batch import PagedView, StepContext, StepSegments, _Tables
 
 N_PINNED = 4          # staging buffers in rotation, so a refill never overtakes a copy in flight
 
@@ -44,6 +44,21 @@ class _DecodeGraph:
             off += _align4(n)
             self.off[("block_table", gk)] = off
             off += _align4(n * width)
+        # tables of their own that parts build for every step: laid out once from a step of this shape (their
+        # sizes may depend on the number of requests only) and refilled before every replay
+        self.builders = dict(runner.model.table_builders)
+        self.part_layout = {}                      # key -> ([(name, offset, size)], scalars)
+        segs0 = self._segments([0] * n)
+        for key, b in self.builders.items():
+            t = b.step_tables(segs0)
+            if t is None:
+                continue
+            pieces = []
+            for name, arr in t.arrays.items():
+                arr = np.asarray(arr, dtype=np.int32).reshape(-1)
+                pieces.append((name, off, arr.size))
+                off += _align4(arr.size)
+            self.part_layout[key] = (pieces, dict(t.scalars))
         self.size = off
         self.dev = torch.zeros(off, dtype=torch.int32, device=dev)
         self.pinned = [torch.zeros(off, dtype=torch.int32, pin_memory=True) for _ in range(N_PINNED)]
@@ -71,11 +86,29 @@ class _DecodeGraph:
             row_seg=piece("row_seg", n), cu_rows=piece("cu_rows", n + 1), seg_pos=piece("seg_pos", n),
             seg_slot=piece("seg_slot", n), logit_rows=piece("logit_rows", n), n_out=n, paged=paged,
             host_cu_rows=list(range(n + 1)), host_seg_pos=[0] * n, host_seg_slot=[0] * n,
-            max_seg_len=1, max_context=max_ctx, decode_only=True)
+            max_seg_len=1, max_context=max_ctx, decode_only=True,
+            tables={key: _Tables(**{name: self.dev[o:o + m] for name, o, m in pieces}, **scalars)
+                    for key, (pieces, scalars) in self.part_layout.items()})
         self.ctx.h2d_bytes = off * 4
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.n_kernels = 0
+
+    def _segments(self, lens) -> StepSegments:
+        n = self.n
+        return StepSegments(n, n, np.arange(n + 1, dtype=np.int32), np.asarray(lens, dtype=np.int32), [1] * n, 1, True)
+
+    def _fill_part_tables(self, lens) -> None:
+        segs = self._segments(lens)
+        for key, (pieces, scalars) in self.part_layout.items():
+            t = self.builders[key].step_tables(segs)
+            if t is None or dict(t.scalars) != scalars or set(t.arrays) != {p[0] for p in pieces}:
+                raise RuntimeError(f"step tables {key!r}: a captured decode step needs the same tables every step")
+            for name, o, m in pieces:
+                arr = np.asarray(t.arrays[name], dtype=np.int32).reshape(-1)
+                if arr.size != m:
+                    raise RuntimeError(f"step tables {key!r}: '{name}' changed its size in a captured decode step")
+                self.host[o:o + m] = arr
 
     def fill(self, runner, reqs: Sequence[Hashable], tokens: Optional[Sequence[int]]) -> None:
         """Write this step's tables into the next staging buffer and start its copy."""
@@ -104,6 +137,8 @@ class _DecodeGraph:
                     bt[j, len(t):] = 0
                     keys[j] = key
                 sm[j] = t[lens[j] // ps] * ps + lens[j] % ps
+        if self.part_layout:
+            self._fill_part_tables(lens)
         np.copyto(self.pinned_np[i], a)
         self.dev.copy_(self.pinned[i], non_blocking=True)
         ev = self.events[i] or torch.cuda.Event()

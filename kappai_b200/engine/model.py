@@ -41,6 +41,13 @@ class Model:
             parts += [b, b.mixer, b.ffn, b.mixer_norm, b.ffn_norm]
         # a decode step may be captured in a CUDA graph only if every part reads its tables from the device
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts if p is not None)
+        # parts that build tables of their own for every step, one builder per key
+        self.table_builders: Dict[object, Part] = {}
+        for p in parts:
+            for q in (p, getattr(p, "position", None)):
+                key = getattr(q, "step_tables_key", None)
+                if key is not None and key not in self.table_builders:
+                    self.table_builders[key] = q
 
     def _make(self, category: str, ps: PartSpec) -> Part:
         part = make_part(category, ps, self.env)

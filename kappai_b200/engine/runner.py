@@ -26,7 +26,10 @@ from ..config.registry import load_config
 from ..parts.base import BuildEnv
 from ..weights.loader import load_weights
 from .batch import Segment, StepContext, build_step_context
+from ..ops import kernels as K
+from ..ops.kernels import MAX_STEP_ROWS
 from .graphs import DecodeGraphs
+from .memory import CacheMemoryError, GroupNeed, plan_cache
 from .model import Model
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -55,11 +58,19 @@ def require_cuda(device) -> torch.device:
 class ModelRunner:
     def __init__(self, model_dir: str, dtype: str = "bfloat16", max_tokens: int = 4096,
                  max_requests: int = 4, page_size: int = 64, max_model_len: Optional[int] = None,
-                 device="cuda:0", cuda_graphs: bool = True):
+                 device="cuda:0", cuda_graphs: bool = True, max_step_tokens: Optional[int] = None,
+                 free_memory=None):
         """``max_tokens``: how many tokens the live requests may hold together,
         each request's count rounded up to a whole page; the page pools are
-        made for exactly this many.  ``max_requests``: state slots.
-        ``cuda_graphs``: replay decode steps from captured CUDA graphs."""
+        made for exactly this many, or the runner refuses to start if the device
+        has no room for them.  0: room for ``max_requests`` requests of
+        ``max_model_len`` tokens, or as much of that as fits beside the weights.
+        ``max_requests``: state slots.  ``cuda_graphs``: replay decode steps
+        from captured CUDA graphs.  ``max_step_tokens``: the most tokens a
+        request gets in one step, if the caller keeps such a limit: pools of
+        windowed page groups are then made no larger than the windows need.
+        ``free_memory``: a function that returns the device's free bytes (for
+        tests; by default the device is asked)."""
         if dtype not in DTYPES:
             raise EngineError(f"dtype '{dtype}': expected bfloat16 or float32")
         self.device = require_cuda(device)
@@ -68,22 +79,39 @@ class ModelRunner:
         self.spec = self.arch.build_spec(self.config)
         if page_size < 1:
             raise EngineError("page_size must be positive")
+        if max_tokens < 0 or max_requests < 1:
+            raise EngineError("max_tokens must not be negative and max_requests must be positive")
         self.page_size = page_size
-        n_pages = max(1, -(-max_tokens // page_size))
-        self.max_model_len = min(self.spec.max_positions, max_model_len or n_pages * page_size)
+        limit = max_model_len or (-(-max_tokens // page_size) * page_size if max_tokens else self.spec.max_positions)
+        self.max_model_len = min(self.spec.max_positions, limit)
         torch.cuda.set_device(self.device)
         env = BuildEnv(self.device, self.dtype, self.max_model_len)
         self.model = Model(self.spec, env)
         load_weights(self.model, model_dir)
         specs = self.model.cache_specs()
         borrowing = self.model.cache_borrowing()
-        group_keys = []
+        elt = torch.empty((), dtype=self.dtype).element_size()
+        needs: Dict[Hashable, GroupNeed] = {}
+        state_bytes = 0
         for s in specs:
-            if isinstance(s, PagedKVSpec) and s.group_key not in group_keys:
-                group_keys.append(s.group_key)
-        self.storage = CacheStorage(specs, borrowing, {gk: n_pages for gk in group_keys}, page_size,
-                                    max_requests, self.dtype, self.device)
-        self.cache = CacheManager({gk: (n_pages, page_size, self.storage.groups[gk].window)
+            if isinstance(s, PagedKVSpec):
+                g = needs.setdefault(s.group_key, GroupNeed(s.group_key, 0, s.window))
+                g.bytes_per_token += 2 * s.num_kv_heads * s.head_dim * elt
+            elif isinstance(s, StateSpec):
+                n = 1
+                for d in s.shape:
+                    n *= d
+                state_bytes += n * torch.empty((), dtype=getattr(torch, s.dtype)).element_size()
+        free = free_memory() if free_memory is not None else torch.cuda.mem_get_info(self.device)[0]
+        try:
+            plan = plan_cache(list(needs.values()), state_bytes, max_requests, page_size, self.max_model_len,
+                              max_tokens, free, max_step_tokens)
+        except CacheMemoryError as e:
+            raise EngineError(str(e)) from None
+        self.cache_plan = plan
+        group_keys = list(needs)
+        self.storage = CacheStorage(specs, borrowing, plan.pages, page_size, max_requests, self.dtype, self.device)
+        self.cache = CacheManager({gk: (plan.pages[gk], page_size, self.storage.groups[gk].window)
                                    for gk in group_keys}, max_requests)
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
@@ -109,11 +137,22 @@ class ModelRunner:
             return False
         return all(-(-n_new // p.page_size) <= p.n_free for p in self.cache.pools.values())
 
+    def check_status(self) -> None:
+        """Wait for the device and raise if a kernel gave up a bounded wait since the last check (its output
+        is then not to be trusted).  The status words are cleared."""
+        bad = sorted(k for k, v in K.read_status().items() if v)
+        if bad:
+            raise EngineError("a kernel's bounded wait gave up (" + ", ".join(bad) + "): the results of the "
+                              "steps since the last check are not valid")
+
     # -- the step
     def _reserve(self, entries: Sequence[StepEntry]) -> List[Tuple[Hashable, int, int]]:
         """Admit new requests and take pages for every entry's new tokens.
         Returns (request, length before, length after) per entry.  Nothing is
         kept of a new request if any entry cannot be served."""
+        n_rows = sum(len(e.tokens) for e in entries)
+        if n_rows > MAX_STEP_ROWS:
+            raise EngineError(f"a step of {n_rows} tokens exceeds the kernels' limit of {MAX_STEP_ROWS} rows a step")
         admitted = []
         try:
             plan = []
@@ -151,7 +190,8 @@ class ModelRunner:
                 block_tables={gk: self.cache.block_table(req, gk) for gk in self.group_page_size},
                 token_slots={gk: self.cache.token_slots(req, gk, old_len, len(e.tokens))
                              for gk in self.group_page_size}))
-        ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len)
+        ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len,
+                                 self.model.table_builders)
         return ctx, [(req, new_len) for req, _, new_len in plan]
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:

@@ -35,8 +35,8 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
-FINISH_EOS, FINISH_LENGTH, FINISH_CONTEXT, FINISH_OOM, FINISH_ABORT = (
-    "eos", "length", "context_full", "out_of_memory", "aborted")
+FINISH_EOS, FINISH_LENGTH, FINISH_CONTEXT, FINISH_OOM, FINISH_ABORT, FINISH_COMPUTE = (
+    "eos", "length", "context_full", "out_of_memory", "aborted", "compute_failed")
 
 
 @dataclass
@@ -116,6 +116,15 @@ class Scheduler:
                 r.state, r.finish_reason = FINISHED, FINISH_ABORT
                 self.finished.append(r)
                 return
+
+    def fail(self, requests, reason: str = FINISH_COMPUTE) -> None:
+        """A step's kernels failed: its requests end with ``reason`` and what they hold is given back (the
+        reference ends a session whose compute failed, src/context.c:1580-1592,1676-1680)."""
+        for r in requests:
+            if r.state != FINISHED:
+                if r in self.waiting:
+                    self.waiting.remove(r)
+                self._finish(r, reason)
 
     # -- one step's plan
     def schedule(self) -> List[ScheduledEntry]:

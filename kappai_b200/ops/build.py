@@ -113,17 +113,24 @@ def _pick_build_dir() -> str:
     raise KernelBuildError("no writable folder for built kernels (set KAPPAI_B200_BUILD_DIR)")
 
 
-def library_path(name: str, extra_flags: Optional[List[str]] = None) -> str:
+def _stem(name: str, variant: str) -> str:
+    return f"lib{name}.{variant}" if variant else f"lib{name}"
+
+
+def library_path(name: str, extra_flags: Optional[List[str]] = None, variant: str = "") -> str:
     src = os.path.join(CSRC_DIR, name + ".cu")
     if not os.path.isfile(src):
         raise KernelBuildError(f"no kernel source {src}")
-    return os.path.join(build_dir(), f"lib{name}-{_digest(src, extra_flags or [])}.so")
+    return os.path.join(build_dir(), f"{_stem(name, variant)}-{_digest(src, extra_flags or [])}.so")
 
 
-def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose: bool = True) -> str:
-    """Compile ``csrc/<name>.cu`` if its built library is missing; return the path."""
+def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose: bool = True,
+                    variant: str = "") -> str:
+    """Compile ``csrc/<name>.cu`` if its built library is missing; return the path.
+    ``variant`` names a second build of the same source with ``extra_flags``
+    (its own file beside the ordinary one)."""
     extra_flags = extra_flags or []
-    out = library_path(name, extra_flags)
+    out = library_path(name, extra_flags, variant)
     if os.path.isfile(out):
         return out
     nvcc = _find_nvcc()
@@ -162,7 +169,7 @@ def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose:
             os.replace(tmp, out)
             # libraries of earlier versions of this source are of no use any more (a process that still has
             # one loaded keeps its mapping)
-            prefix = f"lib{name}-"
+            prefix = _stem(name, variant) + "-"
             for f in os.listdir(os.path.dirname(out)):
                 if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
                     try:
@@ -181,21 +188,26 @@ def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose:
                 pass
 
 
-def load_library(name: str) -> ctypes.CDLL:
+def load_library(name: str, variant: str = "", extra_flags: Optional[List[str]] = None) -> ctypes.CDLL:
     """The loaded library ``name``; compiled first if need be."""
-    lib = _loaded.get(name)
+    key = f"{name}.{variant}" if variant else name
+    lib = _loaded.get(key)
     if lib is not None:
         return lib
     with _lock:
-        lib = _loaded.get(name)
+        lib = _loaded.get(key)
         if lib is None:
-            path = compile_library(name)
+            path = compile_library(name, extra_flags, variant=variant)
             try:
                 lib = ctypes.CDLL(path)
             except OSError as e:
                 raise KernelBuildError(f"cannot load {path}: {e}") from None
-            _loaded[name] = lib
+            _loaded[key] = lib
     return lib
+
+
+def is_loaded(name: str) -> bool:
+    return name in _loaded
 
 
 def build_all(verbose: bool = True, jobs: int = 4) -> List[str]:

@@ -11,13 +11,16 @@ from typing import Optional
 
 import torch
 
-from .build import load_library
+from .build import is_loaded, load_library
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_ACCUM_F32 = 0, 1, 2
 
 
+MAX_STEP_ROWS = 65535     # rows of one step: the row-wise kernels put rows on a grid axis that ends there
+
 LAUNCHES = [0]      # kernel launchers called so far (a launcher may launch more than one kernel)
+LAUNCHES_BY = {}    # the same by launcher name
 
 
 class KernelError(RuntimeError):
@@ -59,6 +62,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
 
 def _check(status: int, what: str) -> None:
     LAUNCHES[0] += 1
+    LAUNCHES_BY[what] = LAUNCHES_BY.get(what, 0) + 1
     if status != 0:
         if status == -95:
             raise KernelError(f"{what}: size not supported by this kernel")
@@ -72,6 +76,84 @@ def _rows_2d(t: torch.Tensor, name: str) -> int:
     if t.dim() != 2 or t.stride(1) != 1:
         raise KernelError(f"{name}: expected a 2-D tensor with contiguous rows")
     return t.stride(0)
+
+
+# --------------------------------------------------------------- status words
+# Kernels that wait on a barrier wait with a limit; one that gives up sets its library's status word, stops
+# issuing work and returns.  The engine reads the words of a step with the step's own device-to-host copy.
+
+_STATUS_LIBS = (("gemm_tc", "tc"), ("gemm_stream", "stream"), ("attention_mma", "attention_mma"),
+                ("attention_tc", "attention_tc"))
+
+
+def read_status() -> dict:
+    """Library -> status word (0, or 1 if a bounded wait gave up since the last call) of every kernel library
+    that is loaded and has one; the words are cleared.  Synchronises the device."""
+    return {lib: _read_one(lib, name) for lib, name in _STATUS_LIBS if is_loaded(lib)}
+
+
+def _read_one(lib: str, name: str) -> int:
+    return int(getattr(load_library(lib), f"kp_{name}_status")()) if is_loaded(lib) else 0
+
+
+def tc_status() -> int:
+    """0, or 1 if a bounded wait of the tcgen05 product kernel gave up since the last call (synchronises)."""
+    return _read_one("gemm_tc", "tc")
+
+
+def stream_status() -> int:
+    return _read_one("gemm_stream", "stream")
+
+
+def attention_tc_status() -> int:
+    return _read_one("attention_tc", "attention_tc")
+
+
+def attention_mma_status() -> int:
+    return _read_one("attention_mma", "attention_mma")
+
+
+class StatusGather:
+    """Collects the status words of the loaded kernel libraries (and one word of its own, ``injected``, that
+    the host may set: a stand-in for a kernel failure where the real one cannot be made) into one device
+    word, with one small kernel behind a step."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self.injected = torch.zeros(1, dtype=torch.int32, device=device)
+        self._libs = None
+        self._addrs: Optional[torch.Tensor] = None
+
+    def _refresh(self) -> None:
+        libs = tuple(lib for lib, _ in _STATUS_LIBS if is_loaded(lib))
+        if libs == self._libs:
+            return
+        addrs = [self.injected.data_ptr()]
+        for lib, name in _STATUS_LIBS:
+            if lib in libs:
+                fn = getattr(load_library(lib), f"kp_{name}_status_address")
+                fn.restype = ctypes.c_void_p
+                a = fn()
+                if not a:
+                    raise KernelError(f"{lib}: no address for its status word")
+                addrs.append(int(a))
+        self._addrs = torch.tensor(addrs, dtype=torch.int64).to(self.device)
+        self._libs = libs
+
+    def gather(self, out: torch.Tensor) -> None:
+        """out[0] (int32, on the device) = OR of the status words, in stream order."""
+        _need(out, "out", torch.int32)
+        self._refresh()
+        _check(load_library("rowwise").kp_gather_status(_ptr(self._addrs), self._addrs.numel(), _ptr(out), _stream()),
+               "gather_status")
+
+    def clear(self) -> dict:
+        """Read and clear every word (synchronises); returns what was set."""
+        st = read_status()
+        if int(self.injected.item()):
+            st["injected"] = 1
+            self.injected.zero_()
+        return {k: v for k, v in st.items() if v}
 
 
 # -------------------------------------------------------------------- rowwise
@@ -342,11 +424,6 @@ def attention_prefill_tc_ok(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
             and cache.shape[0] * cache.shape[1] * cache.shape[2] * page_size < 2 ** 31 - 1)
 
 
-def attention_tc_status() -> int:
-    """0, or 1 if a bounded wait of the tcgen05 attention kernel gave up since the last call (synchronises)."""
-    return int(load_library("attention_tc").kp_attention_tc_status())
-
-
 def attention_prefill_ok(q: torch.Tensor, hd: int) -> bool:
     return USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0
 
@@ -444,11 +521,6 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     return out
 
 
-def tc_status() -> int:
-    """0, or 1 if a bounded wait of the tcgen05 kernel gave up since the last call (synchronises)."""
-    return int(load_library("gemm_tc").kp_tc_status())
-
-
 STREAM_MAX_M = 64          # rows up to which the bulk-copy kernel is preferred
 USE_STREAM = True         # few-row products go to the bulk-copy kernel where their shape fits it
 
@@ -465,11 +537,6 @@ def stream_pays(N: int, K: int) -> bool:
     fills the ring before it waits for the kernel before it, overlaps that kernel's tail inside a model step.
     It loses on the huge grid of a 65536-row head (65 against 48 us)."""
     return N <= 16384
-
-
-def stream_status() -> int:
-    """0, or 1 if a bounded wait of the bulk-copy kernels gave up since the last call (synchronises)."""
-    return int(load_library("gemm_stream").kp_stream_status())
 
 
 SKINNY_NORM_MAX_M = 16

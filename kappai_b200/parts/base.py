@@ -9,6 +9,8 @@ parts layer by layer.
 
 Categories and what each must offer
 -----------------------------------
+any             optionally ``step_tables_key`` and ``step_tables(segs)``: int32
+                  tables built on the host for every step (see :class:`Part`).
 ``mixer``         ``cache_spec()`` -> PagedKVSpec | StateSpec | None;
                   ``forward(h, residual, ctx, cache)`` adds its output (float32)
                   into ``residual`` in place.  It must restart at every
@@ -64,6 +66,18 @@ class Part:
     def __init__(self, params: Dict[str, Any], env: BuildEnv):
         self.params = dict(params)
         self.env = env
+
+    # Step tables.  A part whose kernels need host-built int32 tables for every step (tile lists, scan
+    # boundaries, rows per expert...) names them here: ``step_tables_key`` (hashable; parts with equal keys
+    # share one set of tables) and ``step_tables(segs)``, which gets the step's segments on the host
+    # (``engine.batch.StepSegments``) and returns an ``engine.batch.PartTables`` (or None for a step that
+    # needs none).  The arrays travel in the step's one upload and show up as ``ctx.tables[key].<name>``.
+    # In a captured decode step the arrays live in the graph's static buffer and are refilled before every
+    # replay; their sizes must then depend on the number of requests only.
+    step_tables_key = None
+
+    def step_tables(self, segs):
+        return None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {}

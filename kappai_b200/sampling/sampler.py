@@ -26,13 +26,14 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
 
 
 def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int], indices: Sequence[int],
-           recent: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+           recent: Optional[Sequence[Sequence[int]]] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of ``logits`` [n, vocab] (float32, on the device).
 
     ``seeds[i]`` and ``indices[i]`` fix row i's uniform number (the request's
     resolved seed and how many tokens it has sampled before); ``recent[i]``
     holds the request's last tokens for the repeat penalty.  Returns int32 [n]
-    on the device.  ``logits`` is changed in place where a penalty applies.
+    on the device (``out`` if given).  ``logits`` is changed in place where a
+    penalty applies.
     """
     K._need(logits, "logits", torch.float32)
     n, V = logits.shape
@@ -42,7 +43,7 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
         p.validate(V)
     penalised = recent is not None and any(p.repeat_penalty != 1.0 for p in params)
     if not penalised and all(p.greedy for p in params):
-        return argmax(logits)
+        return argmax(logits, out)
     lib = load_library("sampling")
     dev = logits.device
     stream = K._stream()
@@ -70,7 +71,9 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
     if penalised:
         K._check(lib.kp_repeat_penalty(K._ptr(logits), n, V, K._ptr(d[n * 6:]), width, col(3), stream),
                  "repeat_penalty")
-    out = torch.empty(n, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=dev)
+    K._need(out, "out", torch.int32)
     K._check(lib.kp_sample_rows(K._ptr(logits), n, V, col(0), K._ptr(d[n * 5:n * 6]), col(1), col(2), col(4),
                                 K._ptr(out), stream), "sample_rows")
     out._staging = host           # keep the pinned buffer alive until the copy has run

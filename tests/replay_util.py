@@ -144,6 +144,21 @@ def run_trace(model_dir, dtype, trace, out_dir, max_tokens, page_size=None, time
     return out
 
 
+def cache_stats(out_dir):
+    with open(os.path.join(out_dir, "cache_stats.json")) as f:
+        return json.load(f)
+
+
+def rows_by_place(trace, outputs, first_step=0, last_step=None):
+    """(request, position) -> the logits rows written for it in steps [first_step, last_step)."""
+    out = {}
+    for st, rows in zip(trace.steps, trace.rows):
+        if rows and first_step <= st["step"] < (len(trace.steps) if last_step is None else last_step):
+            for j, place in enumerate(rows):
+                out.setdefault(place, []).append(outputs[st["step"]][j])
+    return out
+
+
 def compare(trace, outputs, expected, tol, what):
     """expected: request -> [T, vocab] logits of the plain implementation.
     Reports the first wrong (step, request, position)."""

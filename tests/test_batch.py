@@ -4,9 +4,22 @@ import numpy as np
 import pytest
 import torch
 
-from kappai_b200.engine.batch import BIG_TILE, ROW_TILE, BatchError, Segment, build_step_context
+from kappai_b200.engine.batch import BatchError, PartTables, Segment, build_step_context
+from kappai_b200.parts.attention import BIG_TILE, ROW_TILE, attention_tiles
 
 CPU = torch.device("cpu")
+
+
+class Tiles:
+    """Stands for an attention part: the step tables it asks for."""
+
+    step_tables_key = "tiles"
+
+    def step_tables(self, segs):
+        return attention_tiles(segs)
+
+
+BUILDERS = {"tiles": Tiles()}
 
 
 def seg(req, n, pos_start, slot, page=16, want=()):
@@ -32,10 +45,11 @@ def test_rows_segments_and_slots():
 
 def test_tile_lists_cover_every_row_once_and_big_tiles_come_longest_first():
     segs = [seg("a", 300, 0, 0), seg("b", 1, 900, 1), seg("c", 130, 512, 2), seg("d", 64, 64, 3)]
-    ctx = build_step_context(segs, {"g": 16}, CPU, 1000, 4096)
-    cu = ctx.cu_rows.tolist()
+    full = build_step_context(segs, {"g": 16}, CPU, 1000, 4096, BUILDERS)
+    ctx = full.tables["tiles"]
+    cu = full.cu_rows.tolist()
     for size, t_seg, t_row0 in ((ROW_TILE, ctx.tile_seg, ctx.tile_row0), (BIG_TILE, ctx.big_tile_seg, ctx.big_tile_row0)):
-        covered = np.zeros(ctx.n_rows, int)
+        covered = np.zeros(full.n_rows, int)
         for s, r0 in zip(t_seg.tolist(), t_row0.tolist()):
             assert cu[s] <= r0 < cu[s + 1] and (r0 - cu[s]) % size == 0
             covered[r0:min(r0 + size, cu[s + 1])] += 1
@@ -52,19 +66,38 @@ def test_tile_lists_cover_every_row_once_and_big_tiles_come_longest_first():
 
 def test_decoded_tokens_that_lead_a_mixed_step_are_set_apart():
     segs = [seg("a", 1, 900, 0), seg("b", 2, 40, 1), seg("c", 300, 0, 2), seg("d", 1, 77, 3)]
-    ctx = build_step_context(segs, {"g": 16}, CPU, 1000, 4096)
+    full = build_step_context(segs, {"g": 16}, CPU, 1000, 4096, BUILDERS)
+    ctx = full.tables["tiles"]
     assert ctx.n_short_rows == 3 and ctx.n_short_tiles == 2
     assert ctx.tile_seg.tolist()[:2] == [0, 1]                        # the lead's small tiles come first
     assert sorted(set(ctx.big_tile_seg.tolist())) == [2, 3]           # big tiles: the other segments only
-    covered = np.zeros(ctx.n_rows, int)
-    cu = ctx.cu_rows.tolist()
+    covered = np.zeros(full.n_rows, int)
+    cu = full.cu_rows.tolist()
     for s, r0 in zip(ctx.big_tile_seg.tolist(), ctx.big_tile_row0.tolist()):
         covered[r0:min(r0 + BIG_TILE, cu[s + 1])] += 1
     assert covered.tolist() == [0] * 3 + [1] * 301
     # all short, or no short lead: one kernel takes the step, nothing is set apart
-    for other in ([seg("a", 1, 9, 0), seg("b", 3, 4, 1)], [seg("a", 9, 9, 0), seg("b", 1, 4, 1)]):
-        c2 = build_step_context(other, {"g": 16}, CPU, 1000, 4096)
-        assert c2.n_short_rows == 0 and c2.n_short_tiles == 0 and c2.n_big_tiles == 2
+    c2 = build_step_context([seg("a", 9, 9, 0), seg("b", 1, 4, 1)], {"g": 16}, CPU, 1000, 4096, BUILDERS).tables["tiles"]
+    assert c2.n_short_rows == 0 and c2.n_short_tiles == 0 and c2.n_big_tiles == 2
+    # short segments only: the split kernel takes the step and no tile list is built
+    assert "tiles" not in build_step_context([seg("a", 1, 9, 0), seg("b", 3, 4, 1)], {"g": 16}, CPU, 1000, 4096,
+                                             BUILDERS).tables
+
+
+def test_a_part_adds_tables_of_its_own_to_the_upload():
+    class Scan:
+        step_tables_key = "scan"
+
+        def step_tables(self, segs):
+            return PartTables(arrays={"seg_end": segs.cu_rows[1:] - 1, "odd": np.arange(3)},
+                              scalars={"n_long": sum(n > 2 for n in segs.seg_len)})
+
+    ctx = build_step_context([seg("a", 5, 0, 0), seg("b", 1, 37, 1), seg("c", 3, 16, 2)], {"g": 16}, CPU, 1000, 4096,
+                             {"scan": Scan(), **BUILDERS})
+    t = ctx.tables["scan"]
+    assert t.seg_end.tolist() == [4, 5, 8] and t.odd.tolist() == [0, 1, 2] and t.n_long == 2
+    assert t.seg_end.dtype == torch.int32 and ctx.tables["tiles"].n_tiles == 3
+    assert ctx.positions.tolist() == [0, 1, 2, 3, 4, 37, 16, 17, 18]          # the fixed tables are where they were
 
 
 def test_refusals():

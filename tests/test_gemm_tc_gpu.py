@@ -77,9 +77,24 @@ def test_linear_picks_the_tensor_core_kernel_for_many_rows():
     from kappai_b200.ops.linear import linear
     a = torch.randn((200, 256), device="cuda").to(DT)
     w = torch.randn((64, 256), device="cuda").to(DT)
-    before = Kn.LAUNCHES[0]
+    count = lambda: {k: Kn.LAUNCHES_BY.get(k, 0) for k in ("gemm_tc", "gemm_nt_simt", "gemm_stream", "gemm_skinny")}
+    before = count()
     out = linear(a, w, out_dtype=torch.float32)
+    after = count()
+    assert after["gemm_tc"] == before["gemm_tc"] + 1 and all(after[k] == before[k] for k in after if k != "gemm_tc")
     ref = Kn.gemm_nt_simt(a, w, torch.empty((200, 64), device="cuda"))
     assert (out - ref).abs().max().item() < 1e-3
-    odd = torch.randn((200, 100), device="cuda").to(DT)          # K % 8 != 0: not for TMA, takes the general kernel
-    linear(odd, torch.randn((64, 100), device="cuda").to(DT))
+    # K % 8 != 0 is not for TMA: the general kernel takes it, and its result is right too
+    odd = torch.randn((200, 100), device="cuda").to(DT)
+    w_odd = torch.randn((64, 100), device="cuda").to(DT)
+    before = count()
+    out = linear(odd, w_odd, out_dtype=torch.float32)
+    after = count()
+    assert after["gemm_nt_simt"] == before["gemm_nt_simt"] + 1 and after["gemm_tc"] == before["gemm_tc"]
+    assert (out - odd.float() @ w_odd.float().t()).abs().max().item() < 1e-2
+    # few rows: the weight-streaming kernels
+    before = count()
+    linear(a[:8], w)
+    after = count()
+    assert after["gemm_stream"] + after["gemm_skinny"] == before["gemm_stream"] + before["gemm_skinny"] + 1
+    assert Kn.tc_status() == 0

@@ -94,11 +94,12 @@ def wide_model(tmp_path_factory):
     return d, PlainLfm2(d)
 
 
-@pytest.mark.parametrize("n_req", [3, 20, 40, 64])
+@pytest.mark.parametrize("n_req", [3, 20, 40, 64, 100, 256])
 def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model):
     """Width 512 (a multiple of the bulk-copy kernel's 512-column chunks): decode steps of 3, 20, 40 and 64
     requests run the weight-streaming products in all their forms (half tile, two, three and four m-tiles,
-    16-row weight tiles) inside the model, from captured graphs; every request's logits against the plain model."""
+    16-row weight tiles) inside the model, from captured graphs; steps of 100 and 256 requests run every product
+    on the tcgen05 kernel with a short box of rows; every request's logits against the plain model."""
     from kappai_b200 import ModelRunner, StepEntry
     from kappai_b200.ops import kernels as K
     d, plain = wide_model
@@ -117,3 +118,53 @@ def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model)
             assert np.abs(lg[i] - refs[i][L + step]).max() <= tol_for("bfloat16", refs[i]), (n_req, step, i)
     assert r.graphs.n_replays >= 2
     assert K.tc_status() == 0 and K.stream_status() == 0
+
+
+def test_a_captured_step_survives_the_growth_of_the_attention_scratch(wide_model):
+    """A decode graph keeps the address of the split-key scratch it was captured with.  Capture a graph while
+    the scratch is small, make a longer request outgrow it, fill the memory that a freed buffer would have
+    returned to with sentinels, then replay the first graph: the sentinels are untouched and the logits right."""
+    import torch
+    from kappai_b200 import ModelRunner, StepEntry
+    d, plain = wide_model
+    rng = np.random.default_rng(7)
+    V = WIDE_CONFIG["vocab_size"]
+    n = 64
+    r = ModelRunner(d, dtype="bfloat16", max_tokens=n * 128 + 1024, max_requests=n, page_size=64, max_model_len=1024)
+    env = r.model.env
+
+    def batch(lens, tag):
+        seqs = [rng.integers(0, V, L + 2).tolist() for L in lens]
+        for i, (s, L) in enumerate(zip(seqs, lens)):
+            r.step([StepEntry((tag, i), s[:L], [])])
+        return seqs
+
+    def decode_and_check(seqs, lens, tag, step):
+        lg = r.step([StepEntry((tag, i), [s[L + step]], [0]) for i, (s, L) in enumerate(zip(seqs, lens))])
+        lg = lg.float().cpu().numpy()
+        for i in (0, 1, n // 2, n - 1):
+            ref = plain.logits(seqs[i][:lens[i] + step + 1])[-1]
+            assert np.abs(lg[i] - ref).max() <= tol_for("bfloat16", ref), (tag, step, i)
+
+    short = rng.integers(3, 60, n).tolist()
+    seqs_a = batch(short, "a")
+    decode_and_check(seqs_a, short, "a", 0)                    # captures the graph of (64 requests, 8 blocks)
+    first = env.shared["attn_scratch"]
+    for i in range(n):
+        r.end(("a", i))
+    long = list(short)
+    long[0] = 600                                              # one request of 10 blocks: the graph of 16 blocks
+    seqs_b = batch(long, "b")
+    decode_and_check(seqs_b, long, "b", 0)
+    assert env.shared["attn_scratch"] is not first and env.shared["attn_scratch"].numel() > first.numel()
+    assert any(t is first for t in env.shared["attn_scratch_retired"])
+    for i in range(n):
+        r.end(("b", i))
+    del first
+    sentinels = [torch.full((68096,), 7.0, device="cuda") for _ in range(64)]      # what a freed scratch would become
+    seqs_c = batch(short, "c")
+    decode_and_check(seqs_c, short, "c", 0)                    # replays the first graph
+    decode_and_check(seqs_c, short, "c", 1)
+    assert r.graphs.n_captures == 2
+    torch.cuda.synchronize()
+    assert all(bool((t == 7.0).all()) for t in sentinels)

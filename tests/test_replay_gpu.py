@@ -45,6 +45,16 @@ def test_all_cuts_agree_with_plain(name, page_size, dtype, model_dirs, plain_mod
     assert max(len(s["entries"]) for s in tr.steps[b:]) >= 2, "the mixed family never had two requests in a step"
     out = R.run_trace(model_dirs[name], dtype, tr, str(tmp_path / "out"), max_tokens, page_size)
     worst = R.compare(tr, out, expected, tol, f"{name}/{dtype}/page{page}")
+    # the pool was small enough that pages went from one request to another
+    stats = R.cache_stats(str(tmp_path / "out"))
+    assert stats and all(g["reused"] > 0 and g["handed_out"] > g["pages"] for g in stats.values()), stats
+    if dtype == "float32":
+        # the 32-bit path sums in an order that does not depend on the cut: every way of cutting gives the
+        # same bits for a (request, position)
+        for place, rows in R.rows_by_place(tr, out).items():
+            assert len(rows) >= 2, place
+            for r in rows[1:]:
+                assert np.array_equal(rows[0], r), f"{name}: float32 logits of {place} differ between cuts"
     print(f"{name} {dtype} page {page}: worst |error| {worst:.3e} (tolerance {tol:.3e}), {len(tr.steps)} steps")
 
 

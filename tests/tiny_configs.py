@@ -40,6 +40,18 @@ TINY_D = dict(
     block_ff_dim=256, block_auto_adjust_ff_dim=False, rope_theta=10000.0, tie_embedding=True)
 TINY_D_SEED = 9
 
+# the LFM2-1.2B shape (for the tests that run the sizes the benchmark times)
+LFM2_1P2B = dict(
+    architectures=["Lfm2ForCausalLM"], vocab_size=65536, hidden_size=2048, num_hidden_layers=16,
+    num_attention_heads=32, num_key_value_heads=8,
+    layer_types=["conv", "conv", "full_attention", "conv", "conv", "full_attention", "conv", "conv",
+                 "full_attention", "conv", "full_attention", "conv", "full_attention", "conv",
+                 "full_attention", "conv"],
+    max_position_embeddings=128000, norm_eps=1e-5, conv_L_cache=3, conv_bias=False,
+    block_ff_dim=8192, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256,
+    rope_theta=1000000.0, tie_embedding=True)
+LFM2_1P2B_SEED = 2
+
 CONFIGS = {"A": (TINY_A, TINY_A_SEED), "B": (TINY_B, TINY_B_SEED), "C": (TINY_C, TINY_C_SEED),
            "D": (TINY_D, TINY_D_SEED)}
 

@@ -20,3 +20,19 @@ def tol_for(dtype, expected):
     if dtype == "float32":
         return FP32_ATOL
     return BF16_REL_STD * float(np.std(expected))
+
+
+def fp32_tol_at_width(width):
+    """The float32 bound at another width.  FP32_ATOL was set at widths of 64 to 128; a sum of K float32
+    products strays from its exact value like sqrt(K) roundings, so the bound grows with the square root of
+    the width (2048: 5.7 x 2e-5 = 1.1e-4)."""
+    return FP32_ATOL * float(np.sqrt(max(width, 64) / 64.0))
+
+
+def bf16_rel_std_for_layers(n_layers):
+    """The bfloat16 bound, as a fraction of the logits' standard deviation, for a model of ``n_layers``.
+    Every layer adds two branch outputs to the float32 residual, each computed from operands rounded to
+    bfloat16 (relative 2^-9 each, about six roundings a branch); the errors of the branches are independent,
+    so what reaches the logits grows like the square root of the number of layers.  BF16_REL_STD (5 %) is
+    the bound of the six-layer test models; sixteen layers get 5 % x sqrt(16 / 6) = 8.2 %."""
+    return BF16_REL_STD * float(np.sqrt(max(n_layers, 6) / 6.0))
