@@ -1,22 +1,35 @@
 #!/usr/bin/env python3
 """Decode and prefill throughput of the engine at the LFM2-1.2B shape.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--workload long|many]
 
 One "step" is one decode step of the whole batch.  The default run has the
 layer sizes of the LFM2-1.2B configuration with random weights (seed 2), a
-batch of 8 requests, prompts of 2,048 tokens and a context limit of 4,096.
-It prints one JSON line:
+batch of 8 requests, prompts of 2,048 tokens and a context limit of 4,096:
+every request decodes from 2,048 to 4,096 tokens (2,048 steps), and CUDA events
+mark windows of exactly K steps at the start, the middle and the end of that
+run.  It prints one JSON line:
 
-* ``value``: decoded tokens a second, timed on the device with CUDA events
-  around exactly K steps (sampled tokens stay on the device between steps);
+* ``value``: decoded tokens a second over the K steps in the middle of the run
+  (context about 3,072; a step's time grows linearly with the context, so this
+  is also the mean over 2,048 -> 4,096, which ``points`` gives beside it),
+  timed on the device (sampled tokens stay on the device between steps);
 * ``e2e``: the same through the Python entry point (``Engine.step``): host
   token ids in, host token ids out, every step;
-* ``prefill``: one 2,048-token prompt in one step, with the fraction of the
-  bf16 matrix peak;
+* ``prefill``: one 2,048-token prompt in one step, on the device alone and
+  from the building of the step's tables to the logits, with the fraction of
+  the bf16 matrix peak;
 * ``roofline``: bytes a decode step has to read (every weight once, the cache
   of the live requests) over its time, against the measured copy bandwidth;
-* ``points``: decode tokens a second at batch 1 and 64.
+* ``points``: the same run at batch 1 and 64, and for every batch the two
+  ends of the run and its mean (tokens a second, milliseconds a step, bytes a
+  step, fraction of the copy bandwidth).
+
+``--workload long`` (LFM2-2.6B shape, 16 requests with prompts of 1k to 30k
+tokens, portions of 2,048, context 32,768) and ``--workload many`` (LFM2-350M
+shape, 256 requests at once, prompts of 16 to 512 tokens, 128 sampled tokens
+each at temperature 0.8) run whole generations through ``Engine`` and print a
+line of their own: tokens a second, steps, preemptions, mean step time.
 
 Only one GPU is used; ``--gpus N`` with N > 1 prints a line that says so and
 exits with 2.
@@ -43,6 +56,9 @@ LFM2_1P2B = dict(
     max_position_embeddings=128000, norm_eps=1e-5, conv_L_cache=3, conv_bias=False,
     block_ff_dim=8192, block_auto_adjust_ff_dim=True, block_ffn_dim_multiplier=1.0, block_multiple_of=256,
     rope_theta=1000000.0, tie_embedding=True)
+LFM2_2P6B = dict(LFM2_1P2B, num_hidden_layers=30, block_ff_dim=10752,
+                 layer_types=["full_attention" if i in (2, 6, 10, 14, 18, 21, 24, 27) else "conv" for i in range(30)])
+LFM2_350M = dict(LFM2_1P2B, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, block_ff_dim=6656)
 SEED = 2
 PROMPT_LEN = 2048
 CONTEXT = 4096
@@ -186,8 +202,11 @@ def cache_bytes_per_step(runner, batch, context):
     return kv + st
 
 
-def run_decode(runner, batch, prompt_len, steps, warmup, rng):
-    """Prefill ``batch`` requests, then time ``steps`` decode steps on the device."""
+def run_decode(runner, batch, prompt_len, context, steps, warmup, rng):
+    """Prefill ``batch`` requests of ``prompt_len`` tokens, then decode every one of them up to ``context``
+    tokens, on the device alone.  CUDA events mark three windows of exactly ``steps`` steps (after the warm-up,
+    in the middle, at the end) and the whole run after the warm-up.  Returns a dict of windows
+    name -> (ms a step, context at the window's middle) and the kernel launchers called in the middle window."""
     import torch
     from kappai_b200 import StepEntry
     from kappai_b200.ops import kernels as K
@@ -200,37 +219,53 @@ def run_decode(runner, batch, prompt_len, steps, warmup, rng):
         logits = runner.step([StepEntry(rid, rng.integers(0, V, prompt_len).tolist(), [prompt_len - 1])])
         t = argmax(logits)
         tok = t if tok is None else torch.cat([tok, t])
-
     entries = [StepEntry(rid, [0], [0]) for rid in ids]
+    n_steps = context - prompt_len                     # the step that makes a request context tokens long is the last
+    if steps + warmup > n_steps:
+        raise SystemExit(f"bench.py: --steps + --warmup must not exceed the {n_steps} steps of the run")
+    starts = {"start": warmup, "mid": max(warmup, n_steps // 2 - steps // 2), "end": n_steps - steps}
+    marks = {}                                         # step index -> event recorded before that step
 
-    def one_step(tok):
-        return argmax(runner.step(entries, device_tokens=tok))     # the sampled tokens never leave the device
+    def mark(j):
+        if j not in marks:
+            marks[j] = torch.cuda.Event(enable_timing=True)
+            marks[j].record()
 
-    for _ in range(warmup):
-        tok = one_step(tok)
+    wanted = {warmup, n_steps}
+    for st in starts.values():
+        wanted |= {st, st + steps}
+    launches = 0
+    for j in range(n_steps + 1):
+        if j in wanted:
+            torch.cuda.synchronize()                   # a window starts and ends with an idle device
+            mark(j)
+        if j == starts["mid"]:
+            K.LAUNCHES[0] = 0
+        if j == starts["mid"] + steps:
+            launches = K.LAUNCHES[0]
+        if j < n_steps:
+            tok = argmax(runner.step(entries, device_tokens=tok))     # the sampled tokens never leave the device
     torch.cuda.synchronize()
-    K.LAUNCHES[0] = 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        tok = one_step(tok)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    launches = K.LAUNCHES[0]
-    context = runner.length(ids[0])
+    out = {name: (marks[st].elapsed_time(marks[st + steps]) / steps, prompt_len + st + steps // 2)
+           for name, st in starts.items()}
+    out["mean"] = (marks[warmup].elapsed_time(marks[n_steps]) / (n_steps - warmup), (prompt_len + warmup + context) // 2)
+    assert runner.length(ids[0]) == context
     for rid in ids:
         runner.end(rid)
-    return ms, launches, context
+    return out, launches
 
 
 def run_prefill(runner, T, warmup, rng):
+    """One prompt of T tokens in one step.  Returns (device ms, submit-to-logits ms), each the median of five:
+    the first is the time of the step's kernels alone (tables already on the device); the second runs from
+    before the step's tables are built on the host, through their copy to the device, to the logits."""
+    import statistics
     import torch
     from kappai_b200 import StepEntry
 
     V = runner.vocab_size
-    times = []
-    for i in range(warmup + 3):
+    dev_ms, all_ms = [], []
+    for i in range(warmup + 5):
         toks = rng.integers(0, V, T).tolist()
         ctx, after = runner.prepare([StepEntry("p", toks, [T - 1])])
         torch.cuda.synchronize()
@@ -240,9 +275,16 @@ def run_prefill(runner, T, warmup, rng):
         e1.record()
         torch.cuda.synchronize()
         runner.end("p")
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        runner.step([StepEntry("p", toks, [T - 1])])
+        f1.record()
+        torch.cuda.synchronize()
+        runner.end("p")
         if i >= warmup:
-            times.append(e0.elapsed_time(e1))
-    return min(times)
+            dev_ms.append(e0.elapsed_time(e1))
+            all_ms.append(f0.elapsed_time(f1))
+    return statistics.median(dev_ms), statistics.median(all_ms)
 
 
 def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
@@ -273,9 +315,67 @@ def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
     h2d = eng.runner.last_h2d_bytes               # the step's table buffer; greedy sampling copies nothing more
-    d2h = batch * 4
+    d2h = batch * 4 + 4                           # the sampled tokens and the step's status word
     eng.shutdown()
     return n / dt, h2d, d2h
+
+
+def run_workload(name: str, rng_seed: int) -> dict:
+    """Whole generations through ``Engine`` (scheduler, chunked prefill beside decoding, sampling), timed by
+    the wall clock around ``generate``-like stepping, as the reference times its runs (src/context.c:1507-1512,
+    1607-1620; src/test/test_bench.c:432-464)."""
+    import numpy as np
+    import torch
+    from kappai_b200 import Engine, EngineArgs, SamplingParams
+
+    if name == "long":
+        cfg, seed, n_req, ctx, max_batch = LFM2_2P6B, 3, 16, 32768, 16
+        lens = np.random.default_rng(rng_seed).integers(1000, 30001, n_req).tolist()
+        n_out, sp_of = 128, lambda i: SamplingParams(temperature=0.0, n_predict=128)
+        label = "LFM2-2.6B shape, 16 requests, prompts U[1000,30000], portions of 2048, context 32768, 128 greedy tokens each"
+    else:
+        cfg, seed, n_req, ctx, max_batch = LFM2_350M, 4, 256, 1024, 256
+        lens = np.random.default_rng(rng_seed).integers(16, 513, n_req).tolist()
+        n_out, sp_of = 128, lambda i: SamplingParams(temperature=0.8, top_k=40, top_p=0.9, min_p=0.1, seed=4 + i, n_predict=128)
+        label = "LFM2-350M shape, 256 requests at once, prompts U[16,512], 128 tokens each at temperature 0.8 (seed 4)"
+    model_dir, c = model_folder(cfg, seed, cfg["num_hidden_layers"])
+    eng = Engine(EngineArgs(model=model_dir, dtype="bfloat16", ctx_size=ctx, max_batch=max_batch, max_step_tokens=2048,
+                            page_size=64, kv_tokens=0))
+    rng = np.random.default_rng(rng_seed + 1)
+    V = eng.vocab_size
+    prompts = [rng.integers(0, V, n).tolist() for n in lens]
+    # warm-up: one short generation builds what is built at first use
+    eng.generate([prompts[0][:64]], SamplingParams(temperature=0.0, n_predict=4))
+    eng.stats = type(eng.stats)()
+    torch.cuda.synchronize()
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = time.perf_counter()
+    ids = [eng.add_request(p, sp_of(i)) for i, p in enumerate(prompts)]
+    first = {}
+    n_steps = 0
+    while eng.has_work():
+        for r in eng.step():
+            first.setdefault(r.id, time.perf_counter() - t0)
+        n_steps += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    clk = clocks.stop()
+    outs = [eng.requests[i].output for i in ids]
+    reasons = sorted({eng.finish_reason(i) for i in ids})
+    n_prompt, n_new = sum(lens), sum(len(o) for o in outs)
+    st = eng.stats
+    rec = {"workload": name, "what": label, "impl": "ours", "dtype": "bf16", "seconds": round(dt, 3),
+           "prompt_tokens": n_prompt, "new_tokens": n_new, "tokens_per_s": round((n_prompt + n_new) / dt, 1),
+           "new_tokens_per_s": round(n_new / dt, 1), "steps": n_steps, "mean_step_ms": round(dt * 1e3 / n_steps, 3),
+           "preemptions": eng.scheduler.n_preemptions, "finish_reasons": reasons,
+           "mean_ttft_s": round(sum(first.values()) / len(first), 3), "kv_tokens": eng.runner.cache_plan.tokens,
+           "graph_captures": eng.runner.graphs.n_captures if eng.runner.graphs else 0,
+           "pp_tokens_per_s": round(st.prompt_tokens / st.prompt_seconds, 1) if st.prompt_seconds else None,
+           "tg_tokens_per_s": round(st.decode_tokens / st.decode_seconds, 1) if st.decode_seconds else None,
+           "clocks": clk}
+    eng.shutdown()
+    return rec
 
 
 def run_probe(model_dir, a, rng) -> int:
@@ -314,6 +414,9 @@ def main() -> int:
     ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
                     help="run a few eager steps (no CUDA graph) of one kind and exit: the small case that a "
                          "profiler is pointed at")
+    ap.add_argument("--workload", choices=["long", "many"], default=None,
+                    help="run a whole scheduling workload through Engine instead of the default line: 'long' "
+                         "(2.6B shape, 16 prompts of 1k to 30k tokens, context 32768) or 'many' (350M shape, 256 requests)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
     a = ap.parse_args()
 
@@ -327,6 +430,9 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
     warmup = max(a.warmup, 3)
+    if a.workload:
+        print(json.dumps(run_workload(a.workload, 40)))
+        return 0
 
     import numpy as np
     import torch
@@ -343,20 +449,30 @@ def main() -> int:
     wbytes = weight_bytes(runner)
     runner_ff = runner.config.intermediate_size
 
+    def window(batch, ms, context):
+        by = wbytes + cache_bytes_per_step(runner, batch, context)
+        gbs = by / (ms * 1e-3) / 1e9
+        return {"tok_s": round(batch * 1e3 / ms, 1), "ms": round(ms, 4), "context": int(context),
+                "gb": round(by / 1e9, 3), "frac": round(gbs / pk["hbm_gbs"], 4)}
+
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, context = run_decode(runner, a.batch, PROMPT_LEN, a.steps, warmup, rng)
+    win, launches = run_decode(runner, a.batch, PROMPT_LEN, CONTEXT, a.steps, warmup, rng)
     clk = clocks.stop()
+    ms, context = win["mid"]
     value = a.batch * 1e3 / ms
-    step_bytes = wbytes + cache_bytes_per_step(runner, a.batch, context - a.steps // 2)
-    achieved = step_bytes / (ms * 1e-3) / 1e9
+    head = window(a.batch, ms, context)
 
     points = {}
-    for b in (1, 64):
-        pms, _, _ = run_decode(runner, b, PROMPT_LEN, max(8, a.steps // 2), warmup, rng)
-        points[f"decode_b{b}"] = round(b * 1e3 / pms, 1)
+    for b in sorted({1, 8, 64, a.batch}):
+        w = win if b == a.batch else run_decode(runner, b, PROMPT_LEN, CONTEXT, a.steps, warmup, rng)[0]
+        points[f"decode_b{b}"] = round(b * 1e3 / w["mid"][0], 1)
+        for name in ("start", "end", "mean"):
+            for k, v in window(b, *w[name]).items():
+                points[f"b{b}_{name}_{k}"] = v
+        points[f"b{b}_mid_frac"] = window(b, *w["mid"])["frac"]
 
-    pf_ms = run_prefill(runner, PROMPT_LEN, warmup, rng)
+    pf_ms, pf_all_ms = run_prefill(runner, PROMPT_LEN, warmup, rng)
     flops = 2 * PROMPT_LEN * matrix_params_per_token(runner) + attention_flops(runner, PROMPT_LEN) \
         + 2 * runner.vocab_size * cfg["hidden_size"]
     pf_frac = flops / (pf_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
@@ -366,7 +482,9 @@ def main() -> int:
     e2e, h2d, d2h = run_e2e(model_dir, a.batch, PROMPT_LEN, a.steps, warmup, rng, n_layers)
 
     rec = {
-        "metric": "decode tok/s at batch 8 (LFM2-1.2B, context 2048->4096)", "value": round(value, 1),
+        "metric": f"decode tok/s at batch {a.batch} (LFM2-1.2B, 2048-token prompts decoding to 4096; the K steps at "
+                  "the middle of the run; both ends and the mean in points)",
+        "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights (seed 2), uniform random token ids",
@@ -378,12 +496,13 @@ def main() -> int:
                    "context_at_timing": context, "page_size": 64, "parallelism": "single GPU",
                    "l2": "inputs larger than L2 (weights 1.8 GB per step)", "peaks": pk["source"]},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h)},
+                "d2h_bytes_per_step": int(d2h), "context": "the first K steps after the prompts (about 2100)"},
         "gpu_launches": int(launches),
         "prefill": {"value": round(PROMPT_LEN * 1e3 / pf_ms, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
-                    "frac": round(pf_frac, 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+                    "frac": round(pf_frac, 4), "ms_from_tables_to_logits": round(pf_all_ms, 3),
+                    "value_from_tables_to_logits": round(PROMPT_LEN * 1e3 / pf_all_ms, 1), "of": "median of 5"},
+        "roofline": {"bound": "hbm", "achieved": round(head["gb"] / (ms * 1e-3), 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": head["frac"], "gb_per_step": head["gb"]},
         "points": points,
         "clocks": clk,
     }

@@ -84,7 +84,7 @@ class Engine:
         # the longest sequence is the model's own limit unless ctx_size asks for less (src/context.c:465-470);
         # the pools hold kv_tokens, or what max_batch requests of that length need, or what fits beside the weights
         self.runner = ModelRunner(args.model, dtype=args.dtype, max_tokens=args.kv_tokens, max_requests=args.max_batch,
-                                  page_size=args.page_size, max_model_len=args.ctx_size or None, device=args.device,
+                                  page_size=args.page_size, max_model_len=args.ctx_size or (1 << 62), device=args.device,
                                   max_step_tokens=args.max_step_tokens, free_memory=free_memory)
         self.scheduler = Scheduler(self.runner.cache, args.max_step_tokens, args.max_batch,
                                    self.runner.max_model_len, self.runner.spec.eos_token_id)

@@ -18,7 +18,7 @@ import pytest
 
 import replay_util as R
 from tiny_configs import LFM2_1P2B, LFM2_1P2B_SEED
-from tolerances import bf16_rel_std_for_layers, fp32_tol_at_width
+from tolerances import bf16_bounds_for, fp32_tol_at_width
 
 pytestmark = pytest.mark.gpu
 
@@ -101,15 +101,17 @@ def test_all_sixteen_layers_bfloat16_against_float32_in_every_cut(tmp_path):
     assert n_multi > 100
 
     # bfloat16 against float32, row by row, in every family
-    rel = bf16_rel_std_for_layers(LFM2_1P2B["num_hidden_layers"])
-    worst, n_rows, flips = 0.0, 0, []
+    rel, rel_rms = bf16_bounds_for(LFM2_1P2B["num_hidden_layers"], LFM2_1P2B["vocab_size"])
+    worst, worst_rms, n_rows, flips = 0.0, 0.0, 0, []
     for st, rows in zip(tr.steps, tr.rows):
         for j, place in enumerate(rows):
             a, b = out16[st["step"]][j].astype(np.float64), out32[st["step"]][j].astype(np.float64)
             tol = rel * float(b.std())
             err = float(np.abs(a - b).max())
-            worst = max(worst, err / float(b.std()))
+            rms = float(np.sqrt(np.mean((a - b) ** 2)))
+            worst, worst_rms = max(worst, err / float(b.std())), max(worst_rms, rms / float(b.std()))
             n_rows += 1
+            assert rms <= rel_rms * float(b.std()), f"step {st['step']} {place}: rms of bf16 - fp32 {rms:.4f}"
             assert err <= tol, (f"step {st['step']} {place}: |bf16 - fp32| {err:.4f} > {tol:.4f} "
                                 f"(entries {[(e['id'], len(e['tokens'])) for e in st['entries']]})")
             t16, t32 = int(np.argmax(a)), int(np.argmax(b))
@@ -117,5 +119,6 @@ def test_all_sixteen_layers_bfloat16_against_float32_in_every_cut(tmp_path):
                 # another greedy token only where float32 itself has a near tie: within twice the bound
                 assert b[t32] - b[t16] <= 2 * tol, (st["step"], place, t16, t32, b[t32] - b[t16], tol)
                 flips.append((place, round(float(b[t32] - b[t16]) / float(b.std()), 4)))
-    print(f"1.2B, 16 layers: {n_rows} rows, worst |bf16 - fp32| = {worst:.4f} of the logits' std (bound {rel:.4f}); "
+    print(f"1.2B, 16 layers: {n_rows} rows, worst |bf16 - fp32| = {worst:.4f} of the logits' std (bound {rel:.4f}), "
+          f"worst rms {worst_rms:.4f} (bound {rel_rms:.4f}); "
           f"{len(flips)} rows with another greedy token, all near ties: {flips[:8]}")

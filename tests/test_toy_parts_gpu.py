@@ -396,3 +396,96 @@ def test_layer_named_twice_and_borrowed_cache(model_dirs, plain_models):
             assert err <= tol_for(dtype, ref), (dtype, err)
     finally:
         unregister_architecture("Lfm2Twice")
+
+
+# ------------------------- a toy mixer with a step table of its own, inside a captured decode step
+def make_toy_with_table():
+    from kappai_b200.cache import StateSpec
+    from kappai_b200.engine.batch import PartTables
+    from kappai_b200.parts import Part, WeightSpec
+
+    class EmaTableMixer(Part):
+        """The moving average of the first toy, but its decode steps read everything from device tensors: the
+        host builds a table of its own for every step (``fresh``: 1 for a segment that starts its sequence,
+        whose state counts as zero), which travels with the step's upload and, in a captured step, lives in the
+        graph's static buffer."""
+        category = "mixer"
+        graph_safe = True
+        step_tables_key = "toy_ema_fresh"
+        calls = []                                     # (decode_only, fresh flags) of every table built: for the test
+
+        def __init__(self, params, env):
+            super().__init__(params, env)
+            self.d = params["hidden_size"]
+
+        def step_tables(self, segs):
+            fresh = (np.asarray(segs.seg_pos) == 0).astype(np.int32)
+            EmaTableMixer.calls.append((segs.decode_only, fresh.tolist()))
+            return PartTables(arrays={"fresh": fresh}, scalars={"n": segs.n_seg})
+
+        def weight_specs(self):
+            return {"decay": WeightSpec((self.d,), "bias"), "proj.weight": WeightSpec((self.d, self.d))}
+
+        def bind(self, w):
+            self.a = torch.sigmoid(w["decay"].float() * 50)
+            self.w = w["proj.weight"].float()
+
+        def cache_spec(self):
+            return StateSpec((self.d,), "float32")
+
+        def forward(self, h, residual, ctx, cache):
+            h = h.float()
+            t = ctx.tables[self.step_tables_key]
+            assert t.n == ctx.n_seg
+            if ctx.decode_only:                         # device tensors only: can be captured
+                slots = ctx.seg_slot.long()
+                keep = (1 - t.fresh).float()[:, None]
+                y = self.a * (cache.tensor[slots] * keep) + (1 - self.a) * h
+                cache.tensor[slots] = y
+                residual += y @ self.w.t()
+                return
+            for s in range(ctx.n_seg):
+                r0, r1 = ctx.host_cu_rows[s], ctx.host_cu_rows[s + 1]
+                slot = ctx.host_seg_slot[s]
+                y = torch.zeros(self.d, device=h.device) if ctx.host_seg_pos[s] == 0 else cache.tensor[slot].clone()
+                ys = []
+                for r in range(r0, r1):
+                    y = self.a * y + (1 - self.a) * h[r]
+                    ys.append(y)
+                cache.tensor[slot] = y
+                residual[r0:r1] += torch.stack(ys) @ self.w.t()
+
+    return EmaTableMixer
+
+
+def test_a_part_with_a_step_table_of_its_own_runs_in_a_captured_step(tmp_path):
+    from kappai_b200 import ModelRunner, StepEntry, write_random_model
+    from kappai_b200.config import register_architecture, unregister_architecture
+    from kappai_b200.parts import register_part, unregister_part
+    Mixer = make_toy_with_table()
+    register_part("mixer", "toy_ema", Mixer)
+    register_architecture("ToyForCausalLM", toy_config_cls(), toy_build_spec)
+    try:
+        cfg = dict(architectures=["ToyForCausalLM"], vocab_size=97, width=24, depth=2, ff=40, max_len=64)
+        d = write_random_model(cfg, str(tmp_path / "toy"), 6)
+        w = {k: v.astype(np.float64) for k, v in P.read_safetensors(os.path.join(d, "model.safetensors")).items()}
+        rng = np.random.default_rng(1)
+        seqs = {"a": rng.integers(0, 97, 12).tolist(), "b": rng.integers(0, 97, 12).tolist()}
+        ref = {k: toy_plain_logits(w, cfg, t) for k, t in seqs.items()}
+        r = ModelRunner(d, dtype="float32", max_tokens=128, max_requests=2, page_size=16)
+        assert r.model.graph_safe and list(r.model.table_builders) == ["toy_ema_fresh"]
+        # "a" starts with a portion of 5 tokens (eager step); "b" token by token from its very first token, so
+        # the first captured step has a fresh segment beside one that is not
+        out = r.step([StepEntry("a", seqs["a"][:5], [4])]).cpu().double().numpy()
+        assert np.abs(out[0] - ref["a"][4]).max() < 1e-4
+        for i in range(7):
+            ents = [StepEntry("a", [seqs["a"][5 + i]], [0]), StepEntry("b", [seqs["b"][i]], [0])]
+            out = r.step(ents).cpu().double().numpy()
+            assert np.abs(out[0] - ref["a"][5 + i]).max() < 1e-4, i
+            assert np.abs(out[1] - ref["b"][i]).max() < 1e-4, i
+        assert r.graphs.n_captures == 1 and r.graphs.n_replays >= 6
+        decode_tables = [fresh for decode_only, fresh in Mixer.calls if decode_only and len(fresh) == 2]
+        assert [0, 1] in decode_tables and decode_tables[-1] == [0, 0]        # the table was rebuilt for the replays
+    finally:
+        unregister_part("mixer", "toy_ema")
+        unregister_architecture("ToyForCausalLM")

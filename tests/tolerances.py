@@ -29,10 +29,20 @@ def fp32_tol_at_width(width):
     return FP32_ATOL * float(np.sqrt(max(width, 64) / 64.0))
 
 
-def bf16_rel_std_for_layers(n_layers):
-    """The bfloat16 bound, as a fraction of the logits' standard deviation, for a model of ``n_layers``.
+BF16_RMS_REL_STD = BF16_REL_STD / 3.53          # the same bound as a root-mean-square error: see below
+
+
+def bf16_bounds_for(n_layers, vocab):
+    """The bfloat16 bounds for a model of ``n_layers`` and a vocabulary of ``vocab``, as fractions of the
+    standard deviation of a row of logits: (bound on the largest error of the row, bound on its
+    root-mean-square error).
+
     Every layer adds two branch outputs to the float32 residual, each computed from operands rounded to
     bfloat16 (relative 2^-9 each, about six roundings a branch); the errors of the branches are independent,
-    so what reaches the logits grows like the square root of the number of layers.  BF16_REL_STD (5 %) is
-    the bound of the six-layer test models; sixteen layers get 5 % x sqrt(16 / 6) = 8.2 %."""
-    return BF16_REL_STD * float(np.sqrt(max(n_layers, 6) / 6.0))
+    so the error of a logit grows like the square root of the number of layers.  The errors of a row's logits
+    are close to Gaussian, and the largest of V Gaussians lies near sqrt(2 ln V) standard deviations: 3.53 for
+    the 512 logits of the six-layer test model, where BF16_REL_STD (5 %) is the bound on the largest error, so
+    its root-mean-square error is bounded by 5 % / 3.53 = 1.42 %; 4.71 for 65536 logits.  Sixteen layers and
+    65536 logits: rms 1.42 % x sqrt(16 / 6) = 2.3 %, largest 2.3 % x 4.71 = 10.9 %."""
+    rms = BF16_RMS_REL_STD * float(np.sqrt(max(n_layers, 6) / 6.0))
+    return rms * float(np.sqrt(2.0 * np.log(max(vocab, 512)))), rms
