@@ -7,6 +7,13 @@ arithmetic runs in float64 by default so that it can judge the float32 path of
 the engine as well as the bfloat16 one; ``dtype=np.float32`` gives the
 reference's own precision.
 
+``storage="bfloat16"`` makes it round to bfloat16 wherever the engine's bfloat16 mode stores a value in 16
+bits (the normalised rows that feed a product, the outputs of in_proj / q,k,v / gate and up, the conv and
+activation outputs, q and the cached k and v after the rotation, the softmax weights that go into the
+product with V, the attention output), with everything else as exact as before: what an ideal
+implementation with the engine's storage points computes.  The residual, the norms' statistics, the conv
+sums, the softmax and the logits are never rounded.
+
 Anchoring: tests/golden/ holds outputs of the reference's own C kernels
 (compiled on the CPU from its source tree) for the parts below, and
 tests/test_plain_vs_golden.py compares this file with them.
@@ -57,6 +64,14 @@ def intermediate_size(cfg):
         m = cfg.get("block_multiple_of", 256)
         ff = m * ((ff + m - 1) // m)
     return ff
+
+
+def round_bf16(a):
+    """Round to the nearest bfloat16 (ties to even), keeping the array's dtype."""
+    a32 = np.ascontiguousarray(a, dtype=np.float32)
+    u = a32.view(np.uint32)
+    u = (u + (((u >> 16) & 1) + np.uint32(0x7FFF))) & np.uint32(0xFFFF0000)
+    return u.view(np.float32).astype(a.dtype)
 
 
 # ------------------------------------------------------------------------ parts
@@ -122,7 +137,7 @@ def rope_neox(v, cos, sin):
     return out
 
 
-def attention(q, k, v, scale, window=None):
+def attention(q, k, v, scale, window=None, store=None):
     """Causal GQA attention of one whole sequence: q [T,H,hd], k,v [T,G,hd];
     head h reads kv head h // (H/G); keys 0..t (src/backend/cpu/scalar/core.c:
     383-433,623-666); scores = (q.k) * scale, softmax with the maximum
@@ -141,8 +156,12 @@ def attention(q, k, v, scale, window=None):
         s = np.where(mask, -np.inf, s)
         s = s - s.max(axis=-1, keepdims=True)
         p = np.exp(s)
-        p = p / p.sum(axis=-1, keepdims=True)
-        out[:, h, :] = p @ v[:, g, :]
+        if store is None:
+            p = p / p.sum(axis=-1, keepdims=True)
+            out[:, h, :] = p @ v[:, g, :]
+        else:
+            # the weights go into the product with V in 16 bits; their sum is taken before the rounding
+            out[:, h, :] = (store(p) @ v[:, g, :]) / p.sum(axis=-1, keepdims=True)
     return out
 
 
@@ -155,10 +174,13 @@ def swiglu(g, u):
 # ------------------------------------------------------------------------ model
 
 class PlainLfm2:
-    def __init__(self, model_dir, dtype=np.float64):
+    def __init__(self, model_dir, dtype=np.float64, storage=None):
         with open(os.path.join(model_dir, "config.json")) as f:
             self.cfg = json.load(f)
         self.dtype = dtype
+        if storage not in (None, "bfloat16"):
+            raise ValueError("storage: None or 'bfloat16'")
+        self.st = round_bf16 if storage == "bfloat16" else (lambda a: a)
         self.w = {k: v.astype(dtype) for k, v in read_safetensors(os.path.join(model_dir, "model.safetensors")).items()}
         c = self.cfg
         self.d = c["hidden_size"]
@@ -174,44 +196,46 @@ class PlainLfm2:
         """src/models/lfm.c:7-21"""
         w, p = self.w, f"model.layers.{i}.conv."
         b = (lambda n: w[p + n + ".bias"]) if self.bias else (lambda n: None)
-        proj = linear(h, w[p + "in_proj.weight"], b("in_proj"))
-        y = shortconv(proj, w[p + "conv.weight"], b("conv"))
+        proj = self.st(linear(h, w[p + "in_proj.weight"], b("in_proj")))
+        y = self.st(shortconv(proj, w[p + "conv.weight"], b("conv")))
         return linear(y, w[p + "out_proj.weight"], b("out_proj"))
 
     def attention_mixer(self, h, i):
         """src/models/lfm.c:23-53"""
         w, p = self.w, f"model.layers.{i}.self_attn."
         T = h.shape[0]
-        q = linear(h, w[p + "q_proj.weight"]).reshape(T, self.H, self.hd)
-        k = linear(h, w[p + "k_proj.weight"]).reshape(T, self.G, self.hd)
-        v = linear(h, w[p + "v_proj.weight"]).reshape(T, self.G, self.hd)
+        q = self.st(linear(h, w[p + "q_proj.weight"])).reshape(T, self.H, self.hd)
+        k = self.st(linear(h, w[p + "k_proj.weight"])).reshape(T, self.G, self.hd)
+        v = self.st(linear(h, w[p + "v_proj.weight"])).reshape(T, self.G, self.hd)
         q = rmsnorm(q, w[p + "q_layernorm.weight"], self.eps)
         k = rmsnorm(k, w[p + "k_layernorm.weight"], self.eps)
         cos, sin = rope_tables(T, self.hd, self.theta)
-        q = rope_neox(q, cos.astype(self.dtype), sin.astype(self.dtype))
-        k = rope_neox(k, cos.astype(self.dtype), sin.astype(self.dtype))
-        o = attention(q, k, v, 1.0 / math.sqrt(self.hd))          # src/recipe/builders.c:244-248
+        q = self.st(rope_neox(q, cos.astype(self.dtype), sin.astype(self.dtype)))
+        k = self.st(rope_neox(k, cos.astype(self.dtype), sin.astype(self.dtype)))
+        rounded = self.st is round_bf16
+        o = self.st(attention(q, k, v, 1.0 / math.sqrt(self.hd), store=round_bf16 if rounded else None))   # src/recipe/builders.c:244-248
         return linear(o.reshape(T, self.H * self.hd), w[p + "out_proj.weight"])
 
     def feed_forward(self, h, i):
         """src/recipe/builders.c:344-388"""
         w, p = self.w, f"model.layers.{i}.feed_forward."
-        return linear(swiglu(linear(h, w[p + "w1.weight"]), linear(h, w[p + "w3.weight"])), w[p + "w2.weight"])
+        g, u = self.st(linear(h, w[p + "w1.weight"])), self.st(linear(h, w[p + "w3.weight"]))
+        return linear(self.st(swiglu(g, u)), w[p + "w2.weight"])
 
     def hidden(self, tokens):
         w = self.w
         x = embedding(w["model.embed_tokens.weight"], tokens)
         for i, kind in enumerate(self.cfg["layer_types"]):
             p = f"model.layers.{i}."
-            h = rmsnorm(x, w[p + "operator_norm.weight"], self.eps)
+            h = self.st(rmsnorm(x, w[p + "operator_norm.weight"], self.eps))
             x = x + (self.conv_mixer(h, i) if kind == "conv" else self.attention_mixer(h, i))
-            h = rmsnorm(x, w[p + "ffn_norm.weight"], self.eps)
+            h = self.st(rmsnorm(x, w[p + "ffn_norm.weight"], self.eps))
             x = x + self.feed_forward(h, i)
         return x
 
     def logits(self, tokens):
         """[T, vocab] for the whole sequence (src/recipe/builders.c:450-468)."""
         x = self.hidden(tokens)
-        h = rmsnorm(x, self.w["model.embedding_norm.weight"], self.eps)
+        h = self.st(rmsnorm(x, self.w["model.embedding_norm.weight"], self.eps))
         head = self.w["model.embed_tokens.weight"] if self.cfg.get("tie_embedding", True) else self.w["lm_head.weight"]
         return linear(h, head)
