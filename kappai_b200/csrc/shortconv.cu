@@ -23,7 +23,20 @@
 template <typename T>
 __device__ __forceinline__ float bx_of(const T* __restrict__ p, size_t row, int ldp, int d, int c) {
     const T* r = p + row * ldp;
-    return to_f32(r[c]) * to_f32(r[2 * (size_t)d + c]);
+    return __fmul_rn(to_f32(r[c]), to_f32(r[2 * (size_t)d + c]));
+}
+
+// One arithmetic for every kernel of this file: each product and each sum is rounded on its own (no fused
+// multiply-add, which the compiler would place differently from kernel to kernel), so that which kernel runs
+// -- it depends on the shape of the step -- changes no bit of a row's result.
+__device__ __forceinline__ float tap(float h, float w) { return __fmul_rn(h, w); }
+__device__ __forceinline__ float add_tap(float sum, float h, float w) { return __fadd_rn(sum, __fmul_rn(h, w)); }
+// K == 3: (h0 w0 + h1 w1) + bx w2 (src/backend/cpu/common.c:2411)
+__device__ __forceinline__ float conv_sum3(float h0, float h1, float bx, float w0, float w1, float w2) {
+    return __fadd_rn(__fadd_rn(__fmul_rn(h0, w0), __fmul_rn(h1, w1)), __fmul_rn(bx, w2));
+}
+__device__ __forceinline__ float gate_out(float c, float sum, bool has_bias, float b) {
+    return __fmul_rn(c, has_bias ? __fadd_rn(sum, b) : sum);
 }
 
 template <typename T>
@@ -53,13 +66,13 @@ __global__ void shortconv_fwd_kernel(const T* __restrict__ p, int ldp, const flo
     }
     float sum;
     if (K == 3) {
-        sum = hist[0] * wc[0] + hist[1] * wc[1] + bx * wc[2];      // src/backend/cpu/common.c:2411
+        sum = conv_sum3(hist[0], hist[1], bx, wc[0], wc[1], wc[2]);
     } else {
-        sum = bx * wc[K - 1];                                      // src/backend/cpu/common.c:2422-2424
-        for (int k = 0; k < K - 1; k++) sum += hist[k] * wc[k];
+        sum = tap(bx, wc[K - 1]);                                  // src/backend/cpu/common.c:2422-2424
+        for (int k = 0; k < K - 1; k++) sum = add_tap(sum, hist[k], wc[k]);
     }
-    if (bias) sum += bias[c];
-    out[(size_t)row * ldo + c] = from_f32<T>(to_f32(p[(size_t)row * ldp + d + c]) * sum);
+    out[(size_t)row * ldo + c] = from_f32<T>(gate_out(to_f32(p[(size_t)row * ldp + d + c]), sum, bias != nullptr,
+                                                      bias ? bias[c] : 0.f));
 }
 
 template <typename T>
@@ -142,11 +155,11 @@ shortconv_fwd_vec_kernel(const T* __restrict__ p, int ldp, const float* __restri
     load_vec<T>(pr + d + c0, cv);
     load_vec<T>(pr + 2 * (size_t)d + c0, xv);
 #pragma unroll
-    for (int i = 0; i < V; i++) bx[i] = bv[i] * xv[i];
+    for (int i = 0; i < V; i++) bx[i] = __fmul_rn(bv[i], xv[i]);
     // same order of summation as the scalar kernel: K == 3: (h0 w0 + h1 w1) + bx w2; else bx w[K-1] + h0 w0 + ...
     if (K != 3) {
 #pragma unroll
-        for (int i = 0; i < V; i++) sum[i] = bx[i] * w[(size_t)(c0 + i) * K + K - 1];
+        for (int i = 0; i < V; i++) sum[i] = tap(bx[i], w[(size_t)(c0 + i) * K + K - 1]);
     }
     for (int k = 0; k < K - 1; k++) {
         const int st_t = t - (K - 1) + k;
@@ -157,7 +170,7 @@ shortconv_fwd_vec_kernel(const T* __restrict__ p, int ldp, const float* __restri
             load_vec<T>(ph + c0, hb);
             load_vec<T>(ph + 2 * (size_t)d + c0, hx);
 #pragma unroll
-            for (int i = 0; i < V; i++) h[i] = hb[i] * hx[i];
+            for (int i = 0; i < V; i++) h[i] = __fmul_rn(hb[i], hx[i]);
         } else {
 #pragma unroll
             for (int i = 0; i < V; i++) h[i] = fresh ? 0.f : st[(size_t)(K - 1 + st_t) * d + c0 + i];
@@ -165,21 +178,20 @@ shortconv_fwd_vec_kernel(const T* __restrict__ p, int ldp, const float* __restri
         if (K == 3) {
 #pragma unroll
             for (int i = 0; i < V; i++) {
-                const float term = h[i] * w[(size_t)(c0 + i) * K + k];
-                sum[i] = k == 0 ? term : sum[i] + term;
+                const float term = tap(h[i], w[(size_t)(c0 + i) * K + k]);
+                sum[i] = k == 0 ? term : __fadd_rn(sum[i], term);
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < V; i++) sum[i] += h[i] * w[(size_t)(c0 + i) * K + k];
+            for (int i = 0; i < V; i++) sum[i] = add_tap(sum[i], h[i], w[(size_t)(c0 + i) * K + k]);
         }
     }
     float o[V];
 #pragma unroll
     for (int i = 0; i < V; i++) {
         float s2 = sum[i];
-        if (K == 3) s2 += bx[i] * w[(size_t)(c0 + i) * K + 2];
-        if (bias) s2 += bias[c0 + i];
-        o[i] = cv[i] * s2;
+        if (K == 3) s2 = add_tap(s2, bx[i], w[(size_t)(c0 + i) * K + 2]);
+        o[i] = gate_out(cv[i], s2, bias != nullptr, bias ? bias[c0 + i] : 0.f);
     }
     store_vec(out + (size_t)row * ldo + c0, o);
 }
@@ -218,7 +230,7 @@ shortconv_fwd_rows_kernel(const T* __restrict__ p, int ldp, const float* __restr
             load_vec<T>(p + (size_t)r * ldp + c0, hb);
             load_vec<T>(p + (size_t)r * ldp + 2 * (size_t)d + c0, hx);
 #pragma unroll
-            for (int i = 0; i < V; i++) hist[k][i] = hb[i] * hx[i];
+            for (int i = 0; i < V; i++) hist[k][i] = __fmul_rn(hb[i], hx[i]);
         } else {
 #pragma unroll
             for (int i = 0; i < V; i++) hist[k][i] = 0.f;
@@ -234,7 +246,7 @@ shortconv_fwd_rows_kernel(const T* __restrict__ p, int ldp, const float* __restr
         load_vec<T>(pr + d + c0, cv);
         load_vec<T>(pr + 2 * (size_t)d + c0, xv);
 #pragma unroll
-        for (int i = 0; i < V; i++) bx[i] = bv[i] * xv[i];
+        for (int i = 0; i < V; i++) bx[i] = __fmul_rn(bv[i], xv[i]);
         if (t < KK - 1) {
             // the head of a segment: rows before it belong to another request; the history is the state (or zero)
             const bool fresh = seg_pos[seg] == 0;
@@ -250,18 +262,18 @@ shortconv_fwd_rows_kernel(const T* __restrict__ p, int ldp, const float* __restr
         }
         if (KK != 3) {
 #pragma unroll
-            for (int i = 0; i < V; i++) sum[i] = bx[i] * wk[KK - 1][i];
+            for (int i = 0; i < V; i++) sum[i] = tap(bx[i], wk[KK - 1][i]);
 #pragma unroll
             for (int k = 0; k < KK - 1; k++)
 #pragma unroll
-                for (int i = 0; i < V; i++) sum[i] += hist[k][i] * wk[k][i];
+                for (int i = 0; i < V; i++) sum[i] = add_tap(sum[i], hist[k][i], wk[k][i]);
         } else {
 #pragma unroll
-            for (int i = 0; i < V; i++) sum[i] = (hist[0][i] * wk[0][i] + hist[1][i] * wk[1][i]) + bx[i] * wk[2][i];
+            for (int i = 0; i < V; i++) sum[i] = conv_sum3(hist[0][i], hist[1][i], bx[i], wk[0][i], wk[1][i], wk[2][i]);
         }
         float o[V];
 #pragma unroll
-        for (int i = 0; i < V; i++) o[i] = cv[i] * (bias ? sum[i] + bs[i] : sum[i]);
+        for (int i = 0; i < V; i++) o[i] = gate_out(cv[i], sum[i], bias != nullptr, bs[i]);
         store_vec(out + (size_t)row * ldo + c0, o);
 #pragma unroll
         for (int k = 0; k + 1 < KK - 1; k++)
@@ -291,13 +303,13 @@ __global__ void shortconv_decode_kernel(const T* __restrict__ p, int ldp, const 
     for (int k = 0; k < K - 1; k++) hist[k] = fresh ? 0.f : st[(size_t)k * d + c];
     float sum;
     if (K == 3) {
-        sum = hist[0] * wc[0] + hist[1] * wc[1] + bx * wc[2];
+        sum = conv_sum3(hist[0], hist[1], bx, wc[0], wc[1], wc[2]);
     } else {
-        sum = bx * wc[K - 1];
-        for (int k = 0; k < K - 1; k++) sum += hist[k] * wc[k];
+        sum = tap(bx, wc[K - 1]);
+        for (int k = 0; k < K - 1; k++) sum = add_tap(sum, hist[k], wc[k]);
     }
-    if (bias) sum += bias[c];
-    out[(size_t)row * ldo + c] = from_f32<T>(to_f32(p[(size_t)row * ldp + d + c]) * sum);
+    out[(size_t)row * ldo + c] = from_f32<T>(gate_out(to_f32(p[(size_t)row * ldp + d + c]), sum, bias != nullptr,
+                                                      bias ? bias[c] : 0.f));
     for (int k = 0; k + 1 < K - 1; k++) st[(size_t)k * d + c] = hist[k + 1];
     st[(size_t)(K - 2) * d + c] = bx;
 }
