@@ -60,6 +60,18 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
         raise KernelError(f"{name}: expected a contiguous tensor")
 
 
+class _Stream:
+    """Stands for "the current stream" among a launcher's arguments."""
+
+
+STREAM = _Stream()
+
+
+def _run(what: str, fn, *args) -> None:
+    """The one door to the kernel libraries: call the launcher ``fn`` on the current stream and check its answer."""
+    _check(fn(*[_stream() if a is STREAM else a for a in args]), what)
+
+
 def _check(status: int, what: str) -> None:
     LAUNCHES[0] += 1
     LAUNCHES_BY[what] = LAUNCHES_BY.get(what, 0) + 1
@@ -144,8 +156,7 @@ class StatusGather:
         """out[0] (int32, on the device) = OR of the status words, in stream order."""
         _need(out, "out", torch.int32)
         self._refresh()
-        _check(load_library("rowwise").kp_gather_status(_ptr(self._addrs), self._addrs.numel(), _ptr(out), _stream()),
-               "gather_status")
+        _run("gather_status", load_library("rowwise").kp_gather_status, _ptr(self._addrs), self._addrs.numel(), _ptr(out), STREAM)
 
     def clear(self) -> dict:
         """Read and clear every word (synchronises); returns what was set."""
@@ -164,8 +175,8 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale:
     if table.shape[1] != d or ids.numel() != n:
         raise KernelError("embed_rows: shape mismatch")
     lib = load_library("rowwise")
-    _check(lib.kp_embed_rows(_ptr(table), _ptr(ids), _ptr(out), n, d, ctypes.c_float(scale),
-                             dtype_code(table.dtype), _stream()), "embed_rows")
+    _run("embed_rows", lib.kp_embed_rows, _ptr(table), _ptr(ids), _ptr(out), n, d, ctypes.c_float(scale),
+                             dtype_code(table.dtype), STREAM)
     return out
 
 
@@ -183,8 +194,8 @@ def rmsnorm_rows(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor
     elif x.shape[0] != n:
         raise KernelError("rmsnorm_rows: x/out mismatch")
     lib = load_library("rowwise")
-    _check(lib.kp_rmsnorm_rows(_ptr(x), _ptr(w), _ptr(out), _ptr(rows), n, d, ctypes.c_float(eps),
-                               dtype_code(out.dtype), _stream()), "rmsnorm_rows")
+    _run("rmsnorm_rows", lib.kp_rmsnorm_rows, _ptr(x), _ptr(w), _ptr(out), _ptr(rows), n, d, ctypes.c_float(eps),
+                               dtype_code(out.dtype), STREAM)
     return out
 
 
@@ -194,7 +205,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if gate_up.shape != (n, 2 * ff):
         raise KernelError("swiglu: shape mismatch")
     lib = load_library("rowwise")
-    _check(lib.kp_swiglu(_ptr(gate_up), _ptr(out), n, ff, dtype_code(out.dtype), _stream()), "swiglu")
+    _run("swiglu", lib.kp_swiglu, _ptr(gate_up), _ptr(out), n, ff, dtype_code(out.dtype), STREAM)
     return out
 
 
@@ -203,8 +214,8 @@ def cast(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
     if src.numel() != dst.numel():
         raise KernelError("cast: size mismatch")
     lib = load_library("rowwise")
-    _check(lib.kp_cast(_ptr(src), _ptr(dst), ctypes.c_longlong(src.numel()), dtype_code(src.dtype),
-                       dtype_code(dst.dtype), _stream()), "cast")
+    _run("cast", lib.kp_cast, _ptr(src), _ptr(dst), ctypes.c_longlong(src.numel()), dtype_code(src.dtype),
+                       dtype_code(dst.dtype), STREAM)
     return dst
 
 
@@ -234,8 +245,8 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
     else:
         raise KernelError("gemm: output dtype must be the operand dtype or float32")
     lib = load_library("gemm_simt")
-    _check(lib.kp_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldc, epi,
-                               dtype_code(a.dtype), _stream()), "gemm_nt_simt")
+    _run("gemm_nt_simt", lib.kp_gemm_nt_simt, _ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldc, epi,
+                               dtype_code(a.dtype), STREAM)
     return out
 
 
@@ -255,9 +266,9 @@ def shortconv_forward(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Ten
     if bias is not None:
         _need(bias, "bias", torch.float32)
     lib = load_library("shortconv")
-    _check(lib.kp_shortconv_forward(_ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(row_seg),
+    _run("shortconv_forward", lib.kp_shortconv_forward, _ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(row_seg),
                                     _ptr(cu_rows), _ptr(seg_pos), _ptr(seg_slot), _ptr(out), _rows_2d(out, "out"),
-                                    n, d, K, dtype_code(p.dtype), _stream()), "shortconv_forward")
+                                    n, d, K, dtype_code(p.dtype), STREAM)
     return out
 
 
@@ -274,9 +285,9 @@ def shortconv_decode(p: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tens
     if bias is not None:
         _need(bias, "bias", torch.float32)
     lib = load_library("shortconv")
-    _check(lib.kp_shortconv_decode(_ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(seg_pos),
+    _run("shortconv_decode", lib.kp_shortconv_decode, _ptr(p), _rows_2d(p, "p"), _ptr(w), _ptr(bias), _ptr(state), _ptr(seg_pos),
                                    _ptr(seg_slot), _ptr(out), _rows_2d(out, "out"), n, d, K, dtype_code(p.dtype),
-                                   _stream()), "shortconv_decode")
+                                   STREAM)
     return out
 
 
@@ -288,9 +299,8 @@ def shortconv_update_state(p: torch.Tensor, state: torch.Tensor, cu_rows: torch.
     if state.shape[2] != d:
         raise KernelError("shortconv_update_state: shape mismatch")
     lib = load_library("shortconv")
-    _check(lib.kp_shortconv_update_state(_ptr(p), _rows_2d(p, "p"), _ptr(state), _ptr(cu_rows), _ptr(seg_pos),
-                                         _ptr(seg_slot), n_seg, d, K, dtype_code(p.dtype), _stream()),
-           "shortconv_update_state")
+    _run("shortconv_update_state", lib.kp_shortconv_update_state, _ptr(p), _rows_2d(p, "p"), _ptr(state), _ptr(cu_rows), _ptr(seg_pos),
+                                         _ptr(seg_slot), n_seg, d, K, dtype_code(p.dtype), STREAM)
 
 
 # ------------------------------------------------------------------ attention
@@ -329,11 +339,11 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Optiona
         if tuple(cache.shape[1:]) != (2, G, page_size, hd):
             raise KernelError(f"qk_norm_rope_kv: cache layout {tuple(cache.shape)}")
     lib = load_library("qkrope")
-    _check(lib.kp_qk_norm_rope_kv(_ptr(qkv), _rows_2d(qkv, "qkv"), _ptr(q_w), _ptr(k_w), ctypes.c_float(eps),
+    _run("qk_norm_rope_kv", lib.kp_qk_norm_rope_kv, _ptr(qkv), _rows_2d(qkv, "qkv"), _ptr(q_w), _ptr(k_w), ctypes.c_float(eps),
                                   _ptr(cos_tab), _ptr(sin_tab), rotary_dim, int(interleaved), _ptr(positions),
                                   _ptr(slot_map), _ptr(q_out), 0 if q_out is None else _rows_2d(q_out, "q_out"), _ptr(cache),
                                   page_size,
-                                  n, H, G, hd, int(write_kv), dtype_code(qkv.dtype), _stream()), "qk_norm_rope_kv")
+                                  n, H, G, hd, int(write_kv), dtype_code(qkv.dtype), STREAM)
     return q_out
 
 
@@ -347,10 +357,10 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tens
     if q.shape[1] != H * hd or out.shape != (n, H * hd) or tuple(cache.shape[1:]) != (2, G, page_size, hd):
         raise KernelError("attention_rows: shape mismatch")
     lib = load_library("attention")
-    _check(lib.kp_attention_rows(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
+    _run("attention_rows", lib.kp_attention_rows, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
                                  _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"),
                                  ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
-                                 dtype_code(q.dtype), _stream()), "attention_rows")
+                                 dtype_code(q.dtype), STREAM)
     return out
 
 
@@ -386,23 +396,21 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
     if USE_MMA_ATTENTION and q.dtype == torch.bfloat16 and hd in (64, 128) and q.stride(0) % 2 == 0:
         # tensor-core chunk pass over smaller chunks, then the same merge
         parts = n_chunks * (SPLIT_CHUNK // SPLIT_CHUNK_MMA)
-        _check(load_library("attention_mma").kp_attention_split_mma(
+        _run("attention_split_mma", load_library("attention_mma").kp_attention_split_mma, 
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), page_size,
             n, H, G, hd, _ptr(out) if fused_merge else ctypes.c_void_p(0), _rows_2d(out, "out"),
-            ctypes.c_longlong(scratch.numel()), _stream()),
-            "attention_split_mma")
+            ctypes.c_longlong(scratch.numel()), STREAM)
         if fused_merge:
             return out
-        _check(lib.kp_attention_merge(_ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
-                                      SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), _stream()),
-               "attention_merge")
+        _run("attention_merge", lib.kp_attention_merge, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
+                                      SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
-    _check(lib.kp_attention_split(_ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
+    _run("attention_split", lib.kp_attention_split, _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1],
                                   _ptr(row_seg), _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch),
                                   n_chunks, ctypes.c_float(scale), int(window or 0), page_size, n, H, G, hd,
-                                  dtype_code(q.dtype), _stream()), "attention_split")
+                                  dtype_code(q.dtype), STREAM)
     LAUNCHES[0] += 1
     return out
 
@@ -451,17 +459,16 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, block_table: torch.T
         _need(big_tile_seg, "big_tile_seg", torch.int32); _need(big_tile_row0, "big_tile_row0", torch.int32)
         if big_tile_seg.numel() != big_tile_row0.numel():
             raise KernelError("attention_prefill: tile lists differ in length")
-        _check(load_library("attention_tc").kp_attention_prefill_tc(
+        _run("attention_prefill_tc", load_library("attention_tc").kp_attention_prefill_tc, 
             _ptr(q), _rows_2d(q, "q"), n, _ptr(cache), ctypes.c_longlong(cache.shape[0]), _ptr(block_table),
             block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos), _ptr(big_tile_seg), _ptr(big_tile_row0),
             big_tile_seg.numel(),
-            _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), page_size, H, G, hd, _stream()),
-            "attention_prefill_tc")
+            _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale), int(window or 0), page_size, H, G, hd, STREAM)
         return out
-    _check(load_library("attention_mma").kp_attention_prefill_mma(
+    _run("attention_prefill_mma", load_library("attention_mma").kp_attention_prefill_mma, 
         _ptr(q), _rows_2d(q, "q"), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(cu_rows), _ptr(seg_pos),
         _ptr(tile_seg), _ptr(tile_row0), tile_seg.numel(), _ptr(out), _rows_2d(out, "out"), ctypes.c_float(scale),
-        int(window or 0), page_size, H, G, hd, _stream()), "attention_prefill_mma")
+        int(window or 0), page_size, H, G, hd, STREAM)
     return out
 
 
@@ -516,8 +523,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             raise KernelError("gemm_tc: bias size")
     epi = _skinny_epilogue(out, accumulate, swiglu)
     lib = load_library("gemm_tc")
-    _check(lib.kp_gemm_tc(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                          _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_tc")
+    _run("gemm_tc", lib.kp_gemm_tc, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                          _rows_2d(out, "out"), M, N, K, epi, STREAM)
     return out
 
 
@@ -569,14 +576,14 @@ def gemm_skinny_norm(x: torch.Tensor, norm_w: torch.Tensor, eps: float, rows: Op
     epi = _skinny_epilogue(out, accumulate, swiglu)
     if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K):
         lib = load_library("gemm_stream")
-        _check(lib.kp_gemm_stream_norm(_ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows),
+        _run("gemm_stream_norm", lib.kp_gemm_stream_norm, _ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows),
                                        _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K,
-                                       epi, _stream()), "gemm_stream_norm")
+                                       epi, STREAM)
         return out
     lib = load_library("gemm_skinny")
-    _check(lib.kp_gemm_skinny_norm(_ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows), _ptr(w),
+    _run("gemm_skinny_norm", lib.kp_gemm_skinny_norm, _ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows), _ptr(w),
                                    _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, epi,
-                                   _stream()), "gemm_skinny_norm")
+                                   STREAM)
     return out
 
 
@@ -627,10 +634,10 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
         raise KernelError("gemm_skinny: output dtype")
     if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K) and M <= STREAM_MAX_M:
         lib = load_library("gemm_stream")
-        _check(lib.kp_gemm_stream(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                                  _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_stream")
+        _run("gemm_stream", lib.kp_gemm_stream, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                                  _rows_2d(out, "out"), M, N, K, epi, STREAM)
         return out
     lib = load_library("gemm_skinny")
-    _check(lib.kp_gemm_skinny(_ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                              _rows_2d(out, "out"), M, N, K, epi, _stream()), "gemm_skinny")
+    _run("gemm_skinny", lib.kp_gemm_skinny, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
+                              _rows_2d(out, "out"), M, N, K, epi, STREAM)
     return out
