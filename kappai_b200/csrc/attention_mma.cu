@@ -131,8 +131,7 @@ __global__ void __launch_bounds__(NW * 32)
 attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache,
                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                      int n_chunks, float scale, int window, int page_size, int H, int G,
-                      int* __restrict__ counters, bf16* __restrict__ out, int ldo) {
+                      int n_chunks, float scale, int window, int page_size, int H, int G) {
     kp_pdl_begin_early_if(gridDim.z > 1);
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_raw = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
@@ -291,35 +290,6 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
         ml[0] = M;
         ml[1] = L;
     }
-    if (counters == nullptr) return;                              // the caller merges with a kernel of its own
-    // The CTA that brings the last chunk of this (row, kv head) merges the chunks, in chunk order (so the
-    // result does not depend on which came last), as attn_merge_kernel does: one launch less in a decode step.
-    __shared__ int last_s;
-    __threadfence();
-    __syncthreads();
-    const int c_lo = k_lo / CHUNK, c_hi = k_hi / CHUNK;
-    if (tid == 0) {
-        int* cnt = counters + (size_t)row * G + kvh;
-        const int last = atomicAdd(cnt, 1) == c_hi - c_lo;
-        if (last) *cnt = 0;                                        // every chunk has come: ready for the next step
-        last_s = last;
-    }
-    __syncthreads();
-    if (!last_s) return;
-    __threadfence();
-    for (int e = tid; e < R * HD; e += NW * 32) {
-        const int r = e / HD, d = e % HD;
-        const float* ml = part_ml + ((size_t)row * H + kvh * R + r) * n_chunks * 2;
-        const float* pa = part_acc + ((size_t)row * H + kvh * R + r) * n_chunks * HD;
-        float mm = -INFINITY;
-        for (int c = c_lo; c <= c_hi; c++) mm = fmaxf(mm, __ldcg(ml + 2 * c));
-        float ll = 0.f;
-        for (int c = c_lo; c <= c_hi; c++) ll += __ldcg(ml + 2 * c + 1) * expf(__ldcg(ml + 2 * c) - mm);
-        const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-        float v = 0.f;
-        for (int c = c_lo; c <= c_hi; c++) v = fmaf(__ldcg(pa + (size_t)c * HD + d), expf(__ldcg(ml + 2 * c) - mm), v);
-        out[(size_t)row * ldo + (size_t)(kvh * R + r) * HD + d] = from_f32<bf16>(v * inv);
-    }
 }
 
 // ------------------------------------------------------------------ prefill (segments of many rows)
@@ -456,8 +426,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
 template <int HD, int NW>
 static int launch_split(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
                         int max_blocks, const int* row_seg, const int* positions, float* part_acc, float* part_ml,
-                        int n_chunks, float scale, int window, int page_size, int n, int H, int G, int* counters,
-                        void* out, int ldo, cudaStream_t s) {
+                        int n_chunks, float scale, int window, int page_size, int n, int H, int G, cudaStream_t s) {
     const size_t smem = 1024 + (size_t)2 * NW * AM_TILE * HD * 2 + sizeof(float) * (NW * AM_RMAX * HD + 2 * NW * AM_RMAX) + 16;
     alignas(64) CUtensorMap tm = {};
     // tiles by TMA where the pages allow it (and the cache is known by its size), else by cp.async
@@ -472,7 +441,7 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
     }
     kp_launch_pdl(kern, dim3(dim3(n_chunks, G, n)), dim3(NW * 32), smem, s, tm,
         (const bf16*)q, ldq, (const bf16*)cache, block_table, max_blocks, row_seg, positions, part_acc, part_ml,
-        n_chunks, scale, window, page_size, H, G, counters, (bf16*)out, ldo);
+        n_chunks, scale, window, page_size, H, G);
     return kp_launch_status();
 }
 
@@ -492,30 +461,21 @@ static int launch_prefill(const void* q, int ldq, const void* cache, const int* 
 extern "C" {
 
 // The chunk partials of the split pass (bfloat16, head size 64 or 128, H/G <= 8); chunks of `chunk_keys` keys
-// (64, 128 or 256), n_chunks of them.  With `out` the kernel also merges the chunks (the last CTA of each row
-// and kv head does); the last n * G words of the scratch (of `scratch_elems` floats) are then counters that
-// must be zero before the first use and are left zero.  Without, the caller runs the merge of attention_decode.cu afterwards (kp_attention_merge, same
-// chunk size) on the same scratch.
+// (64, 128 or 256), n_chunks of them, into `scratch` (n * H * n_chunks * (hd + 2) floats).  The caller runs the
+// merge of attention_decode.cu afterwards (kp_attention_merge, same chunk size) on the same scratch.
 int kp_attention_split_mma(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table, int max_blocks,
                            const int* row_seg, const int* positions, float* scratch, int n_chunks, int chunk_keys,
-                           float scale, int window, int page_size, int n, int H, int G, int hd, void* out, int ldo,
-                           long long scratch_elems, void* stream) {
+                           float scale, int window, int page_size, int n, int H, int G, int hd, void* stream) {
     if (n <= 0) return 0;
     if ((hd != 64 && hd != 128) || G < 1 || H % G || H / G > AM_RMAX || page_size < 1 || n_chunks < 1 || n > 65535 ||
         G > 65535 || (ldq & 1) || (chunk_keys != 64 && chunk_keys != 128 && chunk_keys != 256))
         return KP_ERR_UNSUPPORTED;
     float* part_acc = scratch;
     float* part_ml = scratch + (size_t)n * H * n_chunks * hd;
-    int* counters = nullptr;
-    if (out) {
-        // at the end of the scratch, where no call ever keeps partial results
-        if ((ldo & 1) || scratch_elems < (long long)n * H * n_chunks * (hd + 2) + (long long)n * G) return KP_ERR_UNSUPPORTED;
-        counters = reinterpret_cast<int*>(scratch + scratch_elems) - (size_t)n * G;
-    }
     cudaStream_t s = (cudaStream_t)stream;
 #define AM_SPLIT(HD, NW)                                                                                          \
     return launch_split<HD, NW>(q, ldq, cache, n_pages, block_table, max_blocks, row_seg, positions, part_acc, part_ml, \
-                                n_chunks, scale, window, page_size, n, H, G, counters, out, ldo, s)
+                                n_chunks, scale, window, page_size, n, H, G, s)
     if (hd == 64) {
         if (chunk_keys == 64) AM_SPLIT(64, 1);
         if (chunk_keys == 128) AM_SPLIT(64, 2);

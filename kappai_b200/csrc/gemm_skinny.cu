@@ -10,10 +10,6 @@
 // in warp order, so an output depends on its own activation row only, whatever
 // M is.
 //
-// Fused in front (NORM, M <= 16): the A operand is RMSNorm of the float32
-// residual, a = bf16((x * rsqrt(mean(x^2) + eps)) * w), computed by the CTA
-// while its first weight loads are in flight (src/backend/cpu/scalar/quants.c:
-// 1489-1512 for the formula).  `rows` optionally gathers the rows of x.
 // Epilogues: bias; store bf16 / store fp32 / accumulate into fp32 (residual);
 // SwiGLU (W holds gate rows then up rows, ff apart; the CTA streams both and
 // writes silu(g)*u).  K must be a multiple of 32 and rows 16-byte aligned.
@@ -53,23 +49,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 
-// 8 normalised activations of row x at k..k+7 as four packed bf16 pairs
-__device__ __forceinline__ uint4 normed8(const float* __restrict__ x, const float* __restrict__ nw, float scale) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(x)), b = __ldg(reinterpret_cast<const float4*>(x) + 1);
-    const float4 wa = __ldg(reinterpret_cast<const float4*>(nw)), wb = __ldg(reinterpret_cast<const float4*>(nw) + 1);
-    uint4 r;
-    r.x = pack_bf16((a.x * scale) * wa.x, (a.y * scale) * wa.y);
-    r.y = pack_bf16((a.z * scale) * wa.z, (a.w * scale) * wa.w);
-    r.z = pack_bf16((b.x * scale) * wb.x, (b.y * scale) * wb.y);
-    r.w = pack_bf16((b.z * scale) * wb.z, (b.w * scale) * wb.w);
-    return r;
-}
-
 struct SkinnyArgs {
-    const bf16* A; int lda;              // bf16 activations (NORM = false)
-    const float* X; int ldx;             // float32 residual (NORM = true)
-    const float* norm_w; float eps;
-    const int* rows;                     // optional gather of the rows of X
+    const bf16* A; int lda;              // bf16 activations
     const bf16* W; int ldw;
     const float* bias;
     void* C; int ldc;
@@ -79,14 +60,13 @@ struct SkinnyArgs {
 // MT: m16 tiles of batch rows; HALF: only rows 0..7 of the single tile exist (M <= 8).
 // Each warp walks its k-blocks in stages of SK_U blocks, two stages in flight: the loads of the next
 // stage are issued before the products of the current one.
-template <int MT, bool HALF, int EPI, bool NORM>
+template <int MT, bool HALF, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const SkinnyArgs p) {
     constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;          // weight streams
     constexpr int U = SK_U;
     constexpr int STEP = SK_WARPS * U;
     __shared__ float red[SK_WARPS][NW][MT][4][32];
-    __shared__ float scales[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int M = p.M, K = p.K;
     const int n0 = blockIdx.x * 8;
@@ -118,26 +98,7 @@ gemm_skinny_kernel(const SkinnyArgs p) {
     for (int mt = 0; mt < MT; mt++) {
         r0[mt] = min(mt * 16 + g, M - 1);
         r1[mt] = min(mt * 16 + g + 8, M - 1);
-        if (NORM && p.rows) { r0[mt] = p.rows[r0[mt]]; r1[mt] = p.rows[r1[mt]]; }
     }
-    if (NORM) {
-        // per-row scale: warp w takes rows w and w + SK_WARPS (M <= 16)
-        for (int row = warp; row < M; row += SK_WARPS) {
-            const int xr = p.rows ? p.rows[row] : row;
-            const float4* xp = reinterpret_cast<const float4*>(p.X + (size_t)xr * p.ldx);
-            float ss = 0.f;
-            for (int i = lane; i < (K >> 2); i += 32) {
-                const float4 v = __ldg(xp + i);
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) scales[row] = 1.0f / sqrtf(ss / (float)K + p.eps);
-        }
-        __syncthreads();
-    }
-    float sc0 = 0.f, sc1 = 0.f;
-    if (NORM) { sc0 = scales[min(g, M - 1)]; sc1 = scales[min(g + 8, M - 1)]; }
-
     float acc[NW][MT][4];
 #pragma unroll
     for (int w = 0; w < NW; w++)
@@ -154,14 +115,8 @@ gemm_skinny_kernel(const SkinnyArgs p) {
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
                     uint4 lo, hi = make_uint4(0, 0, 0, 0);
-                    if (NORM) {
-                        const int k = kb * 32 + 8 * t;
-                        lo = normed8(p.X + (size_t)r0[mt] * p.ldx + k, p.norm_w + k, sc0);
-                        if (!HALF) hi = normed8(p.X + (size_t)r1[mt] * p.ldx + k, p.norm_w + k, sc1);
-                    } else {
-                        lo = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r0[mt] * p.lda) + kb * 4 + t);
-                        if (!HALF) hi = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r1[mt] * p.lda) + kb * 4 + t);
-                    }
+                    lo = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r0[mt] * p.lda) + kb * 4 + t);
+                    if (!HALF) hi = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r1[mt] * p.lda) + kb * 4 + t);
 #pragma unroll
                     for (int w = 0; w < NW; w++) {
                         mma_bf16(acc[w][mt], lo.x, hi.x, lo.y, hi.y, wv[u][w].x, wv[u][w].y);
@@ -231,27 +186,25 @@ static int launch_pdl(Kern kern, dim3 grid, cudaStream_t s, const SkinnyArgs& a)
     return (int)e;
 }
 
-template <int MT, bool HALF, bool NORM>
+template <int MT, bool HALF>
 static int launch_epi(const SkinnyArgs& a, int epi, cudaStream_t s) {
     const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
     dim3 grid((n_out + 7) / 8);
     switch (epi) {
-        case EPI_STORE: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE, NORM>, grid, s, a);
-        case EPI_STORE_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE_F32, NORM>, grid, s, a);
-        case EPI_ACCUM_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_ACCUM_F32, NORM>, grid, s, a);
-        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_SWIGLU, NORM>, grid, s, a);
+        case EPI_STORE: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE>, grid, s, a);
+        case EPI_STORE_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_STORE_F32>, grid, s, a);
+        case EPI_ACCUM_F32: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_ACCUM_F32>, grid, s, a);
+        case EPI_SWIGLU: return launch_pdl(gemm_skinny_kernel<MT, HALF, EPI_SWIGLU>, grid, s, a);
         default: return KP_ERR_BAD_ARG;
     }
 }
 
-template <bool NORM>
 static int launch_m(const SkinnyArgs& a, int epi, cudaStream_t s) {
-    if (a.M <= 8) return launch_epi<1, true, NORM>(a, epi, s);
-    if (a.M <= 16) return launch_epi<1, false, NORM>(a, epi, s);
-    if (NORM) return KP_ERR_UNSUPPORTED;
-    if (a.M <= 32) return launch_epi<2, false, false>(a, epi, s);
-    if (a.M <= 48) return launch_epi<3, false, false>(a, epi, s);
-    return launch_epi<4, false, false>(a, epi, s);
+    if (a.M <= 8) return launch_epi<1, true>(a, epi, s);
+    if (a.M <= 16) return launch_epi<1, false>(a, epi, s);
+    if (a.M <= 32) return launch_epi<2, false>(a, epi, s);
+    if (a.M <= 48) return launch_epi<3, false>(a, epi, s);
+    return launch_epi<4, false>(a, epi, s);
 }
 
 static int check_common(int M, int N, int K, int ldw, const void* W, int epi, int* ff) {
@@ -276,20 +229,7 @@ int kp_gemm_skinny(const void* A, int lda, const void* W, int ldw, const float* 
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;
     a.A = (const bf16*)A; a.lda = lda; a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc;
     a.M = M; a.N = N; a.K = K;
-    return launch_m<false>(a, epi, (cudaStream_t)stream);
-}
-
-// The same with RMSNorm of the float32 rows X (optionally gathered by `rows`) fused in front; M <= 16.
-int kp_gemm_skinny_norm(const float* X, int ldx, const float* norm_w, float eps, const int* rows, const void* W,
-                        int ldw, const float* bias, void* C, int ldc, int M, int N, int K, int epi, void* stream) {
-    if (M <= 0 || N <= 0) return 0;
-    SkinnyArgs a = {};
-    int st = check_common(M, N, K, ldw, W, epi, &a.ff);
-    if (st) return st;
-    if (M > 16 || (ldx & 3) || ((uintptr_t)X & 15) || ((uintptr_t)norm_w & 15)) return KP_ERR_UNSUPPORTED;
-    a.X = X; a.ldx = ldx; a.norm_w = norm_w; a.eps = eps; a.rows = rows;
-    a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
-    return launch_m<true>(a, epi, (cudaStream_t)stream);
+    return launch_m(a, epi, (cudaStream_t)stream);
 }
 
 }  // extern "C"

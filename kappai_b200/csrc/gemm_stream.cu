@@ -19,8 +19,7 @@
 //    global memory (L1 serves them), and issue mma.m16n8k16 with the batch rows on the m side.  At a tile's
 //    end their partial sums are added in warp order, so an output depends on its own activation row only.
 //
-// Fused in front (NORM, M <= 16): A = bf16((x * rsqrt(mean(x^2)+eps)) * w) of the float32 residual rows
-// (src/backend/cpu/scalar/quants.c:1489-1512).  Epilogues: bias; store bf16 / fp32; accumulate into fp32;
+// Epilogues: bias; store bf16 / fp32; accumulate into fp32;
 // SwiGLU.  Every mbarrier wait is bounded; a wait that gives up sets a status word (kp_stream_status) and
 // the warp stops waiting for further stages.
 //
@@ -77,22 +76,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ uint4 normed8(const float* __restrict__ x, const float* __restrict__ nw, float scale) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(x)), b = __ldg(reinterpret_cast<const float4*>(x) + 1);
-    const float4 wa = __ldg(reinterpret_cast<const float4*>(nw)), wb = __ldg(reinterpret_cast<const float4*>(nw) + 1);
-    uint4 r;
-    r.x = pack_bf16((a.x * scale) * wa.x, (a.y * scale) * wa.y);
-    r.y = pack_bf16((a.z * scale) * wa.z, (a.w * scale) * wa.w);
-    r.z = pack_bf16((b.x * scale) * wb.x, (b.y * scale) * wb.y);
-    r.w = pack_bf16((b.z * scale) * wb.z, (b.w * scale) * wb.w);
-    return r;
-}
-
 struct StreamArgs {
-    const bf16* A; int lda;              // bf16 activations (NORM = false)
-    const float* X; int ldx;             // float32 residual (NORM = true)
-    const float* norm_w; float eps;
-    const int* rows;                     // optional gather of the rows of X
+    const bf16* A; int lda;              // bf16 activations
     const bf16* W; int ldw;
     const float* bias;
     void* C; int ldc;
@@ -100,10 +85,10 @@ struct StreamArgs {
     int n_stages;                        // stages of the ring
 };
 
-// shared memory: [ring: n_stages x NW*8 rows x ST_ROW_BYTES][full[n_stages]][empty[n_stages]][red][scales]
+// shared memory: [ring: n_stages x NW*8 rows x ST_ROW_BYTES][full[n_stages]][empty[n_stages]][red]
 // WIDE (more than 16 batch rows, no SwiGLU): a tile is 16 rows of W, so that an activation fragment, whose
 // loads weigh more than the weights' once there are several m-tiles, serves two n-tiles.
-template <int MT, bool HALF, int EPI, bool NORM, bool WIDE>
+template <int MT, bool HALF, int EPI, bool WIDE>
 __global__ void __launch_bounds__(ST_THREADS)
 gemm_stream_kernel(const StreamArgs p) {
     constexpr int NW = (EPI == EPI_SWIGLU || WIDE) ? 2 : 1;
@@ -117,7 +102,6 @@ gemm_stream_kernel(const StreamArgs p) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * STAGE_BYTES);
     uint64_t* empty = full + S;
     float* red = reinterpret_cast<float*>(empty + S);                    // [ST_CONSUMERS][NW][MT][4][32]
-    float* scales = red + ST_CONSUMERS * NW * MT * 128;                  // [16]
     const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
     const int n_tiles = (n_out + TROWS - 1) / TROWS;
     const int n_chunks = K / ST_COLS;
@@ -173,37 +157,13 @@ gemm_stream_kernel(const StreamArgs p) {
     for (int mt = 0; mt < MT; mt++) {
         r0[mt] = min(mt * 16 + g, M - 1);
         r1[mt] = min(mt * 16 + g + 8, M - 1);
-        if (NORM && p.rows) { r0[mt] = p.rows[r0[mt]]; r1[mt] = p.rows[r1[mt]]; }
     }
-    if (NORM) {
-        for (int row = warp; row < M; row += ST_CONSUMERS) {
-            const int xr = p.rows ? p.rows[row] : row;
-            const float4* xp = reinterpret_cast<const float4*>(p.X + (size_t)xr * p.ldx);
-            float ss = 0.f;
-            for (int i = lane; i < (K >> 2); i += 32) {
-                const float4 v = __ldg(xp + i);
-                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) scales[row] = 1.0f / sqrtf(ss / (float)K + p.eps);
-        }
-        consumer_sync();
-    }
-    float sc0 = 0.f, sc1 = 0.f;
-    if (NORM) { sc0 = scales[min(g, M - 1)]; sc1 = scales[min(g + 8, M - 1)]; }
-
     auto load_acts = [&](uint4 (&lo)[MT], uint4 (&hi)[MT], int kb) {
 #pragma unroll
         for (int mt = 0; mt < MT; mt++) {
             hi[mt] = make_uint4(0, 0, 0, 0);
-            if (NORM) {
-                const int k = kb * 32 + 8 * t;
-                lo[mt] = normed8(p.X + (size_t)r0[mt] * p.ldx + k, p.norm_w + k, sc0);
-                if (!HALF) hi[mt] = normed8(p.X + (size_t)r1[mt] * p.ldx + k, p.norm_w + k, sc1);
-            } else {
-                lo[mt] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r0[mt] * p.lda) + kb * 4 + t);
-                if (!HALF) hi[mt] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r1[mt] * p.lda) + kb * 4 + t);
-            }
+            lo[mt] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r0[mt] * p.lda) + kb * 4 + t);
+            if (!HALF) hi[mt] = __ldg(reinterpret_cast<const uint4*>(p.A + (size_t)r1[mt] * p.lda) + kb * 4 + t);
         }
     };
 
@@ -302,7 +262,7 @@ gemm_stream_kernel(const StreamArgs p) {
 
 static size_t smem_bytes(int NW, int MT, int n_stages) {
     return (size_t)n_stages * NW * 8 * ST_ROW_BYTES + (size_t)2 * n_stages * 8 +
-           sizeof(float) * (ST_CONSUMERS * NW * MT * 128 + 16);
+           sizeof(float) * (ST_CONSUMERS * NW * MT * 128);
 }
 
 static int n_sm() {
@@ -315,8 +275,6 @@ static int n_sm() {
     return n;
 }
 
-static int g_ctas_per_sm = 0;                // persistent CTAs an SM; 0: chosen by the product's tiles (see launch_epi)
-static int g_ring_bytes = 0;                 // bytes of the ring; 0: likewise (both can be set for measurements)
 
 template <typename Kern>
 static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const StreamArgs& a) {
@@ -327,7 +285,7 @@ static int launch_pdl(Kern kern, dim3 grid, size_t smem, cudaStream_t s, const S
     return (int)kp_launch_pdl(kern, grid, dim3(ST_THREADS), smem, s, a);
 }
 
-template <int MT, bool HALF, bool NORM>
+template <int MT, bool HALF>
 static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     // tiles of 16 rows of W from three m-tiles on (see the kernel; measured at 64 batch rows: 2048 x 5632 15.5 us
     // against 23.7, 2048 x 2048 8.0 against 12.2; at 32 rows the narrow tile is as fast or faster)
@@ -339,8 +297,8 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     // many tiles (6144 x 2048: 6.9 us against 8.1 with 53 KB); a product with at most two tiles an SM (2048
     // rows) does better with two CTAs an SM and more of its long rows in flight (2048 x 5632: 8.3 against 10.3).
     const bool few = n_tiles <= 2 * n_sm();
-    const int per_sm = g_ctas_per_sm ? g_ctas_per_sm : (few ? 2 : 3);
-    const int ring = g_ring_bytes ? g_ring_bytes : (few ? ST_RING_BYTES_FEW : ST_RING_BYTES);
+    const int per_sm = few ? 2 : 3;
+    const int ring = few ? ST_RING_BYTES_FEW : ST_RING_BYTES;
     a.n_stages = ring / (NW * 8 * ST_ROW_BYTES);
     if (a.n_stages < 2) a.n_stages = 2;
     int g = n_sm() * per_sm;
@@ -348,22 +306,20 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     dim3 grid(g);
     const size_t sm = smem_bytes(NW, MT, a.n_stages);
     switch (epi) {
-        case EPI_STORE: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE, NORM, WIDE>, grid, sm, s, a);
-        case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, NORM, WIDE>, grid, sm, s, a);
-        case EPI_ACCUM_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_ACCUM_F32, NORM, WIDE>, grid, sm, s, a);
-        case EPI_SWIGLU: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_SWIGLU, NORM, false>, grid, sm, s, a);
+        case EPI_STORE: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE, WIDE>, grid, sm, s, a);
+        case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, WIDE>, grid, sm, s, a);
+        case EPI_ACCUM_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_ACCUM_F32, WIDE>, grid, sm, s, a);
+        case EPI_SWIGLU: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_SWIGLU, false>, grid, sm, s, a);
         default: return KP_ERR_BAD_ARG;
     }
 }
 
-template <bool NORM>
 static int launch_m(const StreamArgs& a, int epi, cudaStream_t s) {
-    if (a.M <= 8) return launch_epi<1, true, NORM>(a, epi, s);
-    if (a.M <= 16) return launch_epi<1, false, NORM>(a, epi, s);
-    if (NORM) return KP_ERR_UNSUPPORTED;
-    if (a.M <= 32) return launch_epi<2, false, false>(a, epi, s);
-    if (a.M <= 48) return launch_epi<3, false, false>(a, epi, s);
-    return launch_epi<4, false, false>(a, epi, s);
+    if (a.M <= 8) return launch_epi<1, true>(a, epi, s);
+    if (a.M <= 16) return launch_epi<1, false>(a, epi, s);
+    if (a.M <= 32) return launch_epi<2, false>(a, epi, s);
+    if (a.M <= 48) return launch_epi<3, false>(a, epi, s);
+    return launch_epi<4, false>(a, epi, s);
 }
 
 static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void* W, int epi) {
@@ -378,10 +334,6 @@ static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void*
 
 extern "C" {
 
-// Persistent CTAs an SM (1..4), for measurements.
-void kp_gemm_stream_set_ctas_per_sm(int n) { g_ctas_per_sm = n < 0 ? 0 : (n > 8 ? 8 : n); }
-void kp_gemm_stream_set_ring_kb(int kb) { g_ring_bytes = kb <= 0 ? 0 : (kb < 18 ? 18 : (kb > 96 ? 96 : kb)) * 1024; }
-
 int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                    int K, int epi, void* stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -391,20 +343,7 @@ int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* 
     if ((lda & 7) || ((uintptr_t)A & 15)) return KP_ERR_UNSUPPORTED;
     a.A = (const bf16*)A; a.lda = lda; a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc;
     a.M = M; a.N = N; a.K = K;
-    return launch_m<false>(a, epi, (cudaStream_t)stream);
+    return launch_m(a, epi, (cudaStream_t)stream);
 }
-
-int kp_gemm_stream_norm(const float* X, int ldx, const float* norm_w, float eps, const int* rows, const void* W,
-                        int ldw, const float* bias, void* C, int ldc, int M, int N, int K, int epi, void* stream) {
-    if (M <= 0 || N <= 0) return 0;
-    StreamArgs a = {};
-    int st = check_common(a, M, N, K, ldw, W, epi);
-    if (st) return st;
-    if (M > 16 || (ldx & 3) || ((uintptr_t)X & 15) || ((uintptr_t)norm_w & 15)) return KP_ERR_UNSUPPORTED;
-    a.X = X; a.ldx = ldx; a.norm_w = norm_w; a.eps = eps; a.rows = rows;
-    a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc; a.M = M; a.N = N; a.K = K;
-    return launch_m<true>(a, epi, (cudaStream_t)stream);
-}
-
 
 }  // extern "C"

@@ -238,13 +238,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 // ------------------------------------------------------------------------------------------ host side
-static int g_tc_smem_kb = 208;              // shared memory for the ring (tunable for measurements)
+#define TC_SMEM_KB 208                       // shared memory for the ring
+
+// SMs of the current device (asked once)
+static int tc_n_sm() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
 
 template <int BN, int EPI>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaStream_t s) {
     const int stage = a.a_rows * TC_BK * 2 + BN * TC_BK * 2;
     const int slack = (TC_BM - a.a_rows) * TC_BK * 2;          // the MMA's reads past a short last stage
-    int stages = (g_tc_smem_kb * 1024 - slack) / stage;
+    int stages = (TC_SMEM_KB * 1024 - slack) / stage;
     if (stages > 24) stages = 24;
     if (stages < 2) stages = 2;
     a.n_stages = stages;
@@ -259,12 +270,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaSt
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
     const int n_tiles = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
+    const int sms = tc_n_sm();
     dim3 grid(n_tiles < sms ? n_tiles : sms);                  // persistent: one CTA an SM
     kp_launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, s, ta, tw, a);
     return kp_launch_status();
@@ -294,10 +300,11 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     // of a wide one and does half the work; the number of rounds over the SMs decides between them.
     // At most 128 rows (one row of tiles, W streamed once): see below.
     const long long m_tiles = (M + TC_BM - 1) / TC_BM;
+    const int sms = tc_n_sm();
     int bn;
     if (m_tiles > 1) {
-        const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + 147) / 148;
-        const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + 147) / 148;
+        const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + sms - 1) / sms;
+        const long long rounds_narrow = (((n_out + 127) / 128) * m_tiles + sms - 1) / sms;
         bn = (epi == EPI_SWIGLU || rounds_wide * 3 <= rounds_narrow * 2) ? 256 : 128;
     } else {
         // the narrowest tile that still runs in one round over the SMs (as many CTAs as possible pull on the
@@ -305,7 +312,7 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
         const int lowest = epi == EPI_SWIGLU ? 64 : 32;
         auto tiles_at = [&](int w) { const int cols = epi == EPI_SWIGLU ? w / 2 : w; return (n_out + cols - 1) / cols; };
         bn = 256;
-        while (bn > lowest && tiles_at(bn / 2) <= 148) bn /= 2;
+        while (bn > lowest && tiles_at(bn / 2) <= sms) bn /= 2;
     }
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;
@@ -335,8 +342,5 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     }
 #undef TC_PICK
 }
-
-void kp_gemm_tc_set_smem_kb(int kb) { g_tc_smem_kb = kb < 64 ? 64 : (kb > 216 ? 216 : kb); }
-
 
 }  // extern "C"

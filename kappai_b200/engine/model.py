@@ -95,8 +95,7 @@ class Model:
         if ctx.n_out == 0:
             return None
         if self.final_norm is not None:
-            h = (self.final_norm.lazy(x, rows=ctx.logit_rows) if hasattr(self.final_norm, "lazy")
-                 else self.final_norm.forward(x, rows=ctx.logit_rows))
+            h = self.final_norm.forward(x, rows=ctx.logit_rows)
         else:
             h = x.index_select(0, ctx.logit_rows.long()).to(self.env.dtype)
         return self.head.forward(h)

@@ -371,19 +371,14 @@ SPLIT_MAX_RATIO = 8        # query heads per kv head it takes
 
 def attention_split_scratch(n_rows: int, H: int, hd: int, n_chunks: int) -> int:
     """Float elements of scratch that :func:`attention_split` needs."""
-    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2) + n_rows * H
+    return n_rows * H * n_chunks * (SPLIT_CHUNK // min(SPLIT_CHUNK, SPLIT_CHUNK_MMA)) * (hd + 2)
 
 
 def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, row_seg: torch.Tensor,
                     positions: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, n_chunks: int, scale: float,
-                    window: Optional[int], page_size: int, H: int, G: int, hd: int,
-                    fused_merge: bool = False) -> torch.Tensor:
+                    window: Optional[int], page_size: int, H: int, G: int, hd: int) -> torch.Tensor:
     """Split-KV attention (chunks of 256 keys, merged in order).  ``n_chunks``
-    must cover the largest position of the batch; ``scratch`` is float32.
-    ``fused_merge``: the tensor-core chunk kernel merges too (one launch
-    less); the caller vouches that ``scratch`` was zero when it was made and
-    has been used by nothing but calls of this function with it since (its
-    tail holds counters that every call leaves zero)."""
+    must cover the largest position of the batch; ``scratch`` is float32."""
     _need(q, "q", contiguous=False); _need(cache, "cache", q.dtype); _need(out, "out", q.dtype, contiguous=False)
     _need(block_table, "block_table", torch.int32); _need(row_seg, "row_seg", torch.int32)
     _need(positions, "positions", torch.int32); _need(scratch, "scratch", torch.float32)
@@ -400,10 +395,7 @@ def attention_split(q: torch.Tensor, cache: torch.Tensor, block_table: torch.Ten
             _ptr(q), _rows_2d(q, "q"), _ptr(cache), ctypes.c_longlong(cache.shape[0] if USE_TMA_ATTENTION else 0),
             _ptr(block_table), block_table.shape[1], _ptr(row_seg),
             _ptr(positions), _ptr(scratch), parts, SPLIT_CHUNK_MMA, ctypes.c_float(scale), int(window or 0), page_size,
-            n, H, G, hd, _ptr(out) if fused_merge else ctypes.c_void_p(0), _rows_2d(out, "out"),
-            ctypes.c_longlong(scratch.numel()), STREAM)
-        if fused_merge:
-            return out
+            n, H, G, hd, STREAM)
         _run("attention_merge", lib.kp_attention_merge, _ptr(positions), _ptr(out), _rows_2d(out, "out"), _ptr(scratch), parts,
                                       SPLIT_CHUNK_MMA, int(window or 0), n, H, hd, dtype_code(q.dtype), STREAM)
         return out
@@ -544,47 +536,6 @@ def stream_pays(N: int, K: int) -> bool:
     fills the ring before it waits for the kernel before it, overlaps that kernel's tail inside a model step.
     It loses on the huge grid of a 65536-row head (65 against 48 us)."""
     return N <= 16384
-
-
-SKINNY_NORM_MAX_M = 16
-
-
-def skinny_norm_ok(x: torch.Tensor, n_rows: int, w: torch.Tensor) -> bool:
-    """Can the weight-streaming kernel take RMSNorm(x) as its A operand?"""
-    return (x.dtype == torch.float32 and w.dtype == torch.bfloat16 and n_rows <= SKINNY_NORM_MAX_M
-            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 4 == 0
-            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
-def gemm_skinny_norm(x: torch.Tensor, norm_w: torch.Tensor, eps: float, rows: Optional[torch.Tensor],
-                     w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-                     accumulate: bool = False, swiglu: bool = False) -> torch.Tensor:
-    """out = rmsnorm(x[rows] if rows is given else x) @ w.T (+ bias), the norm
-    computed inside the product kernel (at most 16 rows)."""
-    _need(x, "x", torch.float32, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
-    _need(norm_w, "norm_w", torch.float32); _need(out, "out", contiguous=False)
-    K = x.shape[1]
-    M = x.shape[0] if rows is None else rows.numel()
-    if rows is not None:
-        _need(rows, "rows", torch.int32)
-    N = w.shape[0]
-    n_out = N // 2 if swiglu else N
-    if w.shape[1] != K or out.shape != (M, n_out) or norm_w.numel() != K:
-        raise KernelError(f"gemm_skinny_norm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
-    if bias is not None:
-        _need(bias, "bias", torch.float32)
-    epi = _skinny_epilogue(out, accumulate, swiglu)
-    if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K):
-        lib = load_library("gemm_stream")
-        _run("gemm_stream_norm", lib.kp_gemm_stream_norm, _ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows),
-                                       _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K,
-                                       epi, STREAM)
-        return out
-    lib = load_library("gemm_skinny")
-    _run("gemm_skinny_norm", lib.kp_gemm_skinny_norm, _ptr(x), _rows_2d(x, "x"), _ptr(norm_w), ctypes.c_float(eps), _ptr(rows), _ptr(w),
-                                   _rows_2d(w, "w"), _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, epi,
-                                   STREAM)
-    return out
 
 
 def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:

@@ -76,7 +76,6 @@ def attention_tiles(segs, split_ok: bool = True):
 class Attention(Part):
     category = "mixer"
     graph_safe = True
-    accepts_normed_rows = True      # the input goes straight into ops.linear
 
     def __init__(self, params, env):
         super().__init__(params, env)

@@ -17,21 +17,10 @@ class PreNormResidualBlock(Part):
         self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
         return self
 
-    @staticmethod
-    def _normed(norm, part, x):
-        """A part that says it feeds its input straight into ``linear`` gets the
-        norm as a lazy operand (it may then run inside the product kernel);
-        any other part gets the normalised tensor."""
-        if norm is None:
-            return x
-        if getattr(part, "accepts_normed_rows", False) and hasattr(norm, "lazy"):
-            return norm.lazy(x)
-        return norm.forward(x)
-
     def forward(self, x, ctx, cache):
-        self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x), x, ctx, cache)
+        self.mixer.forward(self.mixer_norm.forward(x) if self.mixer_norm is not None else x, x, ctx, cache)
         if self.ffn is not None:
-            self.ffn.forward(self._normed(self.ffn_norm, self.ffn, x), x, ctx)
+            self.ffn.forward(self.ffn_norm.forward(x) if self.ffn_norm is not None else x, x, ctx)
 
 
 register_part("block", "prenorm_residual", PreNormResidualBlock)

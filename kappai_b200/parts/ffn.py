@@ -21,7 +21,6 @@ from .base import Part, WeightSpec, register_part
 class SwiGLU(Part):
     category = "feed_forward"
     graph_safe = True
-    accepts_normed_rows = True      # the input goes straight into ops.linear
 
     def __init__(self, params, env):
         super().__init__(params, env)

@@ -11,7 +11,6 @@ from typing import Dict, Optional
 import torch
 
 from ..ops import kernels as K
-from ..ops.linear import NormedRows
 from .base import Part, WeightSpec, register_part
 
 
@@ -30,11 +29,6 @@ class RMSNorm(Part):
 
     def bind(self, w):
         self.weight = w["weight"].to(torch.float32).contiguous()
-
-    def lazy(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> NormedRows:
-        """The norm as an operand that a product kernel may compute in front of
-        itself; ``.tensor()`` materialises it."""
-        return NormedRows(x, self.weight, self.eps, self.env.dtype, rows)
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x.shape[0] if rows is None else rows.numel()

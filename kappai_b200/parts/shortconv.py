@@ -30,7 +30,6 @@ MAX_KERNEL = 16
 class ShortConv(Part):
     category = "mixer"
     graph_safe = True
-    accepts_normed_rows = True      # the input goes straight into ops.linear
 
     def __init__(self, params, env):
         super().__init__(params, env)

@@ -113,29 +113,3 @@ def test_split_refuses_large_group_ratio():
     with pytest.raises(Kn.KernelError, match="not supported"):
         Kn.attention_split(q, torch.zeros((1, 2, 1, 16, 16), device="cuda"), i32([[0]]), i32([0]), i32([0]),
                            torch.empty_like(q), torch.zeros(100000, device="cuda"), 1, 1.0, None, 16, 16, 1, 16)
-
-
-def test_split_with_the_merge_fused_in():
-    """The tensor-core chunk kernel can merge too (the last CTA of a row and kv head does).  Same numbers as
-    with the merge kernel, for batches of changing size on one scratch array."""
-    from kappai_b200.ops import kernels as Kn
-    rng = np.random.default_rng(44)
-    H, G, hd, page, dtype = 8, 2, 64, 64, torch.bfloat16
-    seq_lens = [1, 255, 256, 257, 700, 513, 90, 1000]
-    cache, bt, ks, vs = paged_setup(rng, seq_lens, page, G, hd, dtype)
-    qs = [rt(rng.standard_normal((L, H, hd)), dtype) for L in seq_lens]
-    n_chunks = 4
-    ws = torch.zeros(Kn.attention_split_scratch(len(seq_lens), H, hd, n_chunks) + 1000, device="cuda")
-    for use in ([0, 1, 2, 3, 4, 5, 6, 7], [4, 7], [7, 6, 5, 4, 3], [0], [1, 2, 3, 4, 5, 6, 7, 0]):
-        pos = [seq_lens[i] - 1 for i in use]
-        q_rows = np.stack([qs[i][-1] for i in use]).reshape(len(use), H * hd)
-        args = (dev(q_rows, dtype), dev(cache, dtype), i32(bt), i32(use), i32(pos))
-        fused = Kn.attention_split(*args, torch.empty((len(use), H * hd), dtype=dtype, device="cuda"), ws, n_chunks, 0.125,
-                                   None, page, H, G, hd, fused_merge=True)
-        ws2 = torch.full((Kn.attention_split_scratch(len(use), H, hd, n_chunks),), float("nan"), device="cuda")
-        plain = Kn.attention_split(*args, torch.empty((len(use), H * hd), dtype=dtype, device="cuda"), ws2, n_chunks,
-                                   0.125, None, page, H, G, hd)
-        assert torch.equal(fused, plain), use
-        for j, i in enumerate(use):
-            ref = P.attention(qs[i], ks[i], vs[i], 0.125, None)[-1]
-            assert np.abs(fused[j].cpu().double().numpy().reshape(H, hd) - ref).max() <= tol(dtype)
