@@ -5,7 +5,7 @@ The reference's entry point is ``engine_init(ctx, args, argc, argv)`` ->
 with a table-driven flag parser (src/config.c:403-447).  The same three calls
 exist here; flags keep the reference's names and meanings where it has them
 (-m, -c, -p, -n, -t, -k, -P, -M, --repeat-penalty, --repeat-last-n, -s,
---metrics, --stream, --time, --debug).  There is no tokenizer in the engine:
+--metrics, --stream, --time, --debug-forward, --debug).  There is no tokenizer in the engine:
 a prompt is a list of token ids ("5,17,3" or "5 17 3") and so is the output.
 
     python -m kappai_b200.cli -m MODEL_DIR -p "5,17,3" -n 16 -t 0
@@ -79,8 +79,10 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--repeat-last-n", type=int, default=64, help="last-n tokens considered by repeat penalty (default 64)")
     b.add_argument("-s", "--seed", type=int, default=0, help="RNG seed (0 = random)")
     d = ap.add_argument_group("Tools / debug")
-    d.add_argument("--time", action="store_true", help="print per-step timing")
-    d.add_argument("--debug", action="store_true", help="enable debug-level logging")
+    d.add_argument("--time", action="store_true", help="print device time by kernel class after generation")
+    d.add_argument("--debug-forward", action="store_true",
+                   help="print per-layer activation stats for the first step and the top logits at every sample")
+    d.add_argument("--debug", action="store_true", help="enable debug-level logging (one line a step)")
     ap.add_argument("positional_prompt", nargs="?", type=parse_tokens, help="prompt (token ids) if -p is not given")
     return ap
 
@@ -95,9 +97,14 @@ def engine_init(argv: Optional[Sequence[str]] = None) -> Tuple[Engine, argparse.
 
         with open(a.random_weights, "r", encoding="utf-8") as f:
             write_random_model(json.load(f), a.model, a.seed)
+    if a.debug:
+        import logging
+
+        logging.basicConfig(stream=sys.stderr, format="[debug] %(message)s")
+        logging.getLogger("kappai_b200").setLevel(logging.DEBUG)
     eng = Engine(EngineArgs(model=a.model, dtype=a.dtype, ctx_size=a.ctx_size, max_batch=a.max_batch,
                             max_step_tokens=a.max_step_tokens, page_size=a.page_size, kv_tokens=a.kv_tokens,
-                            device=a.device))
+                            device=a.device, time_kernels=a.time, debug_forward=a.debug_forward))
     return eng, a
 
 
@@ -146,8 +153,9 @@ def engine_run(eng: Engine, a: argparse.Namespace) -> int:
     if parts:
         print("[ " + " | ".join(parts) + " ]", file=sys.stderr)       # src/context.c:1519-1568
     if a.time:
-        print(f"[ steps: {st.n_steps} | total: {total * 1e3:.1f} ms | preemptions: "
-              f"{eng.scheduler.n_preemptions} ]", file=sys.stderr)
+        # device time by kernel class, in the manner of the reference's profile report (src/profile.c:65-110)
+        print(eng.timer.format(f"{st.n_steps} steps, wall {total * 1e3:.1f} ms, preemptions "
+                               f"{eng.scheduler.n_preemptions}"), file=sys.stderr)
     full = any(eng.finish_reason(i) == "context_full" for i in eng.requests)
     return ENGINE_EXIT_CONTEXT_FULL if full else 0
 

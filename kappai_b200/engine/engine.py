@@ -9,6 +9,8 @@ as ids: text is not part of the engine.
 from __future__ import annotations
 
 import itertools
+import logging
+import sys
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Dict, Hashable, List, Optional, Sequence
@@ -21,6 +23,9 @@ from ..sampling.sampler import sample
 from ..ops import kernels as K
 from .runner import EngineError, ModelRunner, StepEntry
 from .scheduler import RUNNING, Request, ScheduledEntry, Scheduler
+
+
+log = logging.getLogger("kappai_b200")       # --debug turns its DEBUG level on: one line a step
 
 
 @dataclass
@@ -38,6 +43,8 @@ class EngineArgs:
     kv_tokens: int = 0                 # tokens the page pools hold (0: max_batch * ctx_size, or what fits beside the weights)
     device: str = "cuda:0"
     look_ahead: bool = True            # launch the next decode step before the last one's tokens are read
+    time_kernels: bool = False         # --time: device time by kernel class (steps run eagerly meanwhile)
+    debug_forward: bool = False        # --debug-forward: per-layer statistics of the first step, top logits at every sample
 
 
 @dataclass
@@ -99,6 +106,13 @@ class Engine:
         self._staging_turn = 0
         self.n_launched_ahead = 0
         self.status = K.StatusGather(self.runner.device)
+        self.timer: Optional[K.KernelTimer] = None
+        if args.time_kernels:
+            self.timer = K.KernelTimer()
+            K.TIMER[0] = self.timer
+        self._debug_steps = 0
+        if args.debug_forward:
+            self.runner.observer = self._observe_layer
 
     @property
     def vocab_size(self) -> int:
@@ -128,6 +142,25 @@ class Engine:
         by a step that is already under way is dropped."""
         self.scheduler.abort(request_id)
 
+    # -- debugging aids
+    def _observe_layer(self, where: int, x: torch.Tensor) -> None:
+        """--debug-forward: statistics of the residual behind every layer, for the first step only
+        (the reference prints per-layer activation statistics for the first token, src/config.c:150)."""
+        if self._debug_steps > 0:
+            return
+        spec = self.runner.spec
+        name = "embedding" if where < 0 else f"layer {where:3d} ({spec.layers[spec.schedule[where].layer].mixer.kind})"
+        v = x.float()
+        print(f"[debug-forward] {name:<28} rows {v.shape[0]:5d}  min {v.min().item():+.6e}  max {v.max().item():+.6e}  "
+              f"mean {v.mean().item():+.6e}  rms {v.pow(2).mean().sqrt().item():.6e}", file=sys.stderr)
+
+    def _debug_logits(self, logits: torch.Tensor, got: List[Request]) -> None:
+        """--debug-forward: the eight largest logits of every row that is sampled (src/context.c:1175-1211)."""
+        top = torch.topk(logits.float(), min(8, logits.shape[1]), dim=1)
+        for r, vals, idx in zip(got, top.values.tolist(), top.indices.tolist()):
+            print(f"[debug-forward] request {r.id!r} top logits: " + " ".join(f"[{i}]={v:.4f}" for i, v in zip(idx, vals)),
+                  file=sys.stderr)
+
     # -- one turn of the loop
     def _launch(self, plan: List[ScheduledEntry], device_tokens: Optional[torch.Tensor] = None,
                 ahead: int = 0) -> _Launched:
@@ -140,6 +173,10 @@ class Engine:
             entries.append(StepEntry(e.request.id, toks, [e.n - 1] if e.sample else []))
         logits = self.runner.step(entries, device_tokens=device_tokens)
         got = [e.request for e in plan if e.sample]
+        if self.args.debug_forward:
+            self._debug_steps += 1
+            if got:
+                self._debug_logits(logits, got)
         n = len(got)
         # the new tokens and, behind them, one word that says whether a kernel of the step gave up a wait
         buf = torch.empty(n + 1, dtype=torch.int32, device=self.runner.device)
@@ -201,6 +238,13 @@ class Engine:
         self._launched = ahead
         got = [e.request for e in plan if e.sample]
         dt = time.perf_counter() - t0
+        if log.isEnabledFor(logging.DEBUG):
+            log.debug("step %d: %s | %.3f ms | running %d waiting %d | pages free %s | preemptions %d%s",
+                      self.stats.n_steps, " ".join(f"{e.request.id!r}:{e.start}+{e.n}" for e in plan), dt * 1e3,
+                      len(self.scheduler.running), len(self.scheduler.waiting),
+                      "/".join(str(p.n_free) for p in self.runner.cache.pools.values()) or "-",
+                      self.scheduler.n_preemptions,
+                      "".join(f" | {r.id!r} finished: {r.finish_reason}" for r in got if r.finish_reason))
         st = self.stats
         st.n_steps += 1
         if n_prompt >= n_decode:
@@ -244,6 +288,8 @@ class Engine:
         return self.requests[request_id].finish_reason
 
     def shutdown(self) -> None:
+        if self.timer is not None and K.TIMER[0] is self.timer:
+            K.TIMER[0] = None
         if self._launched is not None:
             self._launched.done.synchronize()
             self._launched = None

@@ -86,12 +86,18 @@ class Model:
         return [e.cache_of for e in self.schedule]
 
     # -- the forward pass of one step
-    def forward(self, ctx, cache_views) -> Optional[torch.Tensor]:
+    def forward(self, ctx, cache_views, observer=None) -> Optional[torch.Tensor]:
         """Run the rows of ``ctx`` through every schedule entry; return float32
-        logits [n_out, vocab] of the wanted rows (None if none are wanted)."""
+        logits [n_out, vocab] of the wanted rows (None if none are wanted).
+        ``observer(where, x)``, if given, is shown the float32 residual behind
+        the embedding (where = -1) and behind every schedule entry (its index)."""
         x = self.embedding.forward(ctx.token_ids)
+        if observer is not None:
+            observer(-1, x)
         for i, e in enumerate(self.schedule):
             self.blocks[e.layer].forward(x, ctx, cache_views[i])
+            if observer is not None:
+                observer(i, x)
         if ctx.n_out == 0:
             return None
         if self.final_norm is not None:

@@ -116,6 +116,7 @@ class ModelRunner:
         self.group_page_size = {gk: page_size for gk in group_keys}
         self.vocab_size = self.spec.vocab_size
         self.last_h2d_bytes = 0
+        self.observer = None               # called with the residual behind every layer of a step (debugging): see Model.forward
         self.graphs: Optional[DecodeGraphs] = DecodeGraphs(self) if cuda_graphs else None
 
     # -- requests
@@ -195,7 +196,7 @@ class ModelRunner:
         return ctx, [(req, new_len) for req, _, new_len in plan]
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
-        return self.model.forward(ctx, self.storage.views)
+        return self.model.forward(ctx, self.storage.views, self.observer)
 
     def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None
              ) -> Optional[torch.Tensor]:
@@ -205,7 +206,8 @@ class ModelRunner:
         of the entries are placeholders and those are run instead, so sampled
         tokens need not visit the host between steps.  The returned tensor may
         be reused by the next step: read it before."""
-        if self.graphs is not None and self.model.graph_safe and DecodeGraphs.eligible(entries):
+        if (self.graphs is not None and self.model.graph_safe and self.observer is None and K.TIMER[0] is None
+                and DecodeGraphs.eligible(entries)):
             for e in entries:
                 if not (0 <= int(e.tokens[0]) < self.vocab_size):
                     raise EngineError(f"request {e.req!r}: token id {e.tokens[0]} outside the vocabulary")

@@ -67,9 +67,80 @@ class _Stream:
 STREAM = _Stream()
 
 
-def _run(what: str, fn, *args) -> None:
-    """The one door to the kernel libraries: call the launcher ``fn`` on the current stream and check its answer."""
+class KernelTimer:
+    """Device time by kernel class: while one is installed (``TIMER[0]``), every launcher call is put between
+    two CUDA events on its stream; ``report`` adds them up by class.  The reference keeps per-stage counters of
+    the same kind (src/profile.h:9-47,77-88) and prints them with ``--time`` (src/profile.c:65-110).  A class is
+    the launcher's name, for matrix products with the weight's shape.  Only launches made one by one are seen:
+    the engine runs its steps eagerly (no captured graphs) while it is timed, so the times of small kernels
+    include the gap the host leaves before them."""
+
+    FOLD_AT = 8192
+
+    def __init__(self):
+        self._open = []                    # (class, event before, event after, flops, bytes)
+        self.totals = {}                   # class -> [calls, ms, flops, bytes]
+
+    def add(self, key, e0, e1, work) -> None:
+        self._open.append((key, e0, e1, work))
+        if len(self._open) >= self.FOLD_AT:
+            self.fold()
+
+    def fold(self) -> None:
+        if not self._open:
+            return
+        self._open[-1][2].synchronize()
+        for key, e0, e1, work in self._open:
+            t = self.totals.setdefault(key, [0, 0.0, 0, 0])
+            t[0] += 1
+            t[1] += e0.elapsed_time(e1)
+            if work:
+                t[2] += work[0]
+                t[3] += work[1]
+        self._open = []
+
+    def report(self):
+        """Rows (class, calls, ms, microseconds a call, share in per cent, TFLOP/s or None, GB/s or None),
+        the class that took longest first."""
+        self.fold()
+        total = sum(t[1] for t in self.totals.values()) or 1.0
+        rows = []
+        for key, (calls, ms, flops, nbytes) in sorted(self.totals.items(), key=lambda kv: -kv[1][1]):
+            rows.append((key, calls, ms, ms * 1e3 / calls, 100.0 * ms / total,
+                         flops / (ms * 1e-3) / 1e12 if flops and ms > 0 else None,
+                         nbytes / (ms * 1e-3) / 1e9 if nbytes and ms > 0 else None))
+        return rows
+
+    def format(self, label: str = "kernels") -> str:
+        rows = self.report()
+        total = sum(r[2] for r in rows)
+        out = [f"[profile] {label}  accounted={total * 1e3:.0f} us",
+               f"  {'class':<34} {'ms':>10} {'calls':>8} {'us/call':>9} {'share':>7} {'TFLOP/s':>8} {'GB/s':>8}"]
+        for key, calls, ms, per, share, tf, gb in rows:
+            out.append(f"  {key:<34} {ms:>10.3f} {calls:>8d} {per:>9.2f} {share:>6.2f}% "
+                       f"{'' if tf is None else format(tf, '8.1f'):>8} {'' if gb is None else format(gb, '8.1f'):>8}")
+        return "\n".join(out)
+
+
+TIMER = [None]         # the KernelTimer that watches the launches, if any
+
+
+def _run(what: str, fn, *args, tag: str = "", work=None) -> None:
+    """The one door to the kernel libraries: call the launcher ``fn`` on the current stream and check its
+    answer.  ``tag`` and ``work`` = (flops, bytes) describe the call to a :class:`KernelTimer`."""
+    timer = TIMER[0]
+    if timer is None:
+        _check(fn(*[_stream() if a is STREAM else a for a in args]), what)
+        return
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     _check(fn(*[_stream() if a is STREAM else a for a in args]), what)
+    e1.record()
+    timer.add(what + tag, e0, e1, work)
+
+
+def _gemm_work(M: int, N: int, K: int, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    return (2 * M * N * K, M * K * a.element_size() + N * K * w.element_size() + out.numel() * out.element_size())
 
 
 def _check(status: int, what: str) -> None:
@@ -246,7 +317,7 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
         raise KernelError("gemm: output dtype must be the operand dtype or float32")
     lib = load_library("gemm_simt")
     _run("gemm_nt_simt", lib.kp_gemm_nt_simt, _ptr(a), _ptr(w), _ptr(bias), _ptr(out), M, N, K, lda, ldw, ldc, epi,
-                               dtype_code(a.dtype), STREAM)
+         dtype_code(a.dtype), STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
     return out
 
 
@@ -516,7 +587,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
     epi = _skinny_epilogue(out, accumulate, swiglu)
     lib = load_library("gemm_tc")
     _run("gemm_tc", lib.kp_gemm_tc, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                          _rows_2d(out, "out"), M, N, K, epi, STREAM)
+         _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
     return out
 
 
@@ -586,9 +657,9 @@ def gemm_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optio
     if USE_STREAM and stream_fits(K, swiglu) and stream_pays(N, K) and M <= STREAM_MAX_M:
         lib = load_library("gemm_stream")
         _run("gemm_stream", lib.kp_gemm_stream, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                                  _rows_2d(out, "out"), M, N, K, epi, STREAM)
+             _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
         return out
     lib = load_library("gemm_skinny")
     _run("gemm_skinny", lib.kp_gemm_skinny, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-                              _rows_2d(out, "out"), M, N, K, epi, STREAM)
+         _rows_2d(out, "out"), M, N, K, epi, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w, out))
     return out

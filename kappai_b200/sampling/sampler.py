@@ -21,7 +21,7 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
         out = torch.empty(n, dtype=torch.int32, device=logits.device)
     lib = load_library("sampling")
     scratch = torch.empty(n * 64, dtype=torch.int32, device=logits.device) if V >= 8192 else None
-    K._check(lib.kp_argmax_rows(K._ptr(logits), n, V, K._ptr(out), K._ptr(scratch), K._stream()), "argmax_rows")
+    K._run("argmax_rows", lib.kp_argmax_rows, K._ptr(logits), n, V, K._ptr(out), K._ptr(scratch), K.STREAM)
     return out
 
 
@@ -46,7 +46,6 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
         return argmax(logits, out)
     lib = load_library("sampling")
     dev = logits.device
-    stream = K._stream()
     # one pinned staging buffer: [n,5] floats, [n] top_k, then the recent tokens
     width = 0
     if penalised:
@@ -69,12 +68,11 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequen
     fl = d[:n * 5].view(torch.float32)
     col = lambda j: K._ptr(fl[j * n:(j + 1) * n])
     if penalised:
-        K._check(lib.kp_repeat_penalty(K._ptr(logits), n, V, K._ptr(d[n * 6:]), width, col(3), stream),
-                 "repeat_penalty")
+        K._run("repeat_penalty", lib.kp_repeat_penalty, K._ptr(logits), n, V, K._ptr(d[n * 6:]), width, col(3), K.STREAM)
     if out is None:
         out = torch.empty(n, dtype=torch.int32, device=dev)
     K._need(out, "out", torch.int32)
-    K._check(lib.kp_sample_rows(K._ptr(logits), n, V, col(0), K._ptr(d[n * 5:n * 6]), col(1), col(2), col(4),
-                                K._ptr(out), stream), "sample_rows")
+    K._run("sample_rows", lib.kp_sample_rows, K._ptr(logits), n, V, col(0), K._ptr(d[n * 5:n * 6]), col(1), col(2), col(4),
+           K._ptr(out), K.STREAM)
     out._staging = host           # keep the pinned buffer alive until the copy has run
     return out

@@ -11,10 +11,20 @@ with state, attention over its fp16 cache (online-softmax and plain), SwiGLU,
 argmax and the sampler.  Inputs and outputs are saved; the test
 tests/test_plain_vs_golden.py compares the plain implementation with them.
 
+Whole models too: the reference's loader, recipe builder, executor and CPU backend are compiled in place
+(model.c includes a json-c header that this path never uses: a two-line stand-in is put on the include path;
+the dozen symbols of the monitor, the safetensors reader and other parts that are not built are stubbed),
+tiny LFM2 models with the package's random weights are written as GGUF files, and ref_model.c runs them
+through ``compute_forward_batch`` whole, token by token and in portions.  The logits are saved; the test
+compares the plain implementation's with them, which pins the order of a layer's operations, the mapping of
+query heads to kv heads and the tensor names, not only the single kernels.
+
     python tests/golden/make_golden.py REF          (REF: a checkout of the reference; or $KAPPAI_REFERENCE)
 """
 import ctypes
+import glob
 import os
+import struct
 import subprocess
 import sys
 import tempfile
@@ -41,6 +51,151 @@ def build(ref):
     lib = os.path.join(tmp, "libgolden.so")
     subprocess.run(base + ["-o", lib] + srcs + [stubs, "-lm"], check=True)
     return ctypes.CDLL(lib)
+
+
+# ------------------------------------------------------------------ whole models through the reference
+MODEL_SOURCES = ["arch.c", "common.c", "compute.c", "config.c", "gguf.c", "kvcache.c", "log.c", "memory.c", "model.c",
+                 "profile.c", "sampler.c", "threadpool.c", "weights.c", "cpu_topology.c", "hcs.c", "recipe/*.c",
+                 "models/lfm.c", "models/llama.c", "backend/backend.c", "backend/cpu/common.c", "backend/cpu/nn_ops.c",
+                 "backend/cpu/scalar/core.c", "backend/cpu/scalar/quants.c", "moe/*.c"]
+DATA_SYMBOLS = {"g_monitor"}             # among the stubbed names, those that are variables
+
+
+def build_model_lib(ref):
+    tmp = tempfile.mkdtemp(prefix="golden_model_")
+    shim = os.path.join(tmp, "shim", "json-c")
+    os.makedirs(shim)
+    for h in ("json.h", "json_types.h"):
+        with open(os.path.join(shim, h), "w") as f:
+            f.write("#pragma once\ntypedef struct json_object json_object;\ntypedef struct json_tokener json_tokener;\n")
+    src = os.path.join(ref, "src")
+    files = [os.path.join(HERE, "ref_model.c")]
+    for pat in MODEL_SOURCES:
+        files += sorted(glob.glob(os.path.join(src, pat)))
+    base = ["gcc", "-std=gnu11", "-O1", "-fPIC", "-w", "-I", os.path.join(tmp, "shim"), "-I", src]
+    objs = []
+    for i, f in enumerate(files):
+        o = os.path.join(tmp, f"o{i}.o")
+        subprocess.run(base + ["-c", f, "-o", o], check=True)
+        objs.append(o)
+    first = os.path.join(tmp, "first.so")
+    subprocess.run(["gcc", "-shared", "-o", first] + objs + ["-lm", "-lpthread"], check=True)
+    und = subprocess.run(["nm", "-u", "--dynamic", first], capture_output=True, text=True, check=True).stdout
+    names = [l.split()[1] for l in und.splitlines() if len(l.split()) == 2 and l.split()[0] == "U" and "@" not in l]
+    stubs = os.path.join(tmp, "stubs.c")
+    with open(stubs, "w") as f:
+        f.write("/* symbols of parts of the reference that are not built here and that these runs never reach */\n")
+        for n in names:
+            f.write(f"void *{n} = 0;\n" if n in DATA_SYMBOLS else f"long {n}(void) {{ return 0; }}\n")
+    lib = os.path.join(tmp, "libgoldenmodel.so")
+    subprocess.run(["gcc", "-shared", "-fPIC", "-w", "-o", lib, stubs] + objs + ["-lm", "-lpthread"], check=True)
+    return ctypes.CDLL(lib), names
+
+
+def _gguf_string(s):
+    b = s.encode()
+    return struct.pack("<Q", len(b)) + b
+
+
+def write_gguf(path, cfg, w, ff):
+    """An LFM2 model as a GGUF file of float32 tensors, with the keys and names of the reference's own test
+    writer (src/test/test_synth_gguf.c:349-460).  ``w``: tensor name of the model folder -> array."""
+    d, H, G = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    kv = []
+    k_str = lambda k, v: kv.append(_gguf_string(k) + struct.pack("<I", 8) + _gguf_string(v))
+    k_i32 = lambda k, v: kv.append(_gguf_string(k) + struct.pack("<Ii", 5, v))
+    k_f32 = lambda k, v: kv.append(_gguf_string(k) + struct.pack("<If", 6, v))
+    k_str("general.architecture", "lfm2")
+    k_i32("lfm2.context_length", cfg["max_position_embeddings"])
+    k_i32("lfm2.block_count", cfg["num_hidden_layers"])
+    k_i32("lfm2.embedding_length", d)
+    k_i32("lfm2.feed_forward_length", ff)
+    k_i32("lfm2.attention.head_count", H)
+    heads_kv = [0 if t == "conv" else G for t in cfg["layer_types"]]
+    kv.append(_gguf_string("lfm2.attention.head_count_kv") + struct.pack("<IIQ", 9, 5, len(heads_kv))
+              + struct.pack(f"<{len(heads_kv)}i", *heads_kv))
+    k_i32("lfm2.attention.key_length", cfg.get("head_dim") or d // H)
+    k_f32("lfm2.attention.layer_norm_rms_epsilon", cfg["norm_eps"])
+    k_i32("lfm2.shortconv.l_cache", cfg["conv_L_cache"])
+    k_f32("lfm2.rope.freq_base", cfg["rope_theta"])
+    tensors = []
+    add = lambda name, a: tensors.append((name, np.ascontiguousarray(a, dtype=np.float32)))
+    add("token_embd.weight", w["model.embed_tokens.weight"])
+    add("output_norm.weight", w["model.embedding_norm.weight"])
+    if not cfg.get("tie_embedding", True):
+        add("output.weight", w["lm_head.weight"])
+    for i, t in enumerate(cfg["layer_types"]):
+        p = f"model.layers.{i}."
+        add(f"blk.{i}.attn_norm.weight", w[p + "operator_norm.weight"])
+        if t == "conv":
+            add(f"blk.{i}.shortconv.in_proj.weight", w[p + "conv.in_proj.weight"])
+            add(f"blk.{i}.shortconv.conv.weight", w[p + "conv.conv.weight"].reshape(d, -1))
+            add(f"blk.{i}.shortconv.out_proj.weight", w[p + "conv.out_proj.weight"])
+        else:
+            for a, b in (("attn_q", "q_proj"), ("attn_k", "k_proj"), ("attn_v", "v_proj"), ("attn_output", "out_proj")):
+                add(f"blk.{i}.{a}.weight", w[p + f"self_attn.{b}.weight"])
+            add(f"blk.{i}.attn_q_norm.weight", w[p + "self_attn.q_layernorm.weight"])
+            add(f"blk.{i}.attn_k_norm.weight", w[p + "self_attn.k_layernorm.weight"])
+        add(f"blk.{i}.ffn_norm.weight", w[p + "ffn_norm.weight"])
+        add(f"blk.{i}.ffn_gate.weight", w[p + "feed_forward.w1.weight"])
+        add(f"blk.{i}.ffn_up.weight", w[p + "feed_forward.w3.weight"])
+        add(f"blk.{i}.ffn_down.weight", w[p + "feed_forward.w2.weight"])
+    infos, off = [], 0
+    for name, a in tensors:
+        dims = list(reversed(a.shape))                               # GGUF dims are fastest first
+        infos.append(_gguf_string(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims)
+                     + struct.pack("<IQ", 0, off))
+        off += (a.nbytes + 31) // 32 * 32
+    head = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(kv)) + b"".join(kv) + b"".join(infos)
+    with open(path, "wb") as f:
+        f.write(head)
+        f.write(b"\0" * ((-len(head)) % 32))
+        for name, a in tensors:
+            f.write(a.tobytes())
+            f.write(b"\0" * ((-a.nbytes) % 32))
+
+
+# Models that the reference's LFM2 can run: no biases (it has none), and head_dim = hidden / heads as in every
+# real LFM2 file (with another head size the reference's conv layers write their rows with the stride of the
+# attention buffer, src/recipe/ops_hybrid.c:335-336, which the product that follows does not expect: its
+# results for several rows at once are then not those of its own formulas).  Everything else as the tiny
+# configurations.  tests/test_plain_vs_golden.py has the same table.
+MODEL_CASES = {"A": {}, "B": {"conv_bias": False}, "C": {"hidden_size": 240}}
+MODEL_CUTS = {"whole": lambda n: [0, n], "each": lambda n: list(range(n + 1)),
+              "portions": lambda n: [c for c in (0, 7, 9, 25, 28, 30, 47, 49) if c < n] + [n]}
+
+
+def model_cases(ref, out):
+    root = os.path.dirname(os.path.dirname(HERE))
+    for p in (root, os.path.join(root, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from kappai_b200.weights import write_random_model
+    from plain_lfm2 import intermediate_size, read_safetensors
+    from tiny_configs import CONFIGS
+
+    lib, stubbed = build_model_lib(ref)
+    out["model_stubbed"] = np.array(sorted(stubbed))
+    for name, override in MODEL_CASES.items():
+        cfg, seed = CONFIGS[name]
+        cfg = dict(cfg, **override)
+        d = tempfile.mkdtemp(prefix=f"golden_{name}_")
+        write_random_model(cfg, d, seed)
+        gg = os.path.join(d, "model.gguf")
+        write_gguf(gg, cfg, read_safetensors(os.path.join(d, "model.safetensors")), intermediate_size(cfg))
+        V = cfg["vocab_size"]
+        toks = np.random.default_rng(100 + seed).integers(0, V, 61).astype(np.int32)
+        out[f"model{name}_tokens"] = toks
+        for cut_name, make in MODEL_CUTS.items():
+            cuts = np.asarray(make(len(toks)), dtype=np.int32)
+            rows = np.zeros((len(cuts) - 1, V), np.float32)
+            rc = lib.gold_model_logits(gg.encode(), toks.ctypes.data_as(ctypes.c_void_p), cuts.ctypes.data_as(ctypes.c_void_p),
+                                       len(cuts) - 1, cfg["max_position_embeddings"], 1, rows.ctypes.data_as(ctypes.c_void_p), V)
+            if rc != 0:
+                sys.exit(f"the reference failed on model {name}, cut '{cut_name}': {rc}")
+            keep = np.arange(len(cuts) - 1) if len(cuts) <= 12 else np.array([0, 1, 2, 7, 15, 31, 32, len(cuts) - 2])
+            out[f"model{name}_{cut_name}_positions"] = cuts[1:][keep] - 1       # the position whose logits a row holds
+            out[f"model{name}_{cut_name}_logits"] = rows[keep]
 
 
 def fp(a):
@@ -129,6 +284,7 @@ def main():
     out["sample_logits"], out["sample_rows"] = logits.astype(np.float16).astype(np.float32), np.array(rows, dtype=np.float64)
 
     out["sample_logits"] = out["sample_logits"].astype(np.float16)
+    model_cases(ref, out)
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **out)
     print(f"wrote {os.path.join(HERE, 'golden.npz')} with {len(out)} arrays")
 

@@ -222,15 +222,21 @@ class PlainLfm2:
         g, u = self.st(linear(h, w[p + "w1.weight"])), self.st(linear(h, w[p + "w3.weight"]))
         return linear(self.st(swiglu(g, u)), w[p + "w2.weight"])
 
-    def hidden(self, tokens):
+    def hidden(self, tokens, trace=None):
+        """The residual behind the last layer; ``trace`` (a list) gets a copy of it behind the embedding and
+        behind every layer."""
         w = self.w
         x = embedding(w["model.embed_tokens.weight"], tokens)
+        if trace is not None:
+            trace.append(x.copy())
         for i, kind in enumerate(self.cfg["layer_types"]):
             p = f"model.layers.{i}."
             h = self.st(rmsnorm(x, w[p + "operator_norm.weight"], self.eps))
             x = x + (self.conv_mixer(h, i) if kind == "conv" else self.attention_mixer(h, i))
             h = self.st(rmsnorm(x, w[p + "ffn_norm.weight"], self.eps))
             x = x + self.feed_forward(h, i)
+            if trace is not None:
+                trace.append(x.copy())
         return x
 
     def logits(self, tokens):

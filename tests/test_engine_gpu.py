@@ -272,6 +272,38 @@ def test_command_line(model_dirs, tmp_path):
     assert os.path.isfile(out / "model.safetensors") and os.path.isfile(out / "config.json")
 
 
+def test_time_debug_forward_and_debug_flags(model_dirs, plain_models):
+    """--time prints device time by kernel class, --debug-forward the statistics of the residual behind every
+    layer of the first step (the plain model's, here) and the top logits at every sample, --debug a line a step."""
+    import re
+    prompt = [5, 17, 3, 200, 9, 41, 7]
+    cmd = [sys.executable, "-m", "kappai_b200.cli", "-m", model_dirs["A"], "-p", ",".join(map(str, prompt)), "-n", "4",
+           "-t", "0", "--fp32", "--time", "--debug-forward", "--debug"]
+    p = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    err = p.stderr
+    # per-layer statistics against the plain model
+    trace = []
+    plain_models["A"].hidden(prompt, trace)
+    lines = [l for l in err.splitlines() if l.startswith("[debug-forward]") and ("layer" in l or "embedding" in l)]
+    assert len(lines) == len(trace) == 5, err[-2000:]
+    for line, x in zip(lines, trace):
+        got = {k: float(v) for k, v in re.findall(r"(min|max|mean|rms) ([-+0-9.e]+)", line)}
+        for k, want in (("min", x.min()), ("max", x.max()), ("mean", x.mean()), ("rms", np.sqrt((x * x).mean()))):
+            assert abs(got[k] - want) <= 1e-5 + 1e-4 * abs(want), (line, k, want)
+    assert "(conv)" in lines[1] and "(attention)" in lines[2]
+    tops = [l for l in err.splitlines() if "top logits:" in l]
+    assert len(tops) == 4
+    first = int(re.search(r"top logits: \[(\d+)\]=", tops[0]).group(1))
+    assert first == int(p.stdout.split()[0]) == int(np.argmax(plain_models["A"].logits(prompt)[-1]))
+    # the kernel classes with their times
+    assert "[profile]" in err and re.search(r"gemm_nt_simt 192x64\s+[0-9.]+\s+\d+", err), err[-3000:]
+    assert "rmsnorm_rows" in err and "argmax_rows" in err and "TFLOP/s" in err
+    # one line a step
+    steps = [l for l in err.splitlines() if l.startswith("[debug] step")]
+    assert len(steps) == 4 and "0:0+7" in steps[0] and "finished: length" in steps[-1], steps
+
+
 def test_no_cuda_device_is_refused(model_dirs):
     from kappai_b200.engine.runner import EngineError, ModelRunner
     with pytest.raises(EngineError, match="CUDA"):
