@@ -320,7 +320,7 @@ def run_e2e(model_dir, batch, prompt_len, steps, warmup, rng, n_layers_note):
     return n / dt, h2d, d2h
 
 
-def run_workload(name: str, rng_seed: int) -> dict:
+def run_workload(name: str, rng_seed: int, time_kernels: bool = False) -> dict:
     """Whole generations through ``Engine`` (scheduler, chunked prefill beside decoding, sampling), timed by
     the wall clock around ``generate``-like stepping, as the reference times its runs (src/context.c:1507-1512,
     1607-1620; src/test/test_bench.c:432-464)."""
@@ -340,7 +340,7 @@ def run_workload(name: str, rng_seed: int) -> dict:
         label = "LFM2-350M shape, 256 requests at once, prompts U[16,512], 128 tokens each at temperature 0.8 (seed 4)"
     model_dir, c = model_folder(cfg, seed, cfg["num_hidden_layers"])
     eng = Engine(EngineArgs(model=model_dir, dtype="bfloat16", ctx_size=ctx, max_batch=max_batch, max_step_tokens=2048,
-                            page_size=64, kv_tokens=0))
+                            page_size=64, kv_tokens=0, time_kernels=time_kernels))
     rng = np.random.default_rng(rng_seed + 1)
     V = eng.vocab_size
     prompts = [rng.integers(0, V, n).tolist() for n in lens]
@@ -374,6 +374,10 @@ def run_workload(name: str, rng_seed: int) -> dict:
            "pp_tokens_per_s": round(st.prompt_tokens / st.prompt_seconds, 1) if st.prompt_seconds else None,
            "tg_tokens_per_s": round(st.decode_tokens / st.decode_seconds, 1) if st.decode_seconds else None,
            "clocks": clk}
+    if time_kernels:
+        # (timed runs launch every kernel on its own, between two events: their throughput is not the engine's)
+        print(eng.timer.format(f"workload {name}, every step launched kernel by kernel"), file=sys.stderr)
+        rec["timed_kernel_by_kernel"] = True
     eng.shutdown()
     return rec
 
@@ -417,6 +421,9 @@ def main() -> int:
     ap.add_argument("--workload", choices=["long", "many"], default=None,
                     help="run a whole scheduling workload through Engine instead of the default line: 'long' "
                          "(2.6B shape, 16 prompts of 1k to 30k tokens, context 32768) or 'many' (350M shape, 256 requests)")
+    ap.add_argument("--time", action="store_true",
+                    help="with --workload: launch every kernel on its own between CUDA events and print the device "
+                         "time by kernel class (the run's throughput is then not the engine's)")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of --probe")
     a = ap.parse_args()
 
@@ -431,7 +438,7 @@ def main() -> int:
         return 2
     warmup = max(a.warmup, 3)
     if a.workload:
-        print(json.dumps(run_workload(a.workload, 40)))
+        print(json.dumps(run_workload(a.workload, 40, a.time)))
         return 0
 
     import numpy as np

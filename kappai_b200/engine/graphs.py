@@ -152,12 +152,34 @@ class DecodeGraphs:
     def __init__(self, runner):
         self.runner = runner
         self.graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        self.seen: Dict[Tuple[int, int], int] = {}     # how often a shape has come without being captured
         self.n_captures = 0
         self.n_replays = 0
+
+    # A shape (requests, table width) is captured when it comes for the second time: a capture costs several
+    # steps' time, and under load the number of requests changes from step to step (requests end one by one), so
+    # most shapes are seen once and never again; those run kernel by kernel.
+    CAPTURE_AFTER = 2
 
     @staticmethod
     def eligible(entries) -> bool:
         return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def wants(self, entries) -> bool:
+        """Should this decode step run from a captured graph (one that exists, or one that is due)?"""
+        r = self.runner
+        blocks = 1
+        for e in entries:
+            rc = r.cache.requests.get(e.req)
+            need = (rc.length if rc is not None else 0) + 1
+            for ps in r.group_page_size.values():
+                blocks = max(blocks, -(-need // ps))
+        key = (len(entries), self.width_for(blocks))
+        g = self.graphs.get(key)
+        if g is not None and g.graph is not None:
+            return True
+        self.seen[key] = self.seen.get(key, 0) + 1
+        return self.seen[key] >= self.CAPTURE_AFTER
 
     def width_for(self, blocks: int) -> int:
         w = 8

@@ -207,7 +207,7 @@ class ModelRunner:
         tokens need not visit the host between steps.  The returned tensor may
         be reused by the next step: read it before."""
         if (self.graphs is not None and self.model.graph_safe and self.observer is None and K.TIMER[0] is None
-                and DecodeGraphs.eligible(entries)):
+                and DecodeGraphs.eligible(entries) and self.graphs.wants(entries)):
             for e in entries:
                 if not (0 <= int(e.tokens[0]) < self.vocab_size):
                     raise EngineError(f"request {e.req!r}: token id {e.tokens[0]} outside the vocabulary")

@@ -291,7 +291,7 @@ def test_time_debug_forward_and_debug_flags(model_dirs, plain_models):
         got = {k: float(v) for k, v in re.findall(r"(min|max|mean|rms) ([-+0-9.e]+)", line)}
         for k, want in (("min", x.min()), ("max", x.max()), ("mean", x.mean()), ("rms", np.sqrt((x * x).mean()))):
             assert abs(got[k] - want) <= 1e-5 + 1e-4 * abs(want), (line, k, want)
-    assert "(conv)" in lines[1] and "(attention)" in lines[2]
+    assert "(shortconv)" in lines[1] and "(attention)" in lines[2]
     tops = [l for l in err.splitlines() if "top logits:" in l]
     assert len(tops) == 4
     first = int(re.search(r"top logits: \[(\d+)\]=", tops[0]).group(1))

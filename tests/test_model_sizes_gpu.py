@@ -134,7 +134,7 @@ def test_a_captured_step_survives_the_growth_of_the_attention_scratch(wide_model
     env = r.model.env
 
     def batch(lens, tag):
-        seqs = [rng.integers(0, V, L + 2).tolist() for L in lens]
+        seqs = [rng.integers(0, V, L + 3).tolist() for L in lens]
         for i, (s, L) in enumerate(zip(seqs, lens)):
             r.step([StepEntry((tag, i), s[:L], [])])
         return seqs
@@ -148,7 +148,9 @@ def test_a_captured_step_survives_the_growth_of_the_attention_scratch(wide_model
 
     short = rng.integers(3, 60, n).tolist()
     seqs_a = batch(short, "a")
-    decode_and_check(seqs_a, short, "a", 0)                    # captures the graph of (64 requests, 8 blocks)
+    decode_and_check(seqs_a, short, "a", 0)                    # (a shape is captured when it comes the second time)
+    decode_and_check(seqs_a, short, "a", 1)                    # captures the graph of (64 requests, 8 blocks)
+    assert r.graphs.n_captures == 1
     first = env.shared["attn_scratch"]
     for i in range(n):
         r.end(("a", i))
@@ -156,6 +158,7 @@ def test_a_captured_step_survives_the_growth_of_the_attention_scratch(wide_model
     long[0] = 600                                              # one request of 10 blocks: the graph of 16 blocks
     seqs_b = batch(long, "b")
     decode_and_check(seqs_b, long, "b", 0)
+    decode_and_check(seqs_b, long, "b", 1)
     assert env.shared["attn_scratch"] is not first and env.shared["attn_scratch"].numel() > first.numel()
     assert any(t is first for t in env.shared["attn_scratch_retired"])
     for i in range(n):
