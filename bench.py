@@ -509,7 +509,8 @@ def main() -> int:
                     "frac": round(pf_frac, 4), "ms_from_tables_to_logits": round(pf_all_ms, 3),
                     "value_from_tables_to_logits": round(PROMPT_LEN * 1e3 / pf_all_ms, 1), "of": "median of 5"},
         "roofline": {"bound": "hbm", "achieved": round(head["gb"] / (ms * 1e-3), 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": head["frac"], "gb_per_step": head["gb"]},
+                     "frac": head["frac"], "gb_per_step": head["gb"],
+                     "kernel_class_shares": "profiles/decode_step_b8_launches.txt (ncu launch list of one step)"},
         "points": points,
         "clocks": clk,
     }
