@@ -26,6 +26,12 @@
 // matching BN/2 up rows (two TMA boxes into one tile), so accumulator columns c and BN/2 + c are the gate and
 // up of one output column: the epilogue writes silu(gate) * up.
 //
+// Split over K (few rows only: one row of tiles): a product with fewer tiles than SMs is cut along K into
+// `splits` parts, the unit of work being (tile, part); every CTA writes the float32 partial sums of its unit
+// to scratch memory, and the CTA that brings a tile's last part (a counter per tile) adds the parts in order
+// of their number -- not of their arrival, so the result does not depend on timing -- and runs the epilogue.
+// With it a product of 64 rows by 2048 x 5632 weights keeps 128 SMs streaming instead of 16 to 64.
+//
 // Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
 // stops issuing work, still frees its tensor memory and returns.
 #include "tcgen05.cuh"
@@ -49,7 +55,14 @@ struct TcArgs {
     int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
     int a_rows;                             // rows of the A box: 128, fewer (a multiple of 8) when M < 128
     int n_stages;                           // stages of the ring
+    int splits;                             // parts along K (1: none); only with one row of tiles
+    int kb_per_split;                       // k-blocks a part
+    float* partial;                         // splits > 1: [tile][part][M][BN] partial sums
+    int* counters;                          // splits > 1: [tile] parts that have arrived (zero before and after)
 };
+
+// the epilogue warps (threads 64 ...) among themselves
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_PER_Q * 128) : "memory"); }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -81,6 +94,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
     const int tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (n_out + N_OUT_TILE - 1) / N_OUT_TILE;
     const int n_tiles = tiles_m * tiles_n;
+    const int S = p.splits;                                              // parts along K; a unit of work is (tile, part)
+    const int n_units = n_tiles * S;
     // the CTA is persistent: it takes tiles blockIdx.x, blockIdx.x + gridDim.x, ... ; consecutive tiles
     // share the W tile (m runs fastest), so the CTAs that run together read the same few W tiles from L2
 
@@ -103,9 +118,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int s = 0;                                                    // stage, and the parity of its round
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x) {
+                const int tile = unit / S, part = unit - tile * S;
                 const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
-                for (int kb = 0; kb < n_kb; kb++) {
+                const int kb_lo = part * p.kb_per_split, kb_hi = min(n_kb, kb_lo + p.kb_per_split);
+                for (int kb = kb_lo; kb < kb_hi; kb++) {
                     if (*abort_flag || !kp_mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
                     unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
                     unsigned char* b_dst = a_dst + A_BYTES;
@@ -127,19 +144,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             int s = 0, ti = 0;
             uint32_t ph = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
-                const int b2 = ti & 1;                                    // accumulator of this tile
+            for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ti++) {
+                const int b2 = ti & 1;                                    // accumulator of this unit
                 if (*abort_flag || !kp_mbar_wait_bounded(&acc_empty[b2], ((ti >> 1) & 1) ^ 1)) { *abort_flag = 1; break; }
                 kp_tc_fence_after();
                 const uint32_t tmem_d = tmem_base + (uint32_t)(b2 * BN);
-                for (int kb = 0; kb < n_kb; kb++) {
+                const int part = unit % S;
+                const int kb_lo = part * p.kb_per_split, kb_hi = min(n_kb, kb_lo + p.kb_per_split);
+                for (int kb = kb_lo; kb < kb_hi; kb++) {
                     if (!kp_mbar_wait_bounded(&full[s], ph)) { *abort_flag = 1; ok = false; break; }
                     kp_tc_fence_after();
                     const uint32_t a_addr = kp_smem_u32(tiles + (size_t)s * (A_BYTES + B_BYTES));
                     const uint64_t adesc = kp_umma_desc(a_addr), bdesc = kp_umma_desc(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; k++)      // 32 bytes along K inside the swizzled row: +2 in the address field
-                        kp_umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                        kp_umma_bf16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, ((kb - kb_lo) | k) ? 1u : 0u);
                     kp_umma_commit(&empty[s]);                    // the stage is free when these MMAs have read it
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -147,88 +166,151 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     } else {
-        // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory; it works on tile i while the
-        // MMA warp already fills the other accumulator with tile i + 1
+        // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory; it works on unit i while the
+        // MMA warp already fills the other accumulator with unit i + 1
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;                                 // which of the quarter's warps
+        volatile int* last_flag = abort_flag + 1;                         // this CTA brought a tile's last part
+        // a piece of 32 output columns of row m, from its sums g (and u: the up half, SwiGLU), to C
+        auto finish_piece = [&](const float (&g)[32], const float (&u)[32], int m, int n_base) {
+            const int n_lim = n_out;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                float x = g[j];
+                if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
+                if (EPI == EPI_SWIGLU) {
+                    float up = u[j];
+                    if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
+                    // gate and up are rounded to the storage type first, as the unfused path stores them
+                    const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
+                    x = (gq / (1.0f + expf(-gq))) * uq;
+                }
+                v[j] = x;
+            }
+            const bool whole = p.vec_ok && n_base + 32 <= n_lim;          // 16-byte stores of the whole piece
+            if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+                bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
+                if (whole) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 o;
+                        o.x = pack2(v[j], v[j + 1]); o.y = pack2(v[j + 2], v[j + 3]);
+                        o.z = pack2(v[j + 4], v[j + 5]); o.w = pack2(v[j + 6], v[j + 7]);
+                        *reinterpret_cast<uint4*>(dst + j) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (n_base + j < n_lim) dst[j] = from_f32<bf16>(v[j]);
+                }
+            } else {
+                float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
+                if (whole) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        if (EPI == EPI_ACCUM_F32) {
+                            const float4 c4 = *reinterpret_cast<const float4*>(dst + j);
+                            o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
+                        }
+                        *reinterpret_cast<float4*>(dst + j) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (n_base + j < n_lim) {
+                            float x = v[j];
+                            if (EPI == EPI_ACCUM_F32) x += dst[j];
+                            dst[j] = x;
+                        }
+                    }
+                }
+            }
+        };
         int ti = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ti++) {
+        for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ti++) {
             const int b2 = ti & 1;
+            const int tile = unit / S, part = unit - tile * S;
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
             if (!kp_mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
             kp_tc_fence_after();
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
+            if (S == 1) {
 #pragma unroll 1
-            for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
-                uint32_t r[32];
-                kp_tmem_ld32(lane_base + c, r);
-                uint32_t u[32];
-                if (EPI == EPI_SWIGLU) kp_tmem_ld32(lane_base + BN / 2 + c, u);
-                if (m < p.M) {
-                    const int n_base = n0 + c;
-                    const int n_lim = n_out;
-                    // the 32 values of this thread's row, finished
-                    float v[32];
+                for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
+                    uint32_t r[32], u[32];
+                    kp_tmem_ld32(lane_base + c, r);
+                    if (EPI == EPI_SWIGLU) kp_tmem_ld32(lane_base + BN / 2 + c, u);
+                    if (m < p.M) {
+                        float g[32], up[32];
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        float x = __uint_as_float(r[j]);
-                        if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
-                        if (EPI == EPI_SWIGLU) {
-                            float up = __uint_as_float(u[j]);
-                            if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
-                            // gate and up are rounded to the storage type first, as the unfused path stores them
-                            const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-                            x = (gq / (1.0f + expf(-gq))) * uq;
+                        for (int j = 0; j < 32; j++) {
+                            g[j] = __uint_as_float(r[j]);
+                            up[j] = EPI == EPI_SWIGLU ? __uint_as_float(u[j]) : 0.f;
                         }
-                        v[j] = x;
-                    }
-                    const bool whole = p.vec_ok && n_base + 32 <= n_lim;      // 16-byte stores of the whole piece
-                    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
-                        bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
-                        if (whole) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 o;
-                                o.x = pack2(v[j], v[j + 1]); o.y = pack2(v[j + 2], v[j + 3]);
-                                o.z = pack2(v[j + 4], v[j + 5]); o.w = pack2(v[j + 6], v[j + 7]);
-                                *reinterpret_cast<uint4*>(dst + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++)
-                                if (n_base + j < n_lim) dst[j] = from_f32<bf16>(v[j]);
-                        }
-                    } else {
-                        float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
-                        if (whole) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                if (EPI == EPI_ACCUM_F32) {
-                                    const float4 c4 = *reinterpret_cast<const float4*>(dst + j);
-                                    o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
-                                }
-                                *reinterpret_cast<float4*>(dst + j) = o;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                if (n_base + j < n_lim) {
-                                    float x = v[j];
-                                    if (EPI == EPI_ACCUM_F32) x += dst[j];
-                                    dst[j] = x;
-                                }
-                            }
-                        }
+                        finish_piece(g, up, m, n0 + c);
                     }
                 }
+                // this warp has read the accumulator out: hand it back to the MMA warp
+                kp_tc_fence_before();
+                __syncwarp();
+                if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
+                continue;
             }
-            // this warp has read the accumulator out: hand it back to the MMA warp
+            // split over K: this part's sums of the whole accumulator (BN columns) go to the scratch ...
+            float* mine = p.partial + (((size_t)tile * S + part) * p.M + m) * BN;
+#pragma unroll 1
+            for (int c = half * 32; c < BN; c += 32 * TC_EPI_PER_Q) {
+                uint32_t r[32];
+                kp_tmem_ld32(lane_base + c, r);
+                if (m < p.M) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4*>(mine + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                             __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                }
+            }
             kp_tc_fence_before();
             __syncwarp();
             if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
+            // ... and the CTA that brings a tile's last part adds the parts up, in the order of their numbers
+            __threadfence();
+            epi_sync();
+            if (threadIdx.x == 64) {
+                const int last = atomicAdd(&p.counters[tile], 1) == S - 1;
+                if (last) p.counters[tile] = 0;                            // as it was found, for the next launch
+                *last_flag = last;
+            }
+            epi_sync();
+            if (*last_flag) {
+                __threadfence();
+                if (m < p.M) {
+                    const float* row = p.partial + ((size_t)tile * S * p.M + m) * BN;     // part 0 of this row
+                    const size_t part_stride = (size_t)p.M * BN;
+#pragma unroll 1
+                    for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
+                        float g[32], up[32];
+#pragma unroll
+                        for (int j = 0; j < 32; j++) { g[j] = 0.f; up[j] = 0.f; }
+                        for (int sp = 0; sp < S; sp++) {
+                            const float* src = row + (size_t)sp * part_stride + c;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 t = __ldcg(reinterpret_cast<const float4*>(src + j));
+                                g[j] += t.x; g[j + 1] += t.y; g[j + 2] += t.z; g[j + 3] += t.w;
+                                if (EPI == EPI_SWIGLU) {
+                                    const float4 t2 = __ldcg(reinterpret_cast<const float4*>(src + BN / 2 + j));
+                                    up[j] += t2.x; up[j + 1] += t2.y; up[j + 2] += t2.z; up[j + 3] += t2.w;
+                                }
+                            }
+                        }
+                        finish_piece(g, up, m, n0 + c);
+                    }
+                }
+            }
         }
         if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
     }
@@ -269,18 +351,21 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaSt
     }
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
-    const int n_tiles = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM);
+    const int n_units = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM) * a.splits;
     const int sms = tc_n_sm();
-    dim3 grid(n_tiles < sms ? n_tiles : sms);                  // persistent: one CTA an SM
+    dim3 grid(n_units < sms ? n_units : sms);                  // persistent: one CTA an SM
     kp_launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, s, ta, tw, a);
     return kp_launch_status();
 }
 
 extern "C" {
 
-// epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16)
-int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
-               int K, int epi, void* stream) {
+// epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16).
+// scratch / counters (may be null): memory for the split over K of few-row products: `scratch_floats` floats, and
+// `n_counters` ints that are zero and that every launch leaves zero.  Launches that share them must not overlap.
+int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+                     int K, int epi, float* scratch, long long scratch_floats, int* counters, int n_counters,
+                     void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
@@ -301,6 +386,8 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     // At most 128 rows (one row of tiles, W streamed once): see below.
     const long long m_tiles = (M + TC_BM - 1) / TC_BM;
     const int sms = tc_n_sm();
+    const int lowest = epi == EPI_SWIGLU ? 64 : 32;                      // the narrowest tile
+    auto tiles_at = [&](int w) { const int cols = epi == EPI_SWIGLU ? w / 2 : w; return (n_out + cols - 1) / cols; };
     int bn;
     if (m_tiles > 1) {
         const long long rounds_wide = (((n_out + 255) / 256) * m_tiles + sms - 1) / sms;
@@ -309,10 +396,35 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
     } else {
         // the narrowest tile that still runs in one round over the SMs (as many CTAs as possible pull on the
         // memory, none waits for a second round); products too wide for that take the widest tile
-        const int lowest = epi == EPI_SWIGLU ? 64 : 32;
-        auto tiles_at = [&](int w) { const int cols = epi == EPI_SWIGLU ? w / 2 : w; return (n_out + cols - 1) / cols; };
         bn = 256;
         while (bn > lowest && tiles_at(bn / 2) <= sms) bn /= 2;
+    }
+    // Few rows, a long K and so few output columns that even the narrowest tile leaves half of the SMs without
+    // one (2048 x 5632 at 17 to 128 rows: 29 us unsplit, every CTA reading all of A and a 64th of W): cut along K
+    // (at most 4 parts of at least 4 k-blocks) and take the widest tile that still gives three quarters of the
+    // SMs a unit of work (18 to 20 us).  Measured on the other shapes of the model (K = 2048) the split loses
+    // to the unsplit kernel (the partial sums cost more than the shorter operand reads save), so it is not used there.
+    a.splits = 1;
+    a.kb_per_split = (K + TC_BK - 1) / TC_BK;
+    if (m_tiles == 1 && M > 16 && K >= 4096 && tiles_at(lowest) * 2 <= sms && scratch != nullptr && counters != nullptr &&
+        ((uintptr_t)scratch & 15) == 0) {
+        const int n_kb = (K + TC_BK - 1) / TC_BK;
+        auto parts_at = [&](int w) {
+            int sp = sms / tiles_at(w);
+            if (sp > 4) sp = 4;
+            if (sp > n_kb / 4) sp = n_kb / 4;
+            return sp < 1 ? 1 : sp;
+        };
+        int w = 256;
+        while (w > lowest && tiles_at(w) * parts_at(w) * 4 < sms * 3) w /= 2;
+        const int sp = parts_at(w);
+        if (sp > 1 && tiles_at(w) <= n_counters && (long long)tiles_at(w) * sp * M * w <= scratch_floats) {
+            bn = w;
+            a.splits = sp;
+            a.kb_per_split = (n_kb + sp - 1) / sp;
+            a.partial = scratch;
+            a.counters = counters;
+        }
     }
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;
@@ -341,6 +453,11 @@ int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias
         default: return KP_ERR_BAD_ARG;
     }
 #undef TC_PICK
+}
+
+int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
+               int K, int epi, void* stream) {
+    return kp_gemm_tc_split(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, nullptr, 0, nullptr, 0, stream);
 }
 
 }  // extern "C"

@@ -43,6 +43,38 @@ def test_gemm_tc_against_plain(M, N, K):
     np.testing.assert_allclose(acc.cpu().double().numpy(), res + P.linear(a, w), rtol=2e-5, atol=3e-5 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("M", [17, 40, 64, 100, 128])
+def test_gemm_tc_split_over_k(M):
+    """Few rows, a long K and few output columns: the product is cut along K, the parts are added in a fixed
+    order by the CTA that brings the last one.  Every epilogue against the plain product; twice in a row gives
+    the same bits (the order of the parts does not depend on who arrives when); the counters are left zero."""
+    from kappai_b200.ops import kernels as Kn
+    rng = np.random.default_rng(63)
+    K, N, ff = 4096 + 64, 1000, 1024
+    a = rt(rng.standard_normal((M, K)), DT)
+    w = rt(rng.standard_normal((N, K)) / math.sqrt(K), DT)
+    b = rng.standard_normal(N).astype(np.float32)
+    A, W = dev(a, DT), dev(w, DT)
+    ref = P.linear(a, w, b.astype(np.float64))
+    out = Kn.gemm_tc(A, W, torch.full((M, N), float("nan"), device="cuda"), dev(b))
+    np.testing.assert_allclose(out.cpu().double().numpy(), ref, rtol=2e-5, atol=3e-5 * math.sqrt(K))
+    unsplit = Kn.gemm_tc(A, W, torch.full((M, N), float("nan"), device="cuda"), dev(b), split=False)
+    assert not torch.equal(out, unsplit), "the split did not run (same bits as the unsplit product)"
+    again = Kn.gemm_tc(A, W, torch.full((M, N), float("nan"), device="cuda"), dev(b))
+    assert torch.equal(out, again)
+    res = rng.standard_normal((M, N)).astype(np.float32)
+    acc = dev(res).clone()
+    Kn.gemm_tc(A, W, acc, None, accumulate=True)
+    np.testing.assert_allclose(acc.cpu().double().numpy(), res + P.linear(a, w), rtol=2e-5, atol=3e-5 * math.sqrt(K))
+    wgu = rt(rng.standard_normal((2 * ff, K)) * (2.0 / math.sqrt(K)), DT)
+    gu = rt(P.linear(a, wgu), DT)
+    act = Kn.gemm_tc(A, dev(wgu, DT), torch.empty((M, ff), dtype=DT, device="cuda"), None, swiglu=True)
+    want = P.swiglu(gu[:, :ff], gu[:, ff:])
+    assert np.all(np.abs(act.cpu().double().numpy() - want) <= 2e-2 * np.abs(want) + 2e-2)
+    _, counters = Kn._tc_split_scratch(A.device)
+    assert int(counters.abs().sum().item()) == 0 and Kn.tc_status() == 0
+
+
 def test_gemm_tc_rows_do_not_depend_on_m():
     from kappai_b200.ops import kernels as Kn
     rng = np.random.default_rng(61)
