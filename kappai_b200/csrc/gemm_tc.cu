@@ -260,17 +260,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
                 continue;
             }
-            // split over K: this part's sums of the whole accumulator (BN columns) go to the scratch ...
-            float* mine = p.partial + (((size_t)tile * S + part) * p.M + m) * BN;
+            // split over K: this part's sums of the whole accumulator (BN columns) go to the scratch, laid out
+            // [unit][piece of 32 columns][row][32] so that the rows of a warp's threads lie one behind the other ...
+            float* mine = p.partial + ((size_t)tile * S + part) * p.M * BN + (size_t)m * 32;
 #pragma unroll 1
             for (int c = half * 32; c < BN; c += 32 * TC_EPI_PER_Q) {
                 uint32_t r[32];
                 kp_tmem_ld32(lane_base + c, r);
                 if (m < p.M) {
+                    float* dst = mine + (size_t)(c >> 5) * p.M * 32;
 #pragma unroll
                     for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(mine + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                             __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
                 }
             }
             kp_tc_fence_before();
@@ -288,21 +290,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (*last_flag) {
                 __threadfence();
                 if (m < p.M) {
-                    const float* row = p.partial + ((size_t)tile * S * p.M + m) * BN;     // part 0 of this row
-                    const size_t part_stride = (size_t)p.M * BN;
+                    const float* row = p.partial + (size_t)tile * S * p.M * BN + (size_t)m * 32;    // part 0, piece 0 of this row
+                    const size_t part_stride = (size_t)p.M * BN, piece_stride = (size_t)p.M * 32;
 #pragma unroll 1
                     for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
                         float g[32], up[32];
 #pragma unroll
                         for (int j = 0; j < 32; j++) { g[j] = 0.f; up[j] = 0.f; }
                         for (int sp = 0; sp < S; sp++) {
-                            const float* src = row + (size_t)sp * part_stride + c;
+                            const float* src = row + (size_t)sp * part_stride + (size_t)(c >> 5) * piece_stride;
 #pragma unroll
                             for (int j = 0; j < 32; j += 4) {
                                 const float4 t = __ldcg(reinterpret_cast<const float4*>(src + j));
                                 g[j] += t.x; g[j + 1] += t.y; g[j + 2] += t.z; g[j + 3] += t.w;
                                 if (EPI == EPI_SWIGLU) {
-                                    const float4 t2 = __ldcg(reinterpret_cast<const float4*>(src + BN / 2 + j));
+                                    const float4 t2 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(BN / 64) * piece_stride + j));
                                     up[j] += t2.x; up[j + 1] += t2.y; up[j + 2] += t2.z; up[j + 3] += t2.w;
                                 }
                             }
@@ -406,7 +408,8 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
     // to the unsplit kernel (the partial sums cost more than the shorter operand reads save), so it is not used there.
     a.splits = 1;
     a.kb_per_split = (K + TC_BK - 1) / TC_BK;
-    if (m_tiles == 1 && M > 16 && K >= 4096 && tiles_at(lowest) * 2 <= sms && scratch != nullptr && counters != nullptr &&
+    const bool split_pays = K >= 4096 && tiles_at(lowest) * 2 <= sms;
+    if (m_tiles == 1 && M > 16 && split_pays && scratch != nullptr && counters != nullptr &&
         ((uintptr_t)scratch & 15) == 0) {
         const int n_kb = (K + TC_BK - 1) / TC_BK;
         auto parts_at = [&](int w) {
