@@ -19,8 +19,9 @@
 //    global memory (L1 serves them), and issue mma.m16n8k16 with the batch rows on the m side.  At a tile's
 //    end their partial sums are added in warp order, so an output depends on its own activation row only.
 //
-// Epilogues: bias; store bf16 / fp32; accumulate into fp32;
-// SwiGLU.  Every mbarrier wait is bounded; a wait that gives up sets a status word (kp_stream_status) and
+// Epilogues: bias; store bf16 / fp32; accumulate into fp32; SwiGLU; the conv step of a decode step (a tile holds
+// the 8 matching rows of B, C and X, as the SwiGLU tile holds gate and up: B, C, X are rounded to bfloat16 as the
+// separate kernels store them, then the arithmetic of shortconv.cu's decode kernel, state update included).  Every mbarrier wait is bounded; a wait that gives up sets a status word (kp_stream_status) and
 // the warp stops waiting for further stages.
 //
 // Limits: K a multiple of 512.  Other shapes take the register-streaming kernel.
@@ -32,6 +33,8 @@
 #define EPI_STORE_F32 1
 #define EPI_ACCUM_F32 2
 #define EPI_SWIGLU 3
+#define EPI_CONV_STEP 4                      // W = [B; C; X] rows (in_proj of the gated short convolution): the conv step of
+                                             // one-row segments runs in the epilogue, with the state update
 
 #define ST_CONSUMERS 8                       // consumer warps
 #define ST_THREADS ((ST_CONSUMERS + 1) * 32) // plus the producer warp
@@ -81,8 +84,13 @@ struct StreamArgs {
     const bf16* W; int ldw;
     const float* bias;
     void* C; int ldc;
-    int M, N, K, ff;
+    int M, N, K, ff;                     // ff: output columns of an epilogue that joins rows of W (SwiGLU: N / 2; conv step: N / 3)
     int n_stages;                        // stages of the ring
+    // the conv step (EPI_CONV_STEP): taps [ff][conv_k], optional bias [ff], state [slots][conv_k - 1][ff], and for
+    // every row its position (0: the state counts as zero) and its state slot
+    const float* conv_w; const float* conv_bias; float* conv_state;
+    const int* seg_pos; const int* seg_slot;
+    int conv_k;
 };
 
 // shared memory: [ring: n_stages x NW*8 rows x ST_ROW_BYTES][full[n_stages]][empty[n_stages]][red]
@@ -91,7 +99,7 @@ struct StreamArgs {
 template <int MT, bool HALF, int EPI, bool WIDE>
 __global__ void __launch_bounds__(ST_THREADS)
 gemm_stream_kernel(const StreamArgs p) {
-    constexpr int NW = (EPI == EPI_SWIGLU || WIDE) ? 2 : 1;
+    constexpr int NW = EPI == EPI_CONV_STEP ? 3 : ((EPI == EPI_SWIGLU || WIDE) ? 2 : 1);
     constexpr int ROWS = NW * 8;
     constexpr int TROWS = WIDE ? 16 : 8;                                 // output columns a tile
     constexpr int STAGE_BYTES = ROWS * ST_ROW_BYTES;
@@ -102,7 +110,7 @@ gemm_stream_kernel(const StreamArgs p) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)S * STAGE_BYTES);
     uint64_t* empty = full + S;
     float* red = reinterpret_cast<float*>(empty + S);                    // [ST_CONSUMERS][NW][MT][4][32]
-    const int n_out = (EPI == EPI_SWIGLU) ? p.ff : p.N;
+    const int n_out = (EPI == EPI_SWIGLU || EPI == EPI_CONV_STEP) ? p.ff : p.N;
     const int n_tiles = (n_out + TROWS - 1) / TROWS;
     const int n_chunks = K / ST_COLS;
 
@@ -121,7 +129,7 @@ gemm_stream_kernel(const StreamArgs p) {
             const int n0 = tile * TROWS;
             const bf16* src = nullptr;
             if (lane < ROWS) {
-                const int wrow = WIDE ? min(n0 + lane, n_out - 1) : (lane < 8 ? 0 : p.ff) + min(n0 + (lane & 7), n_out - 1);
+                const int wrow = WIDE ? min(n0 + lane, n_out - 1) : (lane >> 3) * p.ff + min(n0 + (lane & 7), n_out - 1);
                 src = p.W + (size_t)wrow * p.ldw;
             }
             for (int c = 0; c < n_chunks; c++, it++) {
@@ -236,7 +244,36 @@ gemm_stream_kernel(const StreamArgs p) {
             for (int w4 = 0; w4 < ST_CONSUMERS; w4++) v += red[(((w4 * NW + wsel) * MT + mt) * 4 + i) * 32 + l];
             if (p.bias) v += p.bias[n];
             const size_t o = (size_t)m * p.ldc + n;
-            if (EPI == EPI_SWIGLU) {
+            if (EPI == EPI_CONV_STEP) {
+                float cg = 0.f, xv = 0.f;
+#pragma unroll
+                for (int w4 = 0; w4 < ST_CONSUMERS; w4++) {
+                    cg += red[(((w4 * NW + 1) * MT + mt) * 4 + i) * 32 + l];
+                    xv += red[(((w4 * NW + NW - 1) * MT + mt) * 4 + i) * 32 + l];
+                }
+                if (p.bias) { cg += p.bias[p.ff + n]; xv += p.bias[2 * p.ff + n]; }
+                // B, C and X as the separate product stores them, then shortconv.cu's decode step: every product and
+                // sum rounded on its own (src/backend/cpu/common.c:2393-2431)
+                const float b = to_f32(from_f32<bf16>(v)), cq = to_f32(from_f32<bf16>(cg)), xq = to_f32(from_f32<bf16>(xv));
+                const int d = p.ff, Kc = p.conv_k;
+                const float* cw = p.conv_w + (size_t)n * Kc;
+                const bool fresh = p.seg_pos[m] == 0;
+                float* st = p.conv_state + (size_t)p.seg_slot[m] * (Kc - 1) * d;
+                const float bx = __fmul_rn(b, xq);
+                float hist[15];
+                for (int k = 0; k < Kc - 1; k++) hist[k] = fresh ? 0.f : st[(size_t)k * d + n];
+                float sum;
+                if (Kc == 3) {
+                    sum = __fadd_rn(__fadd_rn(__fmul_rn(hist[0], cw[0]), __fmul_rn(hist[1], cw[1])), __fmul_rn(bx, cw[2]));
+                } else {
+                    sum = __fmul_rn(bx, cw[Kc - 1]);
+                    for (int k = 0; k < Kc - 1; k++) sum = __fadd_rn(sum, __fmul_rn(hist[k], cw[k]));
+                }
+                if (p.conv_bias) sum = __fadd_rn(sum, p.conv_bias[n]);
+                ((bf16*)p.C)[o] = from_f32<bf16>(__fmul_rn(cq, sum));
+                for (int k = 0; k + 1 < Kc - 1; k++) st[(size_t)k * d + n] = hist[k + 1];
+                st[(size_t)(Kc - 2) * d + n] = bx;
+            } else if (EPI == EPI_SWIGLU) {
                 float u = 0.f;
 #pragma unroll
                 for (int w4 = 0; w4 < ST_CONSUMERS; w4++) u += red[(((w4 * NW + NW - 1) * MT + mt) * 4 + i) * 32 + l];
@@ -290,9 +327,10 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     // tiles of 16 rows of W from three m-tiles on (see the kernel; measured at 64 batch rows: 2048 x 5632 15.5 us
     // against 23.7, 2048 x 2048 8.0 against 12.2; at 32 rows the narrow tile is as fast or faster)
     constexpr bool WIDE = MT >= 3;
-    const int NW = (epi == EPI_SWIGLU || WIDE) ? 2 : 1;
-    const int n_out = epi == EPI_SWIGLU ? a.ff : a.N;
-    const int n_tiles = (n_out + (WIDE && epi != EPI_SWIGLU ? 15 : 7)) / (WIDE && epi != EPI_SWIGLU ? 16 : 8);
+    const bool joins = epi == EPI_SWIGLU || epi == EPI_CONV_STEP;        // a tile joins rows of W that lie ff apart
+    const int NW = epi == EPI_CONV_STEP ? 3 : ((epi == EPI_SWIGLU || WIDE) ? 2 : 1);
+    const int n_out = joins ? a.ff : a.N;
+    const int n_tiles = (n_out + (WIDE && !joins ? 15 : 7)) / (WIDE && !joins ? 16 : 8);
     // Measured on B200 (8 and 16 rows): three CTAs an SM with a 64 KB ring is best or tied for products with
     // many tiles (6144 x 2048: 6.9 us against 8.1 with 53 KB); a product with at most two tiles an SM (2048
     // rows) does better with two CTAs an SM and more of its long rows in flight (2048 x 5632: 8.3 against 10.3).
@@ -310,6 +348,10 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
         case EPI_STORE_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_STORE_F32, WIDE>, grid, sm, s, a);
         case EPI_ACCUM_F32: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_ACCUM_F32, WIDE>, grid, sm, s, a);
         case EPI_SWIGLU: return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_SWIGLU, false>, grid, sm, s, a);
+        case EPI_CONV_STEP:
+            // at most 16 rows: from 32 rows on the tensor-core kernel and the separate conv kernel are faster (measured)
+            if constexpr (MT == 1) return launch_pdl(gemm_stream_kernel<MT, HALF, EPI_CONV_STEP, false>, grid, sm, s, a);
+            else return KP_ERR_UNSUPPORTED;
         default: return KP_ERR_BAD_ARG;
     }
 }
@@ -329,6 +371,10 @@ static int check_common(StreamArgs& a, int M, int N, int K, int ldw, const void*
         if (N & 1) return KP_ERR_BAD_ARG;
         a.ff = N / 2;
     }
+    if (epi == EPI_CONV_STEP) {
+        if (N % 3) return KP_ERR_BAD_ARG;
+        a.ff = N / 3;
+    }
     return 0;
 }
 
@@ -344,6 +390,26 @@ int kp_gemm_stream(const void* A, int lda, const void* W, int ldw, const float* 
     a.A = (const bf16*)A; a.lda = lda; a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc;
     a.M = M; a.N = N; a.K = K;
     return launch_m(a, epi, (cudaStream_t)stream);
+}
+
+// The in_proj of the gated short convolution with the conv step of a decode step in its epilogue: W = [B; C; X]
+// ([3 d, K]), C = [M, d] bfloat16; conv_w [d][conv_k], conv_bias [d] or null, state [slots][conv_k - 1][d], and
+// for each of the M <= 16 rows its position (seg_pos) and state slot (seg_slot).  Rows are one-row segments.
+int kp_gemm_stream_conv_step(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M,
+                             int N, int K, const float* conv_w, const float* conv_bias, float* conv_state,
+                             const int* seg_pos, const int* seg_slot, int conv_k, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    StreamArgs a = {};
+    int st = check_common(a, M, N, K, ldw, W, EPI_CONV_STEP);
+    if (st) return st;
+    if (M > 16 || (lda & 7) || ((uintptr_t)A & 15) || conv_k < 2 || conv_k > 16 || !conv_w || !conv_state || !seg_pos ||
+        !seg_slot)
+        return KP_ERR_UNSUPPORTED;
+    a.A = (const bf16*)A; a.lda = lda; a.W = (const bf16*)W; a.ldw = ldw; a.bias = bias; a.C = C; a.ldc = ldc;
+    a.M = M; a.N = N; a.K = K;
+    a.conv_w = conv_w; a.conv_bias = conv_bias; a.conv_state = conv_state; a.seg_pos = seg_pos; a.seg_slot = seg_slot;
+    a.conv_k = conv_k;
+    return launch_m(a, EPI_CONV_STEP, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -628,6 +628,44 @@ def stream_pays(N: int, K: int) -> bool:
     return N <= 16384
 
 
+CONV_STEP_MAX_M = 16       # rows up to which the conv step runs in in_proj's epilogue (measured: batch 8 703 -> 672 us a
+                           # step, batch 16 776 -> 741; at 64 rows the tensor-core in_proj and the separate conv kernel win)
+
+
+def conv_step_fusable(a: torch.Tensor, w_in: torch.Tensor, conv_k: int) -> bool:
+    """Can the weight-streaming kernel run the conv step of a decode step in in_proj's epilogue?"""
+    return (USE_STREAM and skinny_ok(a, w_in) and a.shape[0] <= CONV_STEP_MAX_M and stream_fits(a.shape[1], False)
+            and w_in.shape[0] % 3 == 0 and 2 <= conv_k <= 16)
+
+
+def gemm_stream_conv_step(a: torch.Tensor, w_in: torch.Tensor, bias: Optional[torch.Tensor], conv_w: torch.Tensor,
+                          conv_bias: Optional[torch.Tensor], state: torch.Tensor, seg_pos: torch.Tensor,
+                          seg_slot: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = C * conv(B * X)`` for one-row segments, with ``[B | C | X] = a @ w_in.T (+ bias)`` never written
+    out: the product's tile holds the matching rows of B, C and X and its epilogue runs the conv step and the
+    state update of :func:`shortconv_decode` (same arithmetic, same bits)."""
+    _need(a, "a", torch.bfloat16, contiguous=False); _need(w_in, "w_in", torch.bfloat16, contiguous=False)
+    _need(out, "out", torch.bfloat16, contiguous=False)
+    _need(conv_w, "conv_w", torch.float32); _need(state, "state", torch.float32)
+    _need(seg_pos, "seg_pos", torch.int32); _need(seg_slot, "seg_slot", torch.int32)
+    M, K = a.shape
+    N = w_in.shape[0]
+    d, conv_k = N // 3, conv_w.shape[1]
+    if (w_in.shape[1] != K or N != 3 * d or out.shape != (M, d) or conv_w.shape[0] != d
+            or tuple(state.shape[1:]) != (conv_k - 1, d) or seg_pos.numel() != M or seg_slot.numel() != M):
+        raise KernelError("gemm_stream_conv_step: shape mismatch")
+    for t, nm, n in ((bias, "bias", N), (conv_bias, "conv_bias", d)):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"gemm_stream_conv_step: {nm} size")
+    lib = load_library("gemm_stream")
+    _run("gemm_stream_conv_step", lib.kp_gemm_stream_conv_step, _ptr(a), _rows_2d(a, "a"), _ptr(w_in), _rows_2d(w_in, "w_in"),
+         _ptr(bias), _ptr(out), _rows_2d(out, "out"), M, N, K, _ptr(conv_w), _ptr(conv_bias), _ptr(state), _ptr(seg_pos),
+         _ptr(seg_slot), conv_k, STREAM, tag=f" {N}x{K}", work=_gemm_work(M, N, K, a, w_in, out))
+    return out
+
+
 def _skinny_epilogue(out: torch.Tensor, accumulate: bool, swiglu: bool) -> int:
     if swiglu:
         if out.dtype != torch.bfloat16:

@@ -36,6 +36,7 @@ class ShortConv(Part):
         self.d = int(self._p("hidden_size"))
         self.K = int(self._p("kernel_size"))
         self.bias = bool(self._p("bias", False))
+        self.fuse_step = True           # decode steps of few rows: conv step in in_proj's epilogue where the kernel takes it
         if not (2 <= self.K <= MAX_KERNEL):
             raise ConfigError(f"shortconv: kernel_size={self.K} outside 2..{MAX_KERNEL}")
 
@@ -65,6 +66,14 @@ class ShortConv(Part):
     def forward(self, h, residual, ctx, cache):
         """``cache``: a :class:`~kappai_b200.cache.storage.StateView` with tensor
         [n_slots, kernel_size - 1, hidden_size] float32."""
+        if (ctx.decode_only and cache.writes and h.dtype == torch.bfloat16 and self.fuse_step
+                and K.conv_step_fusable(h, self.w_in, self.K)):
+            # a decode step of few rows: the conv step runs in in_proj's epilogue (one launch less a layer)
+            y = torch.empty((ctx.n_rows, self.d), dtype=h.dtype, device=h.device)
+            K.gemm_stream_conv_step(h, self.w_in, self.b_in, self.w_conv, self.b_conv, cache.tensor, ctx.seg_pos,
+                                    ctx.seg_slot, y)
+            linear(y, self.w_out, self.b_out, out=residual, accumulate=True)
+            return
         p = linear(h, self.w_in, self.b_in)
         y = torch.empty((ctx.n_rows, self.d), dtype=p.dtype, device=p.device)
         if ctx.decode_only and cache.writes:

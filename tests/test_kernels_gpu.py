@@ -202,6 +202,49 @@ def test_shortconv_segments_and_state(dtype, d, K, with_bias):
     assert np.array_equal(new_state[untouched], state0[untouched].astype(np.float64))
 
 
+@pytest.mark.parametrize("M,d,K,Kc,with_bias", [(1, 64, 512, 3, False), (8, 96, 1024, 4, True), (11, 200, 512, 2, True),
+                                                (16, 2048, 2048, 3, False)])
+def test_conv_step_in_the_in_proj_epilogue(M, d, K, Kc, with_bias):
+    """The weight-streaming product with the conv step of a decode step in its epilogue: [B | C | X] = a W^T is
+    never written out.  Against the plain product followed by the plain conv step; and the same bits, output and
+    state, as the separate product and decode kernels."""
+    from kappai_b200.ops import kernels as Kn
+    dtype = torch.bfloat16
+    rng = np.random.default_rng(8)
+    a = rt(rng.standard_normal((M, K)), dtype)
+    w_in = rt(rng.standard_normal((3 * d, K)) / np.sqrt(K), dtype)
+    b_in = rng.standard_normal(3 * d).astype(np.float32) * 0.1 if with_bias else None
+    cw = rng.uniform(-0.6, 0.6, (d, Kc)).astype(np.float32)
+    cb = rng.standard_normal(d).astype(np.float32) * 0.1 if with_bias else None
+    n_slots = M + 3
+    slots = rng.permutation(n_slots)[:M]
+    pos = [0 if i % 3 == 1 else 4 + i for i in range(M)]                    # some rows start their sequence
+    state0 = rng.standard_normal((n_slots, Kc - 1, d)).astype(np.float32)
+    A, W = dev(a, dtype), dev(w_in, dtype)
+    assert Kn.conv_step_fusable(A, W, Kc)
+    opt = lambda t: None if t is None else dev(t)
+    st_fused = dev(state0).clone()
+    y_fused = torch.full((M, d), float("nan"), dtype=dtype, device="cuda")
+    Kn.gemm_stream_conv_step(A, W, opt(b_in), dev(cw), opt(cb), st_fused, i32(pos), i32(slots), y_fused)
+    # the separate kernels
+    p = Kn.gemm_skinny(A, W, torch.empty((M, 3 * d), dtype=dtype, device="cuda"), opt(b_in))
+    st_sep = dev(state0).clone()
+    y_sep = torch.empty((M, d), dtype=dtype, device="cuda")
+    Kn.shortconv_decode(p, dev(cw), opt(cb), st_sep, i32(pos), i32(slots), y_sep)
+    assert torch.equal(y_fused, y_sep) and torch.equal(st_fused, st_sep)
+    # the plain implementation, row by row (the product rounded to the storage type, as both paths do)
+    pq = rt(P.linear(a, w_in, None if b_in is None else b_in.astype(np.float64)), dtype)
+    got, new_state = y_fused.cpu().double().numpy(), st_fused.cpu().double().numpy()
+    for i in range(M):
+        ref, hist = conv_stream_reference(pq[i:i + 1], cw.astype(np.float64), None if cb is None else cb.astype(np.float64),
+                                          state0[slots[i]].astype(np.float64), pos[i] == 0)
+        np.testing.assert_allclose(got[i:i + 1], ref, rtol=tol(dtype), atol=tol(dtype), err_msg=f"row {i}")
+        np.testing.assert_allclose(new_state[slots[i]], hist, rtol=1e-2, atol=1e-2, err_msg=f"state of row {i}")
+    untouched = [s for s in range(n_slots) if s not in slots]
+    assert np.array_equal(new_state[untouched], state0[untouched].astype(np.float64))
+    assert Kn.stream_status() == 0
+
+
 def test_shortconv_closed_form():
     """All-ones inputs: y_t = sum of the taps that see data, as in the reference's
     own unit test (src/test/test_hybrid.c:113-142)."""
