@@ -90,6 +90,7 @@ class _DecodeGraph:
             tables={key: _Tables(**{name: self.dev[o:o + m] for name, o, m in pieces}, **scalars)
                     for key, (pieces, scalars) in self.part_layout.items()})
         self.ctx.h2d_bytes = off * 4
+        self.last_used = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
         self.n_kernels = 0
@@ -153,6 +154,9 @@ class DecodeGraphs:
         self.runner = runner
         self.graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self.seen: Dict[Tuple[int, int], int] = {}     # how often a shape has come without being captured
+        self.pool = None                               # the captures' shared memory pool
+        self.clock = 0                                 # counts the steps: a graph remembers when it last ran
+        self.n_evicted = 0
         self.n_captures = 0
         self.n_replays = 0
 
@@ -160,6 +164,10 @@ class DecodeGraphs:
     # steps' time, and under load the number of requests changes from step to step (requests end one by one), so
     # most shapes are seen once and never again; those run kernel by kernel.
     CAPTURE_AFTER = 2
+    # Captured graphs share one memory pool (what a capture frees, the next may use) and at most MAX_GRAPHS are
+    # kept: beyond that the one that was replayed longest ago goes.  Each keeps its activations and an
+    # n x vocabulary logits buffer alive (16 MB at 64 requests and a vocabulary of 65536).
+    MAX_GRAPHS = 64
 
     @staticmethod
     def eligible(entries) -> bool:
@@ -200,6 +208,8 @@ class DecodeGraphs:
         if g is None:
             g = _DecodeGraph(r, n, key[1])
             self.graphs[key] = g
+        self.clock += 1
+        g.last_used = self.clock
         tokens = None if device_tokens is not None else [int(e.tokens[0]) for e in entries]
         g.fill(r, reqs, tokens)
         if device_tokens is not None:
@@ -235,7 +245,9 @@ class DecodeGraphs:
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph):
+            if self.pool is None:
+                self.pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self.pool):
                 g.logits = r.model.forward(g.ctx, r.storage.views)
         finally:
             if gc_was_on:
@@ -245,5 +257,13 @@ class DecodeGraphs:
             t.copy_(s)
         g.graph = graph
         self.n_captures += 1
+        captured = [k for k, v in self.graphs.items() if v.graph is not None]
+        if len(captured) > self.MAX_GRAPHS:
+            # (no kernel of the oldest graph can still be running behind the replays that came after it on this stream)
+            oldest = min((k for k in captured if self.graphs[k] is not g), key=lambda k: self.graphs[k].last_used)
+            torch.cuda.current_stream().synchronize()
+            del self.graphs[oldest]
+            self.seen.pop(oldest, None)
+            self.n_evicted += 1
         graph.replay()
         self.n_replays += 1

@@ -171,3 +171,34 @@ def test_a_captured_step_survives_the_growth_of_the_attention_scratch(wide_model
     assert r.graphs.n_captures == 2
     torch.cuda.synchronize()
     assert all(bool((t == 7.0).all()) for t in sentinels)
+
+
+def test_captured_graphs_share_a_pool_and_the_oldest_goes(wide_model):
+    """With room for two graphs only, a third shape evicts the one that ran longest ago; a shape that comes back
+    is captured again and still right."""
+    from kappai_b200 import ModelRunner, StepEntry
+    d, plain = wide_model
+    rng = np.random.default_rng(9)
+    V = WIDE_CONFIG["vocab_size"]
+    r = ModelRunner(d, dtype="bfloat16", max_tokens=8 * 128, max_requests=8, page_size=64, max_model_len=128)
+    r.graphs.MAX_GRAPHS = 2
+    seqs = [rng.integers(0, V, 40).tolist() for _ in range(4)]
+    refs = [plain.logits(s) for s in seqs]
+    for i, s in enumerate(seqs):
+        r.step([StepEntry(i, s[:5], [])])
+    fed = [5] * 4
+
+    def decode(which, steps):
+        for _ in range(steps):
+            lg = r.step([StepEntry(i, [seqs[i][fed[i]]], [0]) for i in which]).float().cpu().numpy()
+            for j, i in enumerate(which):
+                assert np.abs(lg[j] - refs[i][fed[i]]).max() <= tol_for("bfloat16", refs[i]), (which, i, fed[i])
+                fed[i] += 1
+
+    decode([0, 1, 2, 3], 3)          # shape of 4 requests: captured at its second step
+    decode([0, 1, 2], 3)             # 3 requests
+    assert r.graphs.n_captures == 2 and r.graphs.n_evicted == 0
+    decode([0, 1], 3)                # 2 requests: a third graph, the one of 4 requests goes
+    assert r.graphs.n_captures == 3 and r.graphs.n_evicted == 1 and (4, 8) not in r.graphs.graphs
+    decode([0, 1, 2, 3], 3)          # and is captured again when it comes back
+    assert r.graphs.n_captures == 4 and r.graphs.n_evicted == 2
