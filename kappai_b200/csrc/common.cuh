@@ -71,13 +71,44 @@ __device__ __forceinline__ float block_max(float v, float* smem) {
 // it waits until that kernel has finished and its writes are visible, then lets the kernel after it
 // start in turn.  So launch latency and a kernel's ramp-up hide under its predecessor.  Only work that
 // depends on nothing written by earlier kernels (loading weights) may come before kp_pdl_begin().
+#ifdef KP_TRACE
+struct KpTraceRec { unsigned long long t; unsigned tag; unsigned info; };
+#define KP_TRACE_CAP (1 << 18)
+__device__ KpTraceRec g_kp_trace[KP_TRACE_CAP];
+__device__ unsigned g_kp_trace_n;
+__device__ __forceinline__ void kp_trace_mark(unsigned phase) {
+    unsigned i = atomicAdd(&g_kp_trace_n, 1u);
+    if (i < KP_TRACE_CAP) {
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        unsigned b = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        unsigned g = gridDim.x * gridDim.y * gridDim.z;
+        g_kp_trace[i] = {t, ((unsigned)KP_TRACE << 24) | (phase << 16) | smid, (min(g, 65535u) << 16) | min(b, 65535u)};
+    }
+}
+extern "C" int kp_trace_dump(void* out, int max_recs) {
+    unsigned n = 0, zero = 0;
+    cudaDeviceSynchronize();
+    if (cudaMemcpyFromSymbol(&n, g_kp_trace_n, sizeof(n)) != cudaSuccess) return -1;
+    if (n > KP_TRACE_CAP) n = KP_TRACE_CAP;
+    if ((int)n > max_recs) n = max_recs;
+    if (n && cudaMemcpyFromSymbol(out, g_kp_trace, (size_t)n * sizeof(KpTraceRec)) != cudaSuccess) return -2;
+    cudaMemcpyToSymbol(g_kp_trace_n, &zero, sizeof(zero));
+    return (int)n;
+}
+#define KP_TRACE_MARK(ph) do { if (threadIdx.x == 0) kp_trace_mark(ph); } while (0)
+#define KP_TRACE_MARK_LANE(ph) kp_trace_mark(ph)
+#else
+#define KP_TRACE_MARK(ph)
+#define KP_TRACE_MARK_LANE(ph)
+#endif
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void kp_pdl_begin() { pdl_wait(); pdl_launch_dependents(); }
+__device__ __forceinline__ void kp_pdl_begin() { KP_TRACE_MARK(0); pdl_wait(); KP_TRACE_MARK(1); pdl_launch_dependents(); }
 // The same with the kernel after this one let in first: it may then become resident, and run what it has
 // before its own wait (a product's producers fill their rings with weights), while this kernel still waits
 // for the one before it.  For the small kernels of a decode step that stand between two products.
-__device__ __forceinline__ void kp_pdl_begin_early() { pdl_launch_dependents(); pdl_wait(); }
+__device__ __forceinline__ void kp_pdl_begin_early() { KP_TRACE_MARK(0); pdl_launch_dependents(); pdl_wait(); KP_TRACE_MARK(1); }
 // Early only for a step of several rows: with a single row (batch 1) the early form measured 2 % slower.
 __device__ __forceinline__ void kp_pdl_begin_early_if(bool several_rows) {
     if (several_rows) kp_pdl_begin_early(); else kp_pdl_begin();

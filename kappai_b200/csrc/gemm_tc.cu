@@ -26,11 +26,12 @@
 // matching BN/2 up rows (two TMA boxes into one tile), so accumulator columns c and BN/2 + c are the gate and
 // up of one output column: the epilogue writes silu(gate) * up.
 //
-// Split over K (few rows only: one row of tiles): a product with fewer tiles than SMs is cut along K into
-// `splits` parts, the unit of work being (tile, part); every CTA writes the float32 partial sums of its unit
-// to scratch memory, and the CTA that brings a tile's last part (a counter per tile) adds the parts in order
-// of their number -- not of their arrival, so the result does not depend on timing -- and runs the epilogue.
-// With it a product of 64 rows by 2048 x 5632 weights keeps 128 SMs streaming instead of 16 to 64.
+// Split over K (17 to 128 rows: one row of tiles): the product is cut along K into `splits` parts, the unit of
+// work being (tile, part), all units in one round over the SMs; every CTA writes the float32 partial sums of its
+// unit to scratch memory, waits (bounded) until the tile's other parts are there (a counter per tile), and adds
+// up its share of the tile: the parts in order of their number -- not of their arrival, so the result does not
+// depend on timing -- then the epilogue.  With it every SM brings in a part of A only, and wide tiles still
+// keep all SMs streaming.
 //
 // Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
 // stops issuing work, still frees its tensor memory and returns.
@@ -58,7 +59,7 @@ struct TcArgs {
     int splits;                             // parts along K (1: none); only with one row of tiles
     int kb_per_split;                       // k-blocks a part
     float* partial;                         // splits > 1: [tile][part][M][BN] partial sums
-    int* counters;                          // splits > 1: [tile] parts that have arrived (zero before and after)
+    int* counters;                          // splits > 1: [tile][2] parts that have arrived, CTAs that have added up (zero before and after)
 };
 
 // the epilogue warps (threads 64 ...) among themselves
@@ -67,6 +68,68 @@ __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
+}
+
+// A piece of W output columns (32, or 4 in the split's reduction) of row m, from its sums g (and u: the up half,
+// SwiGLU), to C: bias, SwiGLU or accumulation, and the store (vector stores where rows of C are 16-byte aligned).
+template <int EPI, int W>
+__device__ __forceinline__ void tc_finish(const TcArgs& p, int n_lim, const float (&g)[W], const float (&u)[W], int m,
+                                          int n_base) {
+    float v[W];
+#pragma unroll
+    for (int j = 0; j < W; j++) {
+        float x = g[j];
+        if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
+        if (EPI == EPI_SWIGLU) {
+            float up = u[j];
+            if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
+            // gate and up are rounded to the storage type first, as the unfused path stores them
+            const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
+            x = (gq / (1.0f + expf(-gq))) * uq;
+        }
+        v[j] = x;
+    }
+    const bool whole = p.vec_ok && n_base + W <= n_lim;                  // vector stores of the whole piece
+    if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
+        bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
+        if (whole && W >= 8) {
+#pragma unroll
+            for (int j = 0; j + 8 <= W; j += 8) {
+                uint4 o;
+                o.x = pack2(v[j], v[j + 1]); o.y = pack2(v[j + 2], v[j + 3]);
+                o.z = pack2(v[j + 4], v[j + 5]); o.w = pack2(v[j + 6], v[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = o;
+            }
+        } else if (whole && W == 4) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack2(v[0], v[1]), pack2(v[2], v[3]));
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++)
+                if (n_base + j < n_lim) dst[j] = from_f32<bf16>(v[j]);
+        }
+    } else {
+        float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
+        if (whole) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (EPI == EPI_ACCUM_F32) {
+                    const float4 c4 = *reinterpret_cast<const float4*>(dst + j);
+                    o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++) {
+                if (n_base + j < n_lim) {
+                    float x = v[j];
+                    if (EPI == EPI_ACCUM_F32) x += dst[j];
+                    dst[j] = x;
+                }
+            }
+        }
+    }
 }
 
 template <int BN, int EPI>
@@ -111,10 +174,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     kp_tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    kp_pdl_begin();
 
     if (warp == 0) {
         if (lane == 0) {
+            auto load_w = [&](int s, int kb, int n0) {
+                unsigned char* b_dst = tiles + (size_t)s * (A_BYTES + B_BYTES) + A_BYTES;
+                if (EPI == EPI_SWIGLU) {
+                    kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
+                    kp_tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
+                } else {
+                    kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+                }
+            };
+            // The weights depend on no earlier kernel: the W tiles of the first unit's first k-blocks (as many as
+            // the ring has stages) are on their way before the wait on the kernel before; their A tiles follow it.
+            int pre = 0;
+            if ((int)blockIdx.x < n_units) {
+                const int tile = blockIdx.x / S, part = blockIdx.x - tile * S;
+                const int n0 = (tile / tiles_m) * N_OUT_TILE;
+                const int kb_lo = part * p.kb_per_split, kb_hi = min(n_kb, kb_lo + p.kb_per_split);
+                pre = min(STAGES, kb_hi - kb_lo);
+                for (int i = 0; i < pre; i++) {
+                    kp_mbar_expect_tx(&full[i], A_BYTES + B_BYTES);
+                    load_w(i, kb_lo + i, n0);
+                }
+            }
+            KP_TRACE_MARK_LANE(0);
+            pdl_wait();
+            KP_TRACE_MARK_LANE(1);
+            pdl_launch_dependents();
             int s = 0;                                                    // stage, and the parity of its round
             uint32_t ph = 0;
             bool ok = true;
@@ -123,22 +211,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
                 const int kb_lo = part * p.kb_per_split, kb_hi = min(n_kb, kb_lo + p.kb_per_split);
                 for (int kb = kb_lo; kb < kb_hi; kb++) {
-                    if (*abort_flag || !kp_mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
                     unsigned char* a_dst = tiles + (size_t)s * (A_BYTES + B_BYTES);
-                    unsigned char* b_dst = a_dst + A_BYTES;
-                    kp_mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                    kp_tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
-                    if (EPI == EPI_SWIGLU) {
-                        kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);                       // gate rows
-                        kp_tma_load_2d(b_dst + B_BYTES / 2, &tmW, kb * TC_BK, p.ff + n0, &full[s]);  // up rows
+                    if (pre > 0) {
+                        pre--;                                            // armed, W on its way: only A is missing
                     } else {
-                        kp_tma_load_2d(b_dst, &tmW, kb * TC_BK, n0, &full[s]);
+                        if (*abort_flag || !kp_mbar_wait_bounded(&empty[s], ph ^ 1)) { *abort_flag = 1; ok = false; break; }
+                        kp_mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                        load_w(s, kb, n0);
                     }
+                    kp_tma_load_2d(a_dst, &tmA, kb * TC_BK, m0, &full[s]);
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
+        kp_pdl_begin();
         if (lane == 0) {
             constexpr uint32_t idesc = kp_umma_idesc(TC_BM, BN);
             int s = 0, ti = 0;
@@ -166,68 +253,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
         }
     } else {
+        kp_pdl_begin();
         // epilogue: warp w reads the 32 lanes (w % 4) * 32 ... of tensor memory; it works on unit i while the
         // MMA warp already fills the other accumulator with unit i + 1
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;                                 // which of the quarter's warps
-        volatile int* last_flag = abort_flag + 1;                         // this CTA brought a tile's last part
-        // a piece of 32 output columns of row m, from its sums g (and u: the up half, SwiGLU), to C
-        auto finish_piece = [&](const float (&g)[32], const float (&u)[32], int m, int n_base) {
-            const int n_lim = n_out;
-            float v[32];
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                float x = g[j];
-                if (p.bias && n_base + j < n_lim) x += p.bias[n_base + j];
-                if (EPI == EPI_SWIGLU) {
-                    float up = u[j];
-                    if (p.bias && n_base + j < n_lim) up += p.bias[p.ff + n_base + j];
-                    // gate and up are rounded to the storage type first, as the unfused path stores them
-                    const float gq = to_f32(from_f32<bf16>(x)), uq = to_f32(from_f32<bf16>(up));
-                    x = (gq / (1.0f + expf(-gq))) * uq;
-                }
-                v[j] = x;
-            }
-            const bool whole = p.vec_ok && n_base + 32 <= n_lim;          // 16-byte stores of the whole piece
-            if (EPI == EPI_STORE || EPI == EPI_SWIGLU) {
-                bf16* dst = (bf16*)p.C + (size_t)m * p.ldc + n_base;
-                if (whole) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint4 o;
-                        o.x = pack2(v[j], v[j + 1]); o.y = pack2(v[j + 2], v[j + 3]);
-                        o.z = pack2(v[j + 4], v[j + 5]); o.w = pack2(v[j + 6], v[j + 7]);
-                        *reinterpret_cast<uint4*>(dst + j) = o;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (n_base + j < n_lim) dst[j] = from_f32<bf16>(v[j]);
-                }
-            } else {
-                float* dst = (float*)p.C + (size_t)m * p.ldc + n_base;
-                if (whole) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
-                        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                        if (EPI == EPI_ACCUM_F32) {
-                            const float4 c4 = *reinterpret_cast<const float4*>(dst + j);
-                            o.x += c4.x; o.y += c4.y; o.z += c4.z; o.w += c4.w;
-                        }
-                        *reinterpret_cast<float4*>(dst + j) = o;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (n_base + j < n_lim) {
-                            float x = v[j];
-                            if (EPI == EPI_ACCUM_F32) x += dst[j];
-                            dst[j] = x;
-                        }
-                    }
-                }
-            }
-        };
+        volatile int* last_flag = abort_flag + 1;                         // the tile's parts are all there
         int ti = 0;
         bool ok = true;
         for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ti++) {
@@ -236,6 +267,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
             if (!kp_mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
             kp_tc_fence_after();
+            if (threadIdx.x == 64 && ti == 0) KP_TRACE_MARK_LANE(4);
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
             if (S == 1) {
@@ -251,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                             g[j] = __uint_as_float(r[j]);
                             up[j] = EPI == EPI_SWIGLU ? __uint_as_float(u[j]) : 0.f;
                         }
-                        finish_piece(g, up, m, n0 + c);
+                        tc_finish<EPI, 32>(p, n_out, g, up, m, n0 + c);
                     }
                 }
                 // this warp has read the accumulator out: hand it back to the MMA warp
@@ -278,42 +310,91 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             kp_tc_fence_before();
             __syncwarp();
             if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
-            // ... and the CTA that brings a tile's last part adds the parts up, in the order of their numbers
+            // ... and when all the parts of the tile are there (a counter per tile; the parts of a tile run at the
+            // same time, one a CTA, in a grid of one round), every one of their CTAs adds up its share of the tile,
+            // part by part in the order of their numbers -- not of their arrival, so the result does not depend on
+            // timing -- and runs the epilogue on it.
             __threadfence();
             epi_sync();
             if (threadIdx.x == 64) {
-                const int last = atomicAdd(&p.counters[tile], 1) == S - 1;
-                if (last) p.counters[tile] = 0;                            // as it was found, for the next launch
-                *last_flag = last;
+                int* arrived = p.counters + 2 * tile;
+                KP_TRACE_MARK_LANE(5);
+                atomicAdd(arrived, 1);
+                const unsigned long long t0 = kp_now_ns();
+                int got = 0;
+                while (true) {
+                    int v;
+                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(arrived) : "memory");
+                    if (v >= S) { got = 1; break; }
+                    if (kp_now_ns() - t0 > KP_TMA_WAIT_NS) break;
+                    __nanosleep(64);
+                }
+                *last_flag = got;
+                KP_TRACE_MARK_LANE(6);
             }
             epi_sync();
-            if (*last_flag) {
-                __threadfence();
-                if (m < p.M) {
-                    const float* row = p.partial + (size_t)tile * S * p.M * BN + (size_t)m * 32;    // part 0, piece 0 of this row
-                    const size_t part_stride = (size_t)p.M * BN, piece_stride = (size_t)p.M * 32;
-#pragma unroll 1
-                    for (int c = half * 32; c < N_OUT_TILE; c += 32 * TC_EPI_PER_Q) {
-                        float g[32], up[32];
+            if (!*last_flag) { ok = false; break; }
+            __threadfence();
+            {
+                // the tile's sums lie [piece of 32 columns][row][32] in every part, so a float4 of the output has the
+                // same offset in all of them; this CTA's share is a contiguous range of float4s
+                const int n_vec = N_OUT_TILE / 32 * p.M * 8;
+                const int lo = (int)((long long)n_vec * part / S), hi = (int)((long long)n_vec * (part + 1) / S);
+                const float* base = p.partial + (size_t)tile * S * p.M * BN;
+                const size_t part_stride = (size_t)p.M * BN;
+                // two float4s a thread at a time, the parts four by four: the loads of a round are all in flight
+                // together (each is a trip to L2), the sums still run in the order of the parts
+                constexpr int VI = 2, NT = TC_EPI_PER_Q * 128;
+                constexpr size_t up_off = (size_t)(BN / 64) * 32;        // x p.M: from a gate piece to its up piece
+                for (int i0 = lo + (int)threadIdx.x - 64; i0 < hi; i0 += VI * NT) {
+                    float4 g[VI], up[VI];
 #pragma unroll
-                        for (int j = 0; j < 32; j++) { g[j] = 0.f; up[j] = 0.f; }
-                        for (int sp = 0; sp < S; sp++) {
-                            const float* src = row + (size_t)sp * part_stride + (size_t)(c >> 5) * piece_stride;
+                    for (int v = 0; v < VI; v++) g[v] = up[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int sp0 = 0; sp0 < S; sp0 += 4) {
+                        float4 t[VI][4], t2[VI][4];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                const float4 t = __ldcg(reinterpret_cast<const float4*>(src + j));
-                                g[j] += t.x; g[j + 1] += t.y; g[j + 2] += t.z; g[j + 3] += t.w;
-                                if (EPI == EPI_SWIGLU) {
-                                    const float4 t2 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(BN / 64) * piece_stride + j));
-                                    up[j] += t2.x; up[j + 1] += t2.y; up[j + 2] += t2.z; up[j + 3] += t2.w;
+                        for (int v = 0; v < VI; v++)
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int idx = i0 + v * NT;
+                                t[v][u] = t2[v][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (idx < hi && sp0 + u < S) {
+                                    const float* src = base + (size_t)(sp0 + u) * part_stride + (size_t)idx * 4;
+                                    t[v][u] = __ldcg(reinterpret_cast<const float4*>(src));
+                                    if (EPI == EPI_SWIGLU) t2[v][u] = __ldcg(reinterpret_cast<const float4*>(src + up_off * p.M));
                                 }
                             }
+#pragma unroll
+                        for (int v = 0; v < VI; v++)
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                if (sp0 + u < S) {
+                                    g[v].x += t[v][u].x; g[v].y += t[v][u].y; g[v].z += t[v][u].z; g[v].w += t[v][u].w;
+                                    up[v].x += t2[v][u].x; up[v].y += t2[v][u].y; up[v].z += t2[v][u].z; up[v].w += t2[v][u].w;
+                                }
+                            }
+                    }
+#pragma unroll
+                    for (int v = 0; v < VI; v++) {
+                        const int idx = i0 + v * NT;
+                        if (idx < hi) {
+                            const float g4[4] = {g[v].x, g[v].y, g[v].z, g[v].w}, u4[4] = {up[v].x, up[v].y, up[v].z, up[v].w};
+                            const int piece = idx / (p.M * 8), rem = idx - piece * (p.M * 8);
+                            tc_finish<EPI, 4>(p, n_out, g4, u4, m0 + (rem >> 3), n0 + piece * 32 + (rem & 7) * 4);
                         }
-                        finish_piece(g, up, m, n0 + c);
                     }
                 }
             }
+            // the counters go back to zero with the last CTA that has read the parts
+            epi_sync();
+            if (threadIdx.x == 64) {
+                if (atomicAdd(p.counters + 2 * tile + 1, 1) == S - 1) {
+                    p.counters[2 * tile + 1] = 0;
+                    p.counters[2 * tile] = 0;
+                }
+            }
         }
+        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(2);
         if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
     }
     kp_tc_fence_before();
@@ -323,6 +404,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // ------------------------------------------------------------------------------------------ host side
 #define TC_SMEM_KB 208                       // shared memory for the ring
+#ifndef TC_SPLIT_COST_KB
+#define TC_SPLIT_COST_KB 96                  // what a split over K costs beside the operand reads, as KB brought into an SM
+#endif
 
 // SMs of the current device (asked once)
 static int tc_n_sm() {
@@ -401,35 +485,41 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
         bn = 256;
         while (bn > lowest && tiles_at(bn / 2) <= sms) bn /= 2;
     }
-    // Few rows, a long K and so few output columns that even the narrowest tile leaves half of the SMs without
-    // one (2048 x 5632 at 17 to 128 rows: 29 us unsplit, every CTA reading all of A and a 64th of W): cut along K
-    // (at most 4 parts of at least 4 k-blocks) and take the widest tile that still gives three quarters of the
-    // SMs a unit of work (18 to 20 us).  Measured on the other shapes of the model (K = 2048) the split loses
-    // to the unsplit kernel (the partial sums cost more than the shorter operand reads save), so it is not used there.
+    // 17 to 128 rows (one row of tiles): what bounds the product is the bytes that the busiest SM brings in, about
+    // 45 GB/s an SM whatever the source -- its share of W and, for every tile, all the rows of A.  Unsplit, a
+    // narrow tile reads A once for a few rows of W (64 rows by 2048 x 5632 in 32-row tiles: 720 KB of A for 360 KB
+    // of W) and wide tiles leave SMs idle.  So the product is cut along K as well: (tile width, parts) is chosen
+    // so that the units fill one round over the SMs and a unit brings in the fewest bytes; the price of the split
+    // (partial sums out and in, the wait for the other parts) is counted as TC_SPLIT_COST_KB of traffic.
     a.splits = 1;
     a.kb_per_split = (K + TC_BK - 1) / TC_BK;
-    const bool split_pays = K >= 4096 && tiles_at(lowest) * 2 <= sms;
-    if (m_tiles == 1 && M > 16 && split_pays && scratch != nullptr && counters != nullptr &&
-        ((uintptr_t)scratch & 15) == 0) {
+    a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
+    if (m_tiles == 1 && M > 16 && scratch != nullptr && counters != nullptr && ((uintptr_t)scratch & 15) == 0) {
         const int n_kb = (K + TC_BK - 1) / TC_BK;
-        auto parts_at = [&](int w) {
-            int sp = sms / tiles_at(w);
-            if (sp > 4) sp = 4;
-            if (sp > n_kb / 4) sp = n_kb / 4;
-            return sp < 1 ? 1 : sp;
-        };
-        int w = 256;
-        while (w > lowest && tiles_at(w) * parts_at(w) * 4 < sms * 3) w /= 2;
-        const int sp = parts_at(w);
-        if (sp > 1 && tiles_at(w) <= n_counters && (long long)tiles_at(w) * sp * M * w <= scratch_floats) {
-            bn = w;
-            a.splits = sp;
-            a.kb_per_split = (n_kb + sp - 1) / sp;
+        long long best = -1;
+        int best_bn = bn, best_sp = 1;
+        for (int w = 256; w >= lowest; w /= 2) {
+            const int tiles = tiles_at(w);
+            const long long rounds = (tiles + sms - 1) / sms;
+            for (int sp = 1; sp <= 16; sp++) {
+                if (sp > 1 && (tiles * sp > sms || 2 * tiles > n_counters || sp * 2 > n_kb ||
+                               (long long)tiles * sp * M * w > scratch_floats))
+                    break;
+                const int kbs = (n_kb + sp - 1) / sp;
+                if (sp > 1 && (n_kb + kbs - 1) / kbs != sp) continue;            // a part would be empty
+                long long cost = (sp == 1 ? rounds * n_kb : kbs) * (long long)(TC_BK * 2) * (w + a.a_rows);
+                if (sp > 1) cost += TC_SPLIT_COST_KB * 1024;
+                if (best < 0 || cost < best) { best = cost; best_bn = w; best_sp = sp; }
+            }
+        }
+        bn = best_bn;
+        if (best_sp > 1) {
+            a.splits = best_sp;
+            a.kb_per_split = (n_kb + best_sp - 1) / best_sp;
             a.partial = scratch;
             a.counters = counters;
         }
     }
-    a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
     alignas(64) CUtensorMap ta, tw;
     int st = kp_make_map_bf16_2d(&ta, A, (unsigned long long)M, K, lda, TC_BK, a.a_rows);
     if (st) return st;

@@ -171,8 +171,13 @@ _STATUS_LIBS = (("gemm_tc", "tc"), ("gemm_stream", "stream"), ("attention_mma", 
 
 def read_status() -> dict:
     """Library -> status word (0, or 1 if a bounded wait gave up since the last call) of every kernel library
-    that is loaded and has one; the words are cleared.  Synchronises the device."""
-    return {lib: _read_one(lib, name) for lib, name in _STATUS_LIBS if is_loaded(lib)}
+    that is loaded and has one; the words are cleared.  Synchronises the device.  A tcgen05 product that gave up
+    may have left the counters of its split over K behind: they are set back to zero."""
+    st = {lib: _read_one(lib, name) for lib, name in _STATUS_LIBS if is_loaded(lib)}
+    if st.get("gemm_tc"):
+        for _, counters in _TC_SPLIT.values():
+            counters.zero_()
+    return st
 
 
 def _read_one(lib: str, name: str) -> int:
@@ -551,12 +556,17 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 USE_TC = True              # bfloat16 products of more than 64 rows (and some of fewer) run on tcgen05 tensor cores
 
 
+TC_SPLIT_FROM_M = 17       # rows from which every product goes to the tcgen05 kernel (cut along K where that pays)
+
+
 def tc_pays_for_few_rows(M: int, N: int, swiglu: bool) -> bool:
     """Few-row products that the tcgen05 kernel runs faster than the weight-streaming
     kernels (measured on B200, K = 2048): the 65536-row head from 8 rows on (46 us at
     every M against 48 us at 8 rows and 199 us at 64), and wide products from 32 rows
     on (6144 rows: 13 us at every M against 17 us at 32 rows and 28 us at 64).  Narrow
     products (2048 rows: few tiles) stay with the streaming kernels at every M <= 64."""
+    if M >= TC_SPLIT_FROM_M:
+        return True
     if swiglu:
         return N >= 8192 and M >= 32        # gate/up 11264 x 2048: 19.9 us against 22.9 at 32 rows, 19.8 against 32.1 at 64
     return (N >= 32768 and M >= 8) or (N >= 4096 and M >= 32)
@@ -573,12 +583,12 @@ _TC_SPLIT = {}             # device index -> (float32 scratch, int32 counters) o
 
 
 def _tc_split_scratch(device: torch.device):
-    """Scratch of the split over K: 16 MB of partial sums and a counter per tile, made once a device (the first
+    """Scratch of the split over K: 32 MB of partial sums and two counters per tile, made once a device (the first
     call comes in an eager step, before any capture).  The counters are zero between launches."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     got = _TC_SPLIT.get(key)
     if got is None:
-        got = (torch.empty(1 << 22, dtype=torch.float32, device=device), torch.zeros(1024, dtype=torch.int32, device=device))
+        got = (torch.empty(1 << 23, dtype=torch.float32, device=device), torch.zeros(1024, dtype=torch.int32, device=device))
         _TC_SPLIT[key] = got
     return got
 
