@@ -27,11 +27,11 @@
 // up of one output column: the epilogue writes silu(gate) * up.
 //
 // Split over K (17 to 128 rows: one row of tiles): the product is cut along K into `splits` parts, the unit of
-// work being (tile, part), all units in one round over the SMs; every CTA writes the float32 partial sums of its
-// unit to scratch memory, waits (bounded) until the tile's other parts are there (a counter per tile), and adds
-// up its share of the tile: the parts in order of their number -- not of their arrival, so the result does not
-// depend on timing -- then the epilogue.  With it every SM brings in a part of A only, and wide tiles still
-// keep all SMs streaming.
+// work being (tile, part), all units in one round over the SMs and the parts of a tile one thread-block cluster.
+// Every CTA leaves the float32 sums of its unit in its own shared memory (the ring is free by then); after the
+// cluster's barrier each adds up its share of the tile, reading the other CTAs' sums over the cluster's shared
+// memory, the parts in order of their number -- so the result does not depend on timing -- then the epilogue.
+// With it every SM brings in a part of A only, and wide tiles still keep all SMs streaming.
 //
 // Every wait on an mbarrier is bounded.  A wait that gives up sets a status word (kp_tc_status), the CTA
 // stops issuing work, still frees its tensor memory and returns.
@@ -56,11 +56,23 @@ struct TcArgs {
     int vec_ok;                             // rows of C are 16-byte aligned: whole pieces go out in 16-byte stores
     int a_rows;                             // rows of the A box: 128, fewer (a multiple of 8) when M < 128
     int n_stages;                           // stages of the ring
-    int splits;                             // parts along K (1: none); only with one row of tiles
+    int splits;                             // parts along K (1: none); only with one row of tiles; the cluster's size
     int kb_per_split;                       // k-blocks a part
-    float* partial;                         // splits > 1: [tile][part][M][BN] partial sums
-    int* counters;                          // splits > 1: [tile][2] parts that have arrived, CTAs that have added up (zero before and after)
 };
+
+// all threads of all CTAs of the cluster; what they wrote to shared memory before is visible to the others after
+__device__ __forceinline__ void kp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 16 bytes of the shared memory of the cluster's CTA `rank`, at the place that `addr` has in this CTA's
+__device__ __forceinline__ float4 kp_ld_cluster_f4(uint32_t addr, int rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(addr), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+    return v;
+}
 
 // the epilogue warps (threads 64 ...) among themselves
 __device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_PER_Q * 128) : "memory"); }
@@ -174,6 +186,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     kp_tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    bool parts_ok = false;                                                // (epilogue warps) this CTA's sums are in shared memory
 
     if (warp == 0) {
         if (lane == 0) {
@@ -258,12 +271,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // MMA warp already fills the other accumulator with unit i + 1
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;                                 // which of the quarter's warps
-        volatile int* last_flag = abort_flag + 1;                         // the tile's parts are all there
         int ti = 0;
         bool ok = true;
         for (int unit = blockIdx.x; unit < n_units && ok; unit += gridDim.x, ti++) {
             const int b2 = ti & 1;
-            const int tile = unit / S, part = unit - tile * S;
+            const int tile = unit / S;
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
             if (!kp_mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
             kp_tc_fence_after();
@@ -292,120 +304,101 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
                 continue;
             }
-            // split over K: this part's sums of the whole accumulator (BN columns) go to the scratch, laid out
-            // [unit][piece of 32 columns][row][32] so that the rows of a warp's threads lie one behind the other ...
-            float* mine = p.partial + ((size_t)tile * S + part) * p.M * BN + (size_t)m * 32;
+            // split over K: this part's sums of the whole accumulator (BN columns) go to this CTA's shared memory
+            // (the ring is free: every MMA of the unit has completed), laid out [piece of 32 columns][float4 of
+            // the piece][row][4] so that a warp's rows lie one behind the other; the tile's CTAs -- a cluster --
+            // add them up below
+            float4* mine = reinterpret_cast<float4*>(tiles);
 #pragma unroll 1
             for (int c = half * 32; c < BN; c += 32 * TC_EPI_PER_Q) {
                 uint32_t r[32];
                 kp_tmem_ld32(lane_base + c, r);
                 if (m < p.M) {
-                    float* dst = mine + (size_t)(c >> 5) * p.M * 32;
+                    float4* dst = mine + (size_t)(c >> 5) * 8 * p.M + m;
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    for (int j = 0; j < 8; j++)
+                        dst[(size_t)j * p.M] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                 }
             }
             kp_tc_fence_before();
             __syncwarp();
             if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
-            // ... and when all the parts of the tile are there (a counter per tile; the parts of a tile run at the
-            // same time, one a CTA, in a grid of one round), every one of their CTAs adds up its share of the tile,
-            // part by part in the order of their numbers -- not of their arrival, so the result does not depend on
-            // timing -- and runs the epilogue on it.
-            __threadfence();
-            epi_sync();
-            if (threadIdx.x == 64) {
-                int* arrived = p.counters + 2 * tile;
-                KP_TRACE_MARK_LANE(5);
-                atomicAdd(arrived, 1);
-                const unsigned long long t0 = kp_now_ns();
-                int got = 0;
-                while (true) {
-                    int v;
-                    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(arrived) : "memory");
-                    if (v >= S) { got = 1; break; }
-                    if (kp_now_ns() - t0 > KP_TMA_WAIT_NS) break;
-                    __nanosleep(64);
-                }
-                *last_flag = got;
-                KP_TRACE_MARK_LANE(6);
-            }
-            epi_sync();
-            if (!*last_flag) { ok = false; break; }
-            __threadfence();
-            {
-                // the tile's sums lie [piece of 32 columns][row][32] in every part, so a float4 of the output has the
-                // same offset in all of them; this CTA's share is a contiguous range of float4s
-                const int n_vec = N_OUT_TILE / 32 * p.M * 8;
-                const int lo = (int)((long long)n_vec * part / S), hi = (int)((long long)n_vec * (part + 1) / S);
-                const float* base = p.partial + (size_t)tile * S * p.M * BN;
-                const size_t part_stride = (size_t)p.M * BN;
-                // two float4s a thread at a time, the parts four by four: the loads of a round are all in flight
-                // together (each is a trip to L2), the sums still run in the order of the parts
-                constexpr int VI = 2, NT = TC_EPI_PER_Q * 128;
-                constexpr size_t up_off = (size_t)(BN / 64) * 32;        // x p.M: from a gate piece to its up piece
-                for (int i0 = lo + (int)threadIdx.x - 64; i0 < hi; i0 += VI * NT) {
-                    float4 g[VI], up[VI];
-#pragma unroll
-                    for (int v = 0; v < VI; v++) g[v] = up[v] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int sp0 = 0; sp0 < S; sp0 += 4) {
-                        float4 t[VI][4], t2[VI][4];
-#pragma unroll
-                        for (int v = 0; v < VI; v++)
-#pragma unroll
-                            for (int u = 0; u < 4; u++) {
-                                const int idx = i0 + v * NT;
-                                t[v][u] = t2[v][u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                if (idx < hi && sp0 + u < S) {
-                                    const float* src = base + (size_t)(sp0 + u) * part_stride + (size_t)idx * 4;
-                                    t[v][u] = __ldcg(reinterpret_cast<const float4*>(src));
-                                    if (EPI == EPI_SWIGLU) t2[v][u] = __ldcg(reinterpret_cast<const float4*>(src + up_off * p.M));
-                                }
-                            }
-#pragma unroll
-                        for (int v = 0; v < VI; v++)
-#pragma unroll
-                            for (int u = 0; u < 4; u++) {
-                                if (sp0 + u < S) {
-                                    g[v].x += t[v][u].x; g[v].y += t[v][u].y; g[v].z += t[v][u].z; g[v].w += t[v][u].w;
-                                    up[v].x += t2[v][u].x; up[v].y += t2[v][u].y; up[v].z += t2[v][u].z; up[v].w += t2[v][u].w;
-                                }
-                            }
-                    }
-#pragma unroll
-                    for (int v = 0; v < VI; v++) {
-                        const int idx = i0 + v * NT;
-                        if (idx < hi) {
-                            const float g4[4] = {g[v].x, g[v].y, g[v].z, g[v].w}, u4[4] = {up[v].x, up[v].y, up[v].z, up[v].w};
-                            const int piece = idx / (p.M * 8), rem = idx - piece * (p.M * 8);
-                            tc_finish<EPI, 4>(p, n_out, g4, u4, m0 + (rem >> 3), n0 + piece * 32 + (rem & 7) * 4);
-                        }
-                    }
-                }
-            }
-            // the counters go back to zero with the last CTA that has read the parts
-            epi_sync();
-            if (threadIdx.x == 64) {
-                if (atomicAdd(p.counters + 2 * tile + 1, 1) == S - 1) {
-                    p.counters[2 * tile + 1] = 0;
-                    p.counters[2 * tile] = 0;
-                }
-            }
+            if (threadIdx.x == 64) KP_TRACE_MARK_LANE(5);
+            parts_ok = true;
         }
-        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(2);
         if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
     }
     kp_tc_fence_before();
     __syncthreads();
+    if (S > 1) {
+        // Split over K: the CTAs of a tile are a cluster (rank = part).  When all of them have their sums in
+        // shared memory, each adds up its share of the tile, reading the others' over the cluster's shared
+        // memory: the parts in the order of their numbers, so the result does not depend on timing; then the
+        // epilogue.  Every thread of every CTA comes here, also after a wait that gave up, so the cluster's
+        // barriers always complete; no CTA leaves before the others have read its sums.
+        kp_cluster_sync();
+        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(7);
+        if (warp >= 2 && parts_ok) {
+            const int tile = blockIdx.x / S, part = blockIdx.x - tile * S;
+            const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
+            const int n_vec = N_OUT_TILE / 32 * p.M * 8;                  // float4s of the tile's output
+            const int lo = (int)((long long)n_vec * part / S), hi = (int)((long long)n_vec * (part + 1) / S);
+            const uint32_t mine = kp_smem_u32(tiles);
+            const uint32_t up_off = (uint32_t)(BN / 64) * 8 * p.M * 16;   // bytes from a gate piece to its up piece
+            constexpr int NT = TC_EPI_PER_Q * 128;
+            // VI float4s a thread at a time, the parts four by four: the loads of a round are all in flight
+            // together (each is a trip to another SM), the sums still run in the order of the parts
+            constexpr int VI = EPI == EPI_SWIGLU ? 2 : 4;
+            for (int i0 = lo + (int)threadIdx.x - 64; i0 < hi; i0 += VI * NT) {
+                float4 g[VI], up[VI];
+#pragma unroll
+                for (int v = 0; v < VI; v++) g[v] = up[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp0 = 0; sp0 < S; sp0 += 4) {
+                    float4 t[VI][4], t2[VI][4];
+#pragma unroll
+                    for (int v = 0; v < VI; v++)
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int idx = i0 + v * NT;
+                            t[v][u] = t2[v][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (idx < hi && sp0 + u < S) {
+                                t[v][u] = kp_ld_cluster_f4(mine + (uint32_t)idx * 16, sp0 + u);
+                                if (EPI == EPI_SWIGLU) t2[v][u] = kp_ld_cluster_f4(mine + (uint32_t)idx * 16 + up_off, sp0 + u);
+                            }
+                        }
+#pragma unroll
+                    for (int v = 0; v < VI; v++)
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            if (sp0 + u < S) {
+                                g[v].x += t[v][u].x; g[v].y += t[v][u].y; g[v].z += t[v][u].z; g[v].w += t[v][u].w;
+                                up[v].x += t2[v][u].x; up[v].y += t2[v][u].y; up[v].z += t2[v][u].z; up[v].w += t2[v][u].w;
+                            }
+                }
+#pragma unroll
+                for (int v = 0; v < VI; v++) {
+                    const int idx = i0 + v * NT;
+                    if (idx < hi) {
+                        const float g4[4] = {g[v].x, g[v].y, g[v].z, g[v].w}, u4[4] = {up[v].x, up[v].y, up[v].z, up[v].w};
+                        const int piece = idx / (p.M * 8), rem = idx - piece * (p.M * 8);
+                        const int j4 = rem / p.M, row = rem - j4 * p.M;
+                        tc_finish<EPI, 4>(p, n_out, g4, u4, m0 + row, n0 + piece * 32 + j4 * 4);
+                    }
+                }
+            }
+        }
+        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(6);
+        kp_cluster_sync();
+    }
+    if (threadIdx.x == 64) KP_TRACE_MARK_LANE(2);
     if (warp == 1) kp_tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------------------------------ host side
 #define TC_SMEM_KB 208                       // shared memory for the ring
 #ifndef TC_SPLIT_COST_KB
-#define TC_SPLIT_COST_KB 96                  // what a split over K costs beside the operand reads, as KB brought into an SM
+#define TC_SPLIT_COST_KB 64                  // what a split over K costs beside the operand reads, as KB brought into an SM
 #endif
 
 // SMs of the current device (asked once)
@@ -419,15 +412,19 @@ static int tc_n_sm() {
     return sms;
 }
 
-template <int BN, int EPI>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaStream_t s) {
-    const int stage = a.a_rows * TC_BK * 2 + BN * TC_BK * 2;
-    const int slack = (TC_BM - a.a_rows) * TC_BK * 2;          // the MMA's reads past a short last stage
+// Shared memory of a launch: `stages` ring stages, the slack behind a short last stage, barriers, alignment.
+static size_t tc_smem(int a_rows, int bn, int* stages_out) {
+    const int stage = a_rows * TC_BK * 2 + bn * TC_BK * 2;
+    const int slack = (TC_BM - a_rows) * TC_BK * 2;            // the MMA's reads past a short last stage
     int stages = (TC_SMEM_KB * 1024 - slack) / stage;
     if (stages > 24) stages = 24;
     if (stages < 2) stages = 2;
-    a.n_stages = stages;
-    const size_t smem = (size_t)stages * stage + slack + (size_t)(2 * stages + 4) * 8 + 16 + 1024;
+    *stages_out = stages;
+    return (size_t)stages * stage + slack + (size_t)(2 * stages + 4) * 8 + 16 + 1024;
+}
+
+template <int BN, int EPI>
+static int prepare(size_t smem) {
     auto kern = gemm_tc_kernel<BN, EPI>;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
@@ -435,23 +432,91 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaSt
         if (e != cudaSuccess) return (int)e;
         attr_smem = smem;
     }
+    return 0;
+}
+
+// Clusters of `cluster` CTAs of this kernel that the device runs at once (asked once for each size; 0 if it cannot
+// be said): a split over K wants all its tiles' clusters in one round.
+template <int BN, int EPI>
+static int max_clusters(int cluster, size_t smem) {
+    static int known[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (cluster < 2 || cluster > 8) return 0;
+    if (known[cluster] == 0) {
+        known[cluster] = -1;
+        if (prepare<BN, EPI>(smem) == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(cluster * 64); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = cluster; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<BN, EPI>, &cfg) == cudaSuccess && n > 0) known[cluster] = n;
+            else cudaGetLastError();
+        }
+    }
+    return known[cluster] > 0 ? known[cluster] : 0;
+}
+
+template <int BN, int EPI>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tw, TcArgs a, cudaStream_t s) {
+    int stages = 0;
+    const size_t smem = tc_smem(a.a_rows, BN, &stages);
+    a.n_stages = stages;
+    int st = prepare<BN, EPI>(smem);
+    if (st) return st;
     const int n_out = (EPI == EPI_SWIGLU) ? a.ff : a.N;
     const int n_tile = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
     const int n_units = ((n_out + n_tile - 1) / n_tile) * ((a.M + TC_BM - 1) / TC_BM) * a.splits;
     const int sms = tc_n_sm();
-    dim3 grid(n_units < sms ? n_units : sms);                  // persistent: one CTA an SM
-    kp_launch_pdl(kern, dim3(grid), dim3(TC_THREADS), smem, s, ta, tw, a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a.splits > 1 ? n_units : (n_units < sms ? n_units : sms));   // persistent: one CTA an SM
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 1;
+    if (a.splits > 1) {                                        // the parts of a tile: one cluster
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = a.splits; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
+    cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, EPI>, ta, tw, a);
     return kp_launch_status();
+}
+
+// Clusters of `cluster` CTAs that run at once, for the tile width and epilogue of a launch.
+static int tc_max_clusters(int bn, int epi, int cluster, int a_rows) {
+    int stages = 0;
+    const size_t smem = tc_smem(a_rows, bn, &stages);
+#define TC_MC(BN_, EPI_) return max_clusters<BN_, EPI_>(cluster, smem);
+#define TC_MC_BN(EPI_)                                             \
+    switch (bn) {                                                  \
+        case 256: TC_MC(256, EPI_)                                 \
+        case 128: TC_MC(128, EPI_)                                 \
+        case 64: TC_MC(64, EPI_)                                   \
+        default: return 0;                                         \
+    }
+    switch (epi) {
+        case EPI_STORE: TC_MC_BN(EPI_STORE)
+        case EPI_STORE_F32: TC_MC_BN(EPI_STORE_F32)
+        case EPI_ACCUM_F32: TC_MC_BN(EPI_ACCUM_F32)
+        case EPI_SWIGLU: TC_MC_BN(EPI_SWIGLU)
+        default: return 0;
+    }
+#undef TC_MC_BN
+#undef TC_MC
 }
 
 extern "C" {
 
 // epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16).
-// scratch / counters (may be null): memory for the split over K of few-row products: `scratch_floats` floats, and
-// `n_counters` ints that are zero and that every launch leaves zero.  Launches that share them must not overlap.
+// split: products of 17 to 128 rows may be cut along K (0: never).
 int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
-                     int K, int epi, float* scratch, long long scratch_floats, int* counters, int n_counters,
-                     void* stream) {
+                     int K, int epi, int split, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7) || ((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return KP_ERR_UNSUPPORTED;
     if ((long long)((M + TC_BM - 1) / TC_BM) > 65535) return KP_ERR_UNSUPPORTED;
@@ -494,17 +559,20 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
     a.splits = 1;
     a.kb_per_split = (K + TC_BK - 1) / TC_BK;
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
-    if (m_tiles == 1 && M > 16 && scratch != nullptr && counters != nullptr && ((uintptr_t)scratch & 15) == 0) {
+    if (m_tiles == 1 && M > 16 && split) {
         const int n_kb = (K + TC_BK - 1) / TC_BK;
         long long best = -1;
         int best_bn = bn, best_sp = 1;
-        for (int w = 256; w >= lowest; w /= 2) {
+        for (int w = 256; w >= (lowest < 64 ? 64 : lowest); w /= 2) {
             const int tiles = tiles_at(w);
             const long long rounds = (tiles + sms - 1) / sms;
-            for (int sp = 1; sp <= 16; sp++) {
-                if (sp > 1 && (tiles * sp > sms || 2 * tiles > n_counters || sp * 2 > n_kb ||
-                               (long long)tiles * sp * M * w > scratch_floats))
-                    break;
+            int stages = 0;
+            const size_t ring = tc_smem(a.a_rows, w, &stages) - 2048;
+            for (int sp = 1; sp <= 8; sp++) {
+                if (sp > 1) {
+                    if (tiles * sp > sms || sp * 2 > n_kb || (size_t)M * w * 4 > ring) break;
+                    if (tiles > tc_max_clusters(w, epi, sp, a.a_rows)) continue;  // the clusters would not all run at once
+                }
                 const int kbs = (n_kb + sp - 1) / sp;
                 if (sp > 1 && (n_kb + kbs - 1) / kbs != sp) continue;            // a part would be empty
                 long long cost = (sp == 1 ? rounds * n_kb : kbs) * (long long)(TC_BK * 2) * (w + a.a_rows);
@@ -512,12 +580,10 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
                 if (best < 0 || cost < best) { best = cost; best_bn = w; best_sp = sp; }
             }
         }
-        bn = best_bn;
         if (best_sp > 1) {
+            bn = best_bn;
             a.splits = best_sp;
             a.kb_per_split = (n_kb + best_sp - 1) / best_sp;
-            a.partial = scratch;
-            a.counters = counters;
         }
     }
     alignas(64) CUtensorMap ta, tw;
@@ -550,7 +616,7 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
 
 int kp_gemm_tc(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                int K, int epi, void* stream) {
-    return kp_gemm_tc_split(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, nullptr, 0, nullptr, 0, stream);
+    return kp_gemm_tc_split(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, 0, stream);
 }
 
 }  // extern "C"

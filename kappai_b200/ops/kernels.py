@@ -171,13 +171,8 @@ _STATUS_LIBS = (("gemm_tc", "tc"), ("gemm_stream", "stream"), ("attention_mma", 
 
 def read_status() -> dict:
     """Library -> status word (0, or 1 if a bounded wait gave up since the last call) of every kernel library
-    that is loaded and has one; the words are cleared.  Synchronises the device.  A tcgen05 product that gave up
-    may have left the counters of its split over K behind: they are set back to zero."""
-    st = {lib: _read_one(lib, name) for lib, name in _STATUS_LIBS if is_loaded(lib)}
-    if st.get("gemm_tc"):
-        for _, counters in _TC_SPLIT.values():
-            counters.zero_()
-    return st
+    that is loaded and has one; the words are cleared.  Synchronises the device."""
+    return {lib: _read_one(lib, name) for lib, name in _STATUS_LIBS if is_loaded(lib)}
 
 
 def _read_one(lib: str, name: str) -> int:
@@ -579,26 +574,12 @@ def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-_TC_SPLIT = {}             # device index -> (float32 scratch, int32 counters) of the tcgen05 product's split over K
-
-
-def _tc_split_scratch(device: torch.device):
-    """Scratch of the split over K: 32 MB of partial sums and two counters per tile, made once a device (the first
-    call comes in an eager step, before any capture).  The counters are zero between launches."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    got = _TC_SPLIT.get(key)
-    if got is None:
-        got = (torch.empty(1 << 23, dtype=torch.float32, device=device), torch.zeros(1024, dtype=torch.int32, device=device))
-        _TC_SPLIT[key] = got
-    return got
-
-
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
             accumulate: bool = False, swiglu: bool = False, split: bool = True) -> torch.Tensor:
     """out = a @ w.T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); with
     ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up.  With ``split`` a product of 17 to
-    128 rows that has fewer tiles than the device has SMs is cut along K (the parts are added in a fixed
-    order)."""
+    128 rows is cut along K where that brings fewer bytes into the busiest SM (the parts of a tile are a
+    thread-block cluster and are added in a fixed order)."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
     _need(out, "out", contiguous=False)
     M, K = a.shape
@@ -612,10 +593,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             raise KernelError("gemm_tc: bias size")
     epi = _skinny_epilogue(out, accumulate, swiglu)
     lib = load_library("gemm_tc")
-    scratch, counters = _tc_split_scratch(a.device) if split and 16 < M <= 128 else (None, None)
     _run("gemm_tc", lib.kp_gemm_tc_split, _ptr(a), _rows_2d(a, "a"), _ptr(w), _rows_2d(w, "w"), _ptr(bias), _ptr(out),
-         _rows_2d(out, "out"), M, N, K, epi, _ptr(scratch), ctypes.c_longlong(0 if scratch is None else scratch.numel()),
-         _ptr(counters), 0 if counters is None else counters.numel(), STREAM, tag=f" {N}x{K}",
+         _rows_2d(out, "out"), M, N, K, epi, 1 if split else 0, STREAM, tag=f" {N}x{K}",
          work=_gemm_work(M, N, K, a, w, out))
     return out
 

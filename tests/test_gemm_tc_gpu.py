@@ -45,9 +45,9 @@ def test_gemm_tc_against_plain(M, N, K):
 
 @pytest.mark.parametrize("M", [17, 40, 64, 100, 128])
 def test_gemm_tc_split_over_k(M):
-    """Few rows, a long K and few output columns: the product is cut along K, the parts are added in a fixed
-    order by the CTA that brings the last one.  Every epilogue against the plain product; twice in a row gives
-    the same bits (the order of the parts does not depend on who arrives when); the counters are left zero."""
+    """17 to 128 rows: the product is cut along K, the CTAs of a tile (a cluster) add the parts in a fixed order.
+    Every epilogue against the plain product; twice in a row gives the same bits (the order of the parts does not
+    depend on who arrives when)."""
     from kappai_b200.ops import kernels as Kn
     rng = np.random.default_rng(63)
     K, N, ff = 4096 + 64, 1000, 1024
@@ -71,8 +71,7 @@ def test_gemm_tc_split_over_k(M):
     act = Kn.gemm_tc(A, dev(wgu, DT), torch.empty((M, ff), dtype=DT, device="cuda"), None, swiglu=True)
     want = P.swiglu(gu[:, :ff], gu[:, ff:])
     assert np.all(np.abs(act.cpu().double().numpy() - want) <= 2e-2 * np.abs(want) + 2e-2)
-    _, counters = Kn._tc_split_scratch(A.device)
-    assert int(counters.abs().sum().item()) == 0 and Kn.tc_status() == 0
+    assert Kn.tc_status() == 0
 
 
 def test_gemm_tc_rows_do_not_depend_on_m():
