@@ -199,6 +199,32 @@ gemm_stream_kernel(const StreamArgs p) {
             for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) acc[w][mt][i] = 0.f;
+        // What the epilogue needs beside the sums and that is there already (the old value of an accumulated
+        // output; the conv step's position, state and taps) is fetched now, so that its trips to L2 run under
+        // the main loop instead of behind it.  (One output a thread: a tile of one m-tile and 8 columns.)
+        constexpr bool PRE = MT == 1 && !WIDE && (EPI == EPI_ACCUM_F32 || EPI == EPI_CONV_STEP);
+        float pre_c = 0.f, pre_hist[3] = {0.f, 0.f, 0.f}, pre_cw[4] = {0.f, 0.f, 0.f, 0.f};
+        bool pre_conv = false;
+        if (PRE && threadIdx.x < 128) {
+            const int l = threadIdx.x & 31, i = (threadIdx.x >> 5) & 3;
+            const int m = (l >> 2) + ((i & 2) ? 8 : 0), n = n0 + (l & 3) * 2 + (i & 1);
+            if (m < M && n < n_out) {
+                if (EPI == EPI_ACCUM_F32) pre_c = ((const float*)p.C)[(size_t)m * p.ldc + n];
+                if (EPI == EPI_CONV_STEP && p.conv_k <= 4) {
+                    pre_conv = true;
+                    const int Kc = p.conv_k;
+                    const bool fresh = p.seg_pos[m] == 0;
+                    const float* st = p.conv_state + (size_t)p.seg_slot[m] * (Kc - 1) * p.ff;
+                    const float* cw = p.conv_w + (size_t)n * Kc;
+#pragma unroll
+                    for (int k = 0; k < 3; k++)
+                        if (k < Kc - 1) pre_hist[k] = fresh ? 0.f : st[(size_t)k * p.ff + n];
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        if (k < Kc) pre_cw[k] = cw[k];
+                }
+            }
+        }
         // this warp's k-blocks: warp, warp + 8, ... (two a stage); their activations are fetched PF blocks
         // (one stage) ahead.  Fetching two stages ahead was measured and gained nothing.
         constexpr int PF = 2;
@@ -274,14 +300,22 @@ gemm_stream_kernel(const StreamArgs p) {
                 const bool fresh = p.seg_pos[m] == 0;
                 float* st = p.conv_state + (size_t)p.seg_slot[m] * (Kc - 1) * d;
                 const float bx = __fmul_rn(b, xq);
-                float hist[15];
-                for (int k = 0; k < Kc - 1; k++) hist[k] = fresh ? 0.f : st[(size_t)k * d + n];
+                float hist[15], tap[16];
+                if (pre_conv) {
+#pragma unroll
+                    for (int k = 0; k < 3; k++) hist[k] = pre_hist[k];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) tap[k] = pre_cw[k];
+                } else {
+                    for (int k = 0; k < Kc - 1; k++) hist[k] = fresh ? 0.f : st[(size_t)k * d + n];
+                    for (int k = 0; k < Kc; k++) tap[k] = cw[k];
+                }
                 float sum;
                 if (Kc == 3) {
-                    sum = __fadd_rn(__fadd_rn(__fmul_rn(hist[0], cw[0]), __fmul_rn(hist[1], cw[1])), __fmul_rn(bx, cw[2]));
+                    sum = __fadd_rn(__fadd_rn(__fmul_rn(hist[0], tap[0]), __fmul_rn(hist[1], tap[1])), __fmul_rn(bx, tap[2]));
                 } else {
-                    sum = __fmul_rn(bx, cw[Kc - 1]);
-                    for (int k = 0; k < Kc - 1; k++) sum = __fadd_rn(sum, __fmul_rn(hist[k], cw[k]));
+                    sum = __fmul_rn(bx, tap[Kc - 1]);
+                    for (int k = 0; k < Kc - 1; k++) sum = __fadd_rn(sum, __fmul_rn(hist[k], tap[k]));
                 }
                 if (p.conv_bias) sum = __fadd_rn(sum, p.conv_bias[n]);
                 ((bf16*)p.C)[o] = from_f32<bf16>(__fmul_rn(cq, sum));
@@ -300,7 +334,7 @@ gemm_stream_kernel(const StreamArgs p) {
             } else if (EPI == EPI_STORE_F32) {
                 ((float*)p.C)[o] = v;
             } else {
-                ((float*)p.C)[o] += v;
+                ((float*)p.C)[o] = (PRE ? pre_c : ((float*)p.C)[o]) + v;
             }
         }
         consumer_sync();                                                 // red is free for the next tile

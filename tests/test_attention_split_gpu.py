@@ -113,3 +113,22 @@ def test_split_refuses_large_group_ratio():
     with pytest.raises(Kn.KernelError, match="not supported"):
         Kn.attention_split(q, torch.zeros((1, 2, 1, 16, 16), device="cuda"), i32([[0]]), i32([0]), i32([0]),
                            torch.empty_like(q), torch.zeros(100000, device="cuda"), 1, 1.0, None, 16, 16, 1, 16)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,hd,page", [(32, 8, 64, 64), (5, 1, 48, 32), (8, 2, 128, 16)])
+def test_both_merge_kernels_give_the_same_bits(dtype, H, G, hd, page):
+    """Rows of at most 64 chunks are merged by a warp each, longer ones by a CTA each; which of the two runs is
+    decided by the width of the grid (the largest position of the batch), so a row must get the same bits from
+    both: the same rows once with the chunks they need and once in a grid of 70 chunks."""
+    rng = np.random.default_rng(44)
+    seq_lens = [1, 300, 2000, 513]
+    cache, bt, ks, vs = paged_setup(rng, seq_lens, page, G, hd, dtype)
+    scale = 1.0 / math.sqrt(hd)
+    q_rows = rt(rng.standard_normal((len(seq_lens), H * hd)), dtype)
+    pos = [L - 1 for L in seq_lens]
+    row_seg = list(range(len(seq_lens)))
+    by_warp = run_split(q_rows, cache, bt, row_seg, pos, scale, None, page, H, G, hd, dtype)
+    by_cta = run_split(q_rows, cache, bt, row_seg, pos, scale, None, page, H, G, hd, dtype, n_chunks=70)
+    assert torch.equal(by_warp, by_cta)
+    assert torch.isfinite(by_warp.float()).all()
