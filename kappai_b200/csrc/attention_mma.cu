@@ -50,6 +50,11 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// `bytes` (a multiple of 16, both addresses 16-byte aligned) from global to shared memory; completes on `bar`
+__device__ __forceinline__ void kp_bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(kp_smem_u32(dst)), "l"(src), "r"(bytes), "r"(kp_smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -292,6 +297,256 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __res
     }
 }
 
+// ------------------------------------------------------------------ decode, persistent (head size 64, chunks of 256 keys)
+// The same chunk pass as attn_split_mma_kernel<64, 4, true>, built so that the cache streams without a break:
+// one persistent CTA an SM; a producer warp walks the CTA's share of the (row, kv head, chunk) items, looks up
+// the pages and issues the TMA loads of an item's K and V tiles (and a bulk copy of its Q rows) into a ring of
+// AR_STAGES stages; as many groups of four consumer warps take the items in turn (item k: stage and group
+// k % AR_STAGES), each warp one 64-key tile as above, and write the chunk's partial result in the same format.
+// (One CTA an item spends most of its life on the chain position -> block table -> first byte, and only three
+// fit an SM: 2.9 TB/s at 8 rows, 4.2 at 64.)  Every wait is bounded; a wait that gives up sets the status word.
+#define AR_GROUPS 3                          // groups of consumer warps = stages of the ring: group g reads stage g
+#define AR_STAGES AR_GROUPS
+#define AR_NW 4
+#define AR_THREADS ((AR_GROUPS * AR_NW + 1) * 32)
+#define AR_CHUNK (AR_NW * AM_TILE)
+
+struct ArMeta { int row, kvh, chunk, k_lo, k_hi, pad0, pad1, pad2; };
+
+template <int HD>
+__host__ __device__ constexpr size_t ar_stage_bytes() { return (size_t)2 * AR_NW * AM_TILE * HD * 2 + 1024; }
+template <int HD>
+static size_t ar_smem_bytes() {
+    return 1024 + AR_STAGES * ar_stage_bytes<HD>() + AR_STAGES * sizeof(ArMeta) + 2 * AR_STAGES * 8 +
+           AR_GROUPS * sizeof(float) * (AR_NW * AM_RMAX * HD + 2 * AR_NW * AM_RMAX) + 16;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(AR_THREADS)
+attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __restrict__ q, int ldq,
+                       const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_seg,
+                       const int* __restrict__ positions, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                       int n_chunks, float scale, int window, int page_size, int H, int G, int n_rows) {
+    kp_pdl_begin_early_if(n_rows > 1);
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    constexpr size_t STAGE = ar_stage_bytes<HD>();
+    constexpr size_t KV = (size_t)AR_NW * AM_TILE * HD * 2;                // bytes of a stage's K tiles (and of its V tiles)
+    ArMeta* metas = reinterpret_cast<ArMeta*>(base + AR_STAGES * STAGE);
+    uint64_t* full = reinterpret_cast<uint64_t*>(metas + AR_STAGES);
+    uint64_t* empty = full + AR_STAGES;
+    float* scratch = reinterpret_cast<float*>(empty + AR_STAGES);       // [group]: wO [NW][RMAX][HD], wm, wl [NW][RMAX]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int R = H / G;
+
+    if (tid == 0) {
+        for (int s = 0; s < AR_STAGES; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], AR_NW); }
+        kp_mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (warp == AR_GROUPS * AR_NW) {
+        // ---- producer
+        const int n_items = n_rows * G * n_chunks;
+        const int box = min(page_size, AM_TILE), n_boxes = AR_CHUNK / box;   // keys a box; at most 32 boxes (pages of 8 keys)
+        int k = 0;
+        bool alive = true;
+        for (int it0 = blockIdx.x; it0 < n_items && alive; it0 += 32 * gridDim.x) {
+            // 32 candidates at a time, one a lane: which of them have keys to read
+            const int it = it0 + lane * gridDim.x;
+            int c_row = 0, c_kvh = 0, c_chunk = 0, c_lo = 0, c_hi = -1, c_seg = 0;
+            bool valid = false;
+            if (it < n_items) {
+                // chunk by chunk, so that the chunks that exist (the first ones, or a window's band) spread evenly
+                // over the CTAs whatever the numbers of chunks and CTAs
+                c_chunk = it / (n_rows * G);
+                const int rest = it - c_chunk * (n_rows * G);
+                c_kvh = rest % G;
+                c_row = rest / G;
+                const int pos = positions[c_row];
+                c_lo = window > 0 ? max(0, pos - window + 1) : 0;
+                c_hi = pos;
+                const int c0 = c_chunk * AR_CHUNK;
+                valid = !(c0 > c_hi || c0 + AR_CHUNK - 1 < c_lo);
+                if (valid) c_seg = row_seg[c_row];
+            }
+            unsigned todo = __ballot_sync(0xffffffffu, valid);
+            while (todo && alive) {
+                const int src = __ffs(todo) - 1;
+                todo &= todo - 1;
+                const int row = __shfl_sync(0xffffffffu, c_row, src), kvh = __shfl_sync(0xffffffffu, c_kvh, src);
+                const int chunk = __shfl_sync(0xffffffffu, c_chunk, src), seg = __shfl_sync(0xffffffffu, c_seg, src);
+                const int k_lo = __shfl_sync(0xffffffffu, c_lo, src), k_hi = __shfl_sync(0xffffffffu, c_hi, src);
+                const int c0 = chunk * AR_CHUNK;
+                // lane b: box b of the chunk
+                const int key0 = c0 + lane * box;
+                const bool need = lane < n_boxes && key0 <= k_hi && key0 + box - 1 >= k_lo;
+                const int page = need ? block_table[(size_t)seg * max_blocks + key0 / page_size] : 0;
+                const unsigned boxes = __ballot_sync(0xffffffffu, need);
+                const int s = k % AR_STAGES;
+                uint64_t* fbar = &full[s];
+                unsigned char* st = base + (size_t)s * STAGE;
+                int ok = 1;
+                if (lane == 0) {
+                    ok = kp_mbar_wait_bounded(&empty[s], ((k / AR_STAGES) & 1) ^ 1) ? 1 : 0;
+                    if (ok) {
+                        ArMeta m;
+                        m.row = row; m.kvh = kvh; m.chunk = chunk; m.k_lo = k_lo; m.k_hi = k_hi; m.pad0 = m.pad1 = m.pad2 = 0;
+                        metas[s] = m;
+                        const uint32_t q_bytes = (uint32_t)R * HD * 2;
+                        kp_mbar_expect_tx(fbar, (uint32_t)__popc(boxes) * 2 * box * HD * 2 + q_bytes);
+                        kp_bulk_g2s(st + 2 * KV, q + (size_t)row * ldq + (size_t)kvh * R * HD, q_bytes, fbar);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+                if (lane == 0) KP_TRACE_MARK_LANE(8);
+                if (need) {
+                    const int row_k = ((page * 2) * G + kvh) * page_size + key0 % page_size;       // row of the 2-D view
+                    const int row_v = row_k + G * page_size;
+                    const int in_chunk = key0 - c0;
+                    const size_t off = ((size_t)(in_chunk / AM_TILE) * AM_TILE * HD + (size_t)(in_chunk % AM_TILE) * 64) * 2;
+                    kp_tma_load_2d(st + off, &tmC, 0, row_k, fbar);
+                    kp_tma_load_2d(st + KV + off, &tmC, 0, row_v, fbar);
+                }
+                k++;
+            }
+        }
+        // no more items: a mark for each group
+        for (int e = 0; e < AR_GROUPS && alive; e++, k++) {
+            const int s = k % AR_STAGES;
+            if (lane == 0) {
+                if (kp_mbar_wait_bounded(&empty[s], ((k / AR_STAGES) & 1) ^ 1)) {
+                    metas[s].row = -1;
+                    kp_mbar_arrive(&full[s]);
+                } else {
+                    alive = false;
+                }
+            }
+            alive = __shfl_sync(0xffffffffu, alive ? 1 : 0, 0) != 0;
+        }
+        if (!alive && lane == 0) atomicExch(&g_attn_status, 1);
+        return;
+    }
+
+    // ---- consumers: group grp, warp wg of it
+    const int grp = warp / AR_NW, wg = warp % AR_NW, g = lane >> 2, t = lane & 3;
+    float* wO = scratch + (size_t)grp * (AR_NW * AM_RMAX * HD + 2 * AR_NW * AM_RMAX);
+    float* wm = wO + AR_NW * AM_RMAX * HD;
+    float* wl = wm + AR_NW * AM_RMAX;
+    const int gtid = tid - grp * AR_NW * 32;                          // thread of the group
+    auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(AR_NW * 32) : "memory"); };
+    for (int k = grp;; k += AR_GROUPS) {
+        const int s = k % AR_STAGES;
+        if (!kp_mbar_wait_bounded(&full[s], (k / AR_STAGES) & 1)) {
+            if (lane == 0) atomicExch(&g_attn_status, 1);
+            break;
+        }
+        const ArMeta me = metas[s];
+        if (me.row < 0) break;
+        if (wg == 0 && lane == 0 && grp < 2) KP_TRACE_MARK_LANE(9 + grp * 2);
+        unsigned char* st = base + (size_t)s * STAGE;
+        bf16* Kt = reinterpret_cast<bf16*>(st) + (size_t)wg * AM_TILE * HD;
+        bf16* Vt = reinterpret_cast<bf16*>(st + KV) + (size_t)wg * AM_TILE * HD;
+        const bf16* Qs = reinterpret_cast<const bf16*>(st + 2 * KV);
+        const int k_lo = me.k_lo, k_hi = me.k_hi;
+        const int t0 = me.chunk * AR_CHUNK + wg * AM_TILE;            // first key of this warp's tile
+        uint32_t qf[HD / 16][4];
+        {
+            const bf16* qr = Qs + (size_t)min(g, R - 1) * HD;
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ks++) {
+                uint32_t lo = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 2 * t);
+                uint32_t hi = *reinterpret_cast<const uint32_t*>(qr + ks * 16 + 8 + 2 * t);
+                if (g >= R) lo = hi = 0;
+                qf[ks][0] = lo; qf[ks][1] = 0; qf[ks][2] = hi; qf[ks][3] = 0;
+            }
+        }
+        // V rows of keys that this row does not read hold whatever was there: zero them (P is 0 there, but
+        // 0 * NaN is not); K rows need nothing, their scores are masked
+        if (t0 < k_lo || t0 + AM_TILE - 1 > k_hi) {
+            for (int idx = lane; idx < AM_TILE * (HD / 8); idx += 32) {
+                const int r = idx / (HD / 8), c = idx % (HD / 8);
+                if (t0 + r < k_lo || t0 + r > k_hi) *reinterpret_cast<uint4*>(tile_chunk<HD>(Vt, r, c)) = make_uint4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+        float sc[8][4];
+        qk_tile<HD>(sc, qf, Kt, lane);
+        float m = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int key = t0 + nt * 8 + 2 * t + i;
+                const float v = (key >= k_lo && key <= k_hi) ? sc[nt][i] * scale : -INFINITY;
+                sc[nt][i] = v;
+                m = fmaxf(m, v);
+            }
+        }
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+        m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+        float l = 0.f;
+        uint32_t pf[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; nt++) {
+            const float p0 = m == -INFINITY ? 0.f : expf(sc[nt][0] - m), p1 = m == -INFINITY ? 0.f : expf(sc[nt][1] - m);
+            // the sum runs over the values as they enter the product (rounded to bfloat16)
+            const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+            l += __low2float(pb) + __high2float(pb);
+            pf[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&pb);
+            pf[nt >> 1][(nt & 1) * 2 + 1] = 0;
+        }
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        float o[HD / 8][4];
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; dn++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) o[dn][i] = 0.f;
+        pv_tile<HD>(o, pf, Vt, lane);
+        __syncwarp();
+        if (lane == 0) kp_mbar_arrive(&empty[s]);                     // this warp has read its tiles (and Q, and the item)
+
+        if (g < R) {
+#pragma unroll
+            for (int dn = 0; dn < HD / 8; dn++) {
+                wO[((size_t)wg * AM_RMAX + g) * HD + dn * 8 + 2 * t] = o[dn][0];
+                wO[((size_t)wg * AM_RMAX + g) * HD + dn * 8 + 2 * t + 1] = o[dn][1];
+            }
+            if (t == 0) { wm[wg * AM_RMAX + g] = m; wl[wg * AM_RMAX + g] = l; }
+        }
+        group_sync();
+        // the warps' partial results, combined in warp order
+        for (int e = gtid; e < R * HD; e += AR_NW * 32) {
+            const int r = e / HD, d = e % HD;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < AR_NW; w++) M = fmaxf(M, wm[w * AM_RMAX + r]);
+            float acc = 0.f;
+#pragma unroll
+            for (int w = 0; w < AR_NW; w++) {
+                const float mw = wm[w * AM_RMAX + r];
+                if (mw != -INFINITY) acc = fmaf(wO[((size_t)w * AM_RMAX + r) * HD + d], expf(mw - M), acc);
+            }
+            part_acc[(((size_t)me.row * H + me.kvh * R + r) * n_chunks + me.chunk) * HD + d] = acc;
+        }
+        if (gtid < R) {
+            float M = -INFINITY, L = 0.f;
+            for (int w = 0; w < AR_NW; w++) M = fmaxf(M, wm[w * AM_RMAX + gtid]);
+            for (int w = 0; w < AR_NW; w++) {
+                const float mw = wm[w * AM_RMAX + gtid];
+                if (mw != -INFINITY) L = fmaf(wl[w * AM_RMAX + gtid], expf(mw - M), L);
+            }
+            float* ml = part_ml + (((size_t)me.row * H + me.kvh * R + gtid) * n_chunks + me.chunk) * 2;
+            ml[0] = M;
+            ml[1] = L;
+        }
+        if (wg == 0 && lane == 0 && grp < 2) KP_TRACE_MARK_LANE(10 + grp * 2);
+        group_sync();                                                 // the group's scratch is free for its next item
+    }
+}
+
 // ------------------------------------------------------------------ prefill (segments of many rows)
 // One CTA: 64 consecutive rows (tile `qt` of segment `seg`) of one head.  tile_seg / tile_q0 list the tiles.
 template <int HD>
@@ -423,6 +678,19 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restr
     }
 }
 
+#ifndef USE_RING
+#define USE_RING 1
+#endif
+static int am_n_sm() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
 template <int HD, int NW>
 static int launch_split(const void* q, int ldq, const void* cache, long long n_pages, const int* block_table,
                         int max_blocks, const int* row_seg, const int* positions, float* part_acc, float* part_ml,
@@ -434,6 +702,24 @@ static int launch_split(const void* q, int ldq, const void* cache, long long n_p
                      !((uintptr_t)cache & 15) &&
                      kp_make_map_bf16_2d(&tm, cache, (unsigned long long)n_pages * 2 * G * page_size, HD, HD, 64,
                                          page_size < AM_TILE ? page_size : AM_TILE) == 0;
+    if constexpr (HD == 64 && NW == AR_NW) {
+        // the persistent form where its Q copy can run: 16-byte aligned rows of Q, whole 16 bytes of Q a kv head
+        if (USE_RING && tma && !((uintptr_t)q & 15) && (ldq % 8) == 0 && ((H / G) * HD * 2) % 16 == 0) {
+            const size_t rs = ar_smem_bytes<HD>();
+            static bool ready = false;
+            if (!ready) {
+                cudaError_t e = cudaFuncSetAttribute(attn_split_ring_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rs);
+                if (e != cudaSuccess) return (int)e;
+                ready = true;
+            }
+            const long long items = (long long)n * G * n_chunks;
+            const int sms = am_n_sm();
+            kp_launch_pdl(attn_split_ring_kernel<HD>, dim3((unsigned)(items < sms ? items : sms)), dim3(AR_THREADS), rs, s, tm,
+                          (const bf16*)q, ldq, block_table, max_blocks, row_seg, positions, part_acc, part_ml, n_chunks, scale,
+                          window, page_size, H, G, n);
+            return kp_launch_status();
+        }
+    }
     auto kern = tma ? attn_split_mma_kernel<HD, NW, true> : attn_split_mma_kernel<HD, NW, false>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
