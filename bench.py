@@ -407,6 +407,76 @@ def run_probe(model_dir, a, rng) -> int:
     return 0
 
 
+def run_timeline(model_dir, a, rng) -> int:
+    """The kernels of one captured decode step on the device's own clock: when each one's wait on the kernel
+    before it was over, how long until the next one's was, and how early it had become resident (see
+    kappai_b200/ops/timeline.py).  Under the trace marks a step runs 10 to 15 % slower."""
+    from kappai_b200.ops import timeline
+    timeline.enable()
+    import torch
+    from kappai_b200 import ModelRunner, StepEntry
+    from kappai_b200.ops import kernels as K
+    from kappai_b200.sampling.sampler import argmax
+
+    B, T = a.batch, a.prompt_len
+    runner = ModelRunner(model_dir, dtype="bfloat16", max_tokens=B * CONTEXT, max_requests=B, page_size=64,
+                         max_model_len=CONTEXT)
+    V = runner.vocab_size
+    tok = None
+    for i in range(B):
+        t = argmax(runner.step([StepEntry(i, rng.integers(0, V, T).tolist(), [T - 1])]))
+        tok = t if tok is None else torch.cat([tok, t])
+    entries = [StepEntry(i, [0], [0]) for i in range(B)]
+    names = None
+    for _ in range(6):                                    # the step that is captured logs the names of its launches
+        K.LAUNCH_LOG[0] = []
+        before = len(runner.graphs.graphs)
+        logits = runner.step(entries, device_tokens=tok)
+        if len(runner.graphs.graphs) > before:
+            names = list(K.LAUNCH_LOG[0])
+        K.LAUNCH_LOG[0] = None
+        tok = argmax(logits)
+    K.LAUNCH_LOG[0] = None
+    torch.cuda.synchronize()
+    timeline.records()                                    # (clears)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        tok = argmax(runner.step(entries, device_tokens=tok))
+    e1.record()
+    torch.cuda.synchronize()
+    ks = timeline.kernels(timeline.records())
+    # the middle one of the three steps: from its first kernel (the embedding) to the next step's
+    per_step = len(ks) // 3
+    step = ks[per_step:2 * per_step + 1]
+    # the names of the captured step's launches, then the sampler's; only if they account for every launch seen
+    n_sampling = sum(1 for k in step[:-1] if k["lib"] == "sampling")
+    in_graph = per_step - n_sampling
+    print(f"launches: {len(ks)} in three steps, {n_sampling} of the sampler a step, {len(names or [])} names logged",
+          file=sys.stderr)
+    if names is not None and in_graph > 0 and len(names) >= in_graph:
+        names = names[-in_graph:] + ["argmax"] * n_sampling      # (the capturing call runs the step more than once: the last run)
+    else:
+        names = None
+    print(f"decode step, batch {B}, context {T + 7}, traced build: {e0.elapsed_time(e1) / 3 * 1e3:.1f} us a step, "
+          f"{per_step} launches")
+    print(timeline.table(step, names))
+    by = {}
+    for i, k in enumerate(step[:-1]):
+        w, nxt = k["waited_first"], step[i + 1]["waited_first"]
+        if w is None or nxt is None:
+            continue
+        name = (names[i] if names and i < len(names) else k["lib"])
+        got = by.setdefault(name, [0, 0.0])
+        got[0] += 1
+        got[1] += nxt - w
+    total = sum(v[1] for v in by.values())
+    print(f"\nby kernel (time on the step's critical path; {total:.1f} us in all):")
+    for name, (n, us) in sorted(by.items(), key=lambda kv: -kv[1][1]):
+        print(f"  {name:44s} {n:4d} x {us / n:7.2f} us = {us:8.1f} us  {100 * us / total:5.1f} %")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -415,7 +485,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (0 = all)")
-    ap.add_argument("--probe", choices=["decode", "prefill"], default=None,
+    ap.add_argument("--probe", choices=["decode", "prefill", "timeline"], default=None,
                     help="run a few eager steps (no CUDA graph) of one kind and exit: the small case that a "
                          "profiler is pointed at")
     ap.add_argument("--workload", choices=["long", "many"], default=None,
@@ -449,6 +519,8 @@ def main() -> int:
     n_layers = a.layers or LFM2_1P2B["num_hidden_layers"]
     model_dir, cfg = model_folder(LFM2_1P2B, SEED, n_layers)
     rng = np.random.default_rng(SEED)
+    if a.probe == "timeline":
+        return run_timeline(model_dir, a, rng)
     if a.probe:
         return run_probe(model_dir, a, rng)
     runner = ModelRunner(model_dir, dtype="bfloat16", max_tokens=64 * CONTEXT, max_requests=64, page_size=64,

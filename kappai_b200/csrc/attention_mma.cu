@@ -400,7 +400,6 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { alive = false; break; }
-                if (lane == 0) KP_TRACE_MARK_LANE(8);
                 if (need) {
                     const int row_k = ((page * 2) * G + kvh) * page_size + key0 % page_size;       // row of the 2-D view
                     const int row_v = row_k + G * page_size;
@@ -444,7 +443,6 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
         }
         const ArMeta me = metas[s];
         if (me.row < 0) break;
-        if (wg == 0 && lane == 0 && grp < 2) KP_TRACE_MARK_LANE(9 + grp * 2);
         unsigned char* st = base + (size_t)s * STAGE;
         bf16* Kt = reinterpret_cast<bf16*>(st) + (size_t)wg * AM_TILE * HD;
         bf16* Vt = reinterpret_cast<bf16*>(st + KV) + (size_t)wg * AM_TILE * HD;
@@ -542,7 +540,6 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
             ml[0] = M;
             ml[1] = L;
         }
-        if (wg == 0 && lane == 0 && grp < 2) KP_TRACE_MARK_LANE(10 + grp * 2);
         group_sync();                                                 // the group's scratch is free for its next item
     }
 }

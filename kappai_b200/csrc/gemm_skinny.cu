@@ -90,7 +90,9 @@ gemm_skinny_kernel(const SkinnyArgs p) {
     };
     // weights of the first stage: independent of everything that ran before
     load_stage(wa, warp);
+    KP_TRACE_MARK(0);
     pdl_wait();                                               // now the activations are there
+    KP_TRACE_MARK(1);
     pdl_launch_dependents();
 
     int r0[MT], r1[MT];

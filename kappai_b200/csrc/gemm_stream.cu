@@ -40,17 +40,8 @@
 #define ST_THREADS ((ST_CONSUMERS + 1) * 32) // plus the producer warp
 #define ST_COLS 512                          // columns of a stage: 16 k-blocks of 32, 2 a consumer warp
 #define ST_ROW_BYTES (ST_COLS * 2 + 64)      // a stage row in shared memory: 1 KB of data, pitch = 64 mod 128
-#ifndef ST_RING_KB
-#define ST_RING_KB 64
-#endif
-#ifndef ST_RING_FEW_KB
-#define ST_RING_FEW_KB 88
-#endif
-#ifndef ST_PER_SM_MANY
-#define ST_PER_SM_MANY 3
-#endif
-#define ST_RING_BYTES (ST_RING_KB * 1024)            // the ring with three CTAs an SM: 7 stages of 8 rows, 3 of 2 x 8
-#define ST_RING_BYTES_FEW (ST_RING_FEW_KB * 1024)        // with two CTAs an SM (products with few tiles): 10 stages of 8 rows
+#define ST_RING_BYTES (64 * 1024)            // the ring with three CTAs an SM: 7 stages of 8 rows, 3 of 2 x 8
+#define ST_RING_BYTES_FEW (88 * 1024)        // with two CTAs an SM (products with few tiles): 10 stages of 8 rows
 
 KP_STATUS_WORD(g_stream_status, stream)          // 0 ok; 1: a bounded wait gave up
 
@@ -262,10 +253,8 @@ gemm_stream_kernel(const StreamArgs p) {
         };
         for (int c = 0; c < n_chunks; c += PF / 2) {
             run_stage(c, std::integral_constant<int, 0>{});
-            if (c == 0 && tile == blockIdx.x) KP_TRACE_MARK(4);
             if (PF == 4 && c + 1 < n_chunks) run_stage(c + 1, std::integral_constant<int, (PF == 4 ? 2 : 0)>{});
         }
-        if (tile == blockIdx.x) KP_TRACE_MARK(5);
         // the tile's result: the warps' partial sums, added in warp order
 #pragma unroll
         for (int w = 0; w < NW; w++)
@@ -384,7 +373,7 @@ static int launch_epi(StreamArgs a, int epi, cudaStream_t s) {
     // many tiles (6144 x 2048: 6.9 us against 8.1 with 53 KB); a product with at most two tiles an SM (2048
     // rows) does better with two CTAs an SM and more of its long rows in flight (2048 x 5632: 8.3 against 10.3).
     const bool few = n_tiles <= 2 * n_sm();
-    const int per_sm = few ? 2 : ST_PER_SM_MANY;
+    const int per_sm = few ? 2 : 3;
     const int ring = few ? ST_RING_BYTES_FEW : ST_RING_BYTES;
     a.n_stages = ring / (NW * 8 * ST_ROW_BYTES);
     if (a.n_stages < 2) a.n_stages = 2;

@@ -279,7 +279,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
             if (!kp_mbar_wait_bounded(&acc_full[b2], (ti >> 1) & 1) || *abort_flag) { ok = false; break; }
             kp_tc_fence_after();
-            if (threadIdx.x == 64 && ti == 0) KP_TRACE_MARK_LANE(4);
             const int m = m0 + q * 32 + lane;
             const uint32_t lane_base = tmem_base + (uint32_t)(b2 * BN) + ((uint32_t)(q * 32) << 16);
             if (S == 1) {
@@ -324,7 +323,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             kp_tc_fence_before();
             __syncwarp();
             if (lane == 0) kp_mbar_arrive(&acc_empty[b2]);
-            if (threadIdx.x == 64) KP_TRACE_MARK_LANE(5);
             parts_ok = true;
         }
         if (!ok && lane == 0) atomicExch(&g_tc_status, 1);
@@ -338,7 +336,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // epilogue.  Every thread of every CTA comes here, also after a wait that gave up, so the cluster's
         // barriers always complete; no CTA leaves before the others have read its sums.
         kp_cluster_sync();
-        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(7);
         if (warp >= 2 && parts_ok) {
             const int tile = blockIdx.x / S, part = blockIdx.x - tile * S;
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
@@ -388,7 +385,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
             }
         }
-        if (threadIdx.x == 64) KP_TRACE_MARK_LANE(6);
         kp_cluster_sync();
     }
     if (threadIdx.x == 64) KP_TRACE_MARK_LANE(2);

@@ -188,6 +188,9 @@ def compile_library(name: str, extra_flags: Optional[List[str]] = None, verbose:
                 pass
 
 
+TIMELINE = [False]      # ops.timeline.enable(): every library loaded from now on is its build with the trace marks
+
+
 def load_library(name: str, variant: str = "", extra_flags: Optional[List[str]] = None) -> ctypes.CDLL:
     """The loaded library ``name``; compiled first if need be."""
     key = f"{name}.{variant}" if variant else name
@@ -197,7 +200,10 @@ def load_library(name: str, variant: str = "", extra_flags: Optional[List[str]] 
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
-            path = compile_library(name, extra_flags, variant=variant)
+            if TIMELINE[0] and not variant and name in LIBRARIES:
+                path = compile_library(name, [f"-DKP_TRACE={LIBRARIES.index(name) + 1}"], variant="timeline")
+            else:
+                path = compile_library(name, extra_flags, variant=variant)
             try:
                 lib = ctypes.CDLL(path)
             except OSError as e:
@@ -208,6 +214,11 @@ def load_library(name: str, variant: str = "", extra_flags: Optional[List[str]] 
 
 def is_loaded(name: str) -> bool:
     return name in _loaded
+
+
+def loaded_libraries() -> dict:
+    """Name (``name`` or ``name.variant``) -> loaded library."""
+    return dict(_loaded)
 
 
 def build_all(verbose: bool = True, jobs: int = 4) -> List[str]:

@@ -131,6 +131,8 @@ def _run(what: str, fn, *args, tag: str = "", work=None) -> None:
     timer = TIMER[0]
     if timer is None:
         _check(fn(*[_stream() if a is STREAM else a for a in args]), what)
+        if LAUNCH_LOG[0] is not None and tag:
+            LAUNCH_LOG[0][-1] += tag
         return
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -143,9 +145,14 @@ def _gemm_work(M: int, N: int, K: int, a: torch.Tensor, w: torch.Tensor, out: to
     return (2 * M * N * K, M * K * a.element_size() + N * K * w.element_size() + out.numel() * out.element_size())
 
 
+LAUNCH_LOG = [None]        # a list: every launch appends its name (bench.py --probe timeline names a step's kernels by it)
+
+
 def _check(status: int, what: str) -> None:
     LAUNCHES[0] += 1
     LAUNCHES_BY[what] = LAUNCHES_BY.get(what, 0) + 1
+    if LAUNCH_LOG[0] is not None:
+        LAUNCH_LOG[0].append(what)
     if status != 0:
         if status == -95:
             raise KernelError(f"{what}: size not supported by this kernel")
@@ -551,20 +558,21 @@ def skinny_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
 USE_TC = True              # bfloat16 products of more than 64 rows (and some of fewer) run on tcgen05 tensor cores
 
 
+TC_HEAD_FROM_M = 2         # rows from which a 65536-row head goes to the tcgen05 kernel (measured: one row ties)
 TC_SPLIT_FROM_M = 17       # rows from which every product goes to the tcgen05 kernel (cut along K where that pays)
 
 
 def tc_pays_for_few_rows(M: int, N: int, swiglu: bool) -> bool:
     """Few-row products that the tcgen05 kernel runs faster than the weight-streaming
-    kernels (measured on B200, K = 2048): the 65536-row head from 8 rows on (46 us at
-    every M against 48 us at 8 rows and 199 us at 64), and wide products from 32 rows
-    on (6144 rows: 13 us at every M against 17 us at 32 rows and 28 us at 64).  Narrow
-    products (2048 rows: few tiles) stay with the streaming kernels at every M <= 64."""
+    kernels (measured on B200, K = 2048, inside a decode step): the 65536-row head from
+    2 rows on (a step of 2 rows 638 -> 602 us, of 4 rows 661 -> 624; one row ties), every
+    product from 17 rows on (there the kernel cuts the product along K: a step of 64 rows
+    1600 -> 1320 us), and below that wide products from 32 rows on."""
     if M >= TC_SPLIT_FROM_M:
         return True
     if swiglu:
         return N >= 8192 and M >= 32        # gate/up 11264 x 2048: 19.9 us against 22.9 at 32 rows, 19.8 against 32.1 at 64
-    return (N >= 32768 and M >= 8) or (N >= 4096 and M >= 32)
+    return (N >= 32768 and M >= TC_HEAD_FROM_M) or (N >= 4096 and M >= 32)
 
 
 def tc_ok(a: torch.Tensor, w: torch.Tensor) -> bool:
