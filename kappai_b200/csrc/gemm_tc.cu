@@ -176,6 +176,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     // set-up that depends on no earlier kernel comes before the wait on it
     if (threadIdx.x == 0) {
+        // (the tensor maps are fetched now: the first TMA load through a map that has not been used waits for it)
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmW)) : "memory");
         for (int s = 0; s < STAGES; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], 1); }
         for (int b2 = 0; b2 < 2; b2++) { kp_mbar_init(&acc_full[b2], 1); kp_mbar_init(&acc_empty[b2], 4 * TC_EPI_PER_Q); }
         *abort_flag = 0;
@@ -572,7 +575,10 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
                 const int kbs = (n_kb + sp - 1) / sp;
                 if (sp > 1 && (n_kb + kbs - 1) / kbs != sp) continue;            // a part would be empty
                 long long cost = (sp == 1 ? rounds * n_kb : kbs) * (long long)(TC_BK * 2) * (w + a.a_rows);
-                if (sp > 1) cost += TC_SPLIT_COST_KB * 1024;
+                if (sp > 1) {
+                    // the sums that a CTA reads from the others come in over the same port
+                    cost += TC_SPLIT_COST_KB * 1024 + (long long)M * w * 4 * (sp - 1) / sp;
+                }
                 if (best < 0 || cost < best) { best = cost; best_bn = w; best_sp = sp; }
             }
         }
