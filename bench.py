@@ -439,11 +439,8 @@ def run_timeline(model_dir, a, rng) -> int:
     K.LAUNCH_LOG[0] = None
     torch.cuda.synchronize()
     timeline.records()                                    # (clears)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
     for _ in range(3):
         tok = argmax(runner.step(entries, device_tokens=tok))
-    e1.record()
     torch.cuda.synchronize()
     ks = timeline.kernels(timeline.records())
     # the middle one of the three steps: from its first kernel (the embedding) to the next step's
@@ -458,8 +455,8 @@ def run_timeline(model_dir, a, rng) -> int:
         names = names[-in_graph:] + ["argmax"] * n_sampling      # (the capturing call runs the step more than once: the last run)
     else:
         names = None
-    print(f"decode step, batch {B}, context {T + 7}, traced build: {e0.elapsed_time(e1) / 3 * 1e3:.1f} us a step, "
-          f"{per_step} launches")
+    span = step[-1]["waited_first"] - step[0]["waited_first"]     # from this step's first kernel to the next step's
+    print(f"decode step, batch {B}, context {T + 7}, traced build: {span:.1f} us a step, {per_step} launches")
     print(timeline.table(step, names))
     by = {}
     for i, k in enumerate(step[:-1]):
