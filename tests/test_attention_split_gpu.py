@@ -28,7 +28,10 @@ def run_split(q_rows, cache, bt, row_seg, pos, scale, window, page, H, G, hd, dt
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,hd,page,window", [
     (4, 2, 16, 16, None), (5, 1, 48, 32, None), (32, 8, 64, 64, None), (8, 2, 128, 16, 300), (2, 2, 256, 8, None),
-    (8, 1, 32, 64, None), (6, 3, 80, 128, 17)])
+    (8, 1, 32, 64, None), (6, 3, 80, 128, 17),
+    # head size 64 in bfloat16 takes the persistent kernel: pages of 8 keys (32 boxes a chunk) to 128 (half a box a
+    # tile), one to eight heads a kv head, windows that cut chunks and tiles
+    (8, 8, 64, 16, None), (16, 2, 64, 32, 100), (4, 2, 64, 128, None), (6, 2, 64, 8, 37), (8, 4, 64, 64, 300)])
 def test_split_matches_whole_sequence_attention(dtype, H, G, hd, page, window):
     rng = np.random.default_rng(40)
     seq_lens = [1, 255, 256, 257, 700, 513]

@@ -23,7 +23,10 @@ def _no_timeouts():
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 8, 8), (129, 130, 72), (300, 331, 120), (2048, 2048, 2048),
                                    (257, 6144, 2048), (130, 2048, 5632), (1000, 96, 200), (512, 1000, 4096),
                                    # few rows: short A boxes, and tiles of 64 columns while W has few rows
-                                   (1, 200, 72), (8, 6144, 2048), (17, 2048, 5632), (64, 331, 120), (100, 20000, 256)])
+                                   (1, 200, 72), (8, 6144, 2048), (17, 2048, 5632), (64, 331, 120), (100, 20000, 256),
+                                   # 17 to 128 rows, the products of a decode step: cut along K, clusters of 3 to 8 CTAs
+                                   (64, 2048, 5632), (24, 6144, 2048), (128, 2048, 2048), (96, 3072, 2048), (33, 1024, 4608),
+                                   (48, 2560, 10240), (17, 9216, 1024)])
 def test_gemm_tc_against_plain(M, N, K):
     from kappai_b200.ops import kernels as Kn
     rng = np.random.default_rng(60)
