@@ -193,6 +193,29 @@ static inline int grid_for(size_t total, int block) {
     return (int)g;
 }
 
+// The tables of a captured decode step, brought to the device by a kernel instead of a copy engine: `src` is the
+// step's staging buffer in pinned host memory (the device reads it over the bus), `dst` the static buffer that the
+// graph's kernels read; and, in the same launch, the step's token ids from where the sampler left them.  (A
+// 2 KB cudaMemcpyAsync between two graph launches costs about 10 us of stream time, this about 3.)
+__global__ void step_tables_kernel(const int4* src, int4* __restrict__ dst, int n4, const int* __restrict__ tok_src,
+                                   int tok_off, int n_tok) {
+    kp_pdl_begin();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    // with tokens given, their place in the tables (words tok_off ..., whole int4s) is theirs alone
+    const bool toks = tok_src != nullptr && i * 4 >= tok_off && i * 4 < tok_off + (n_tok + 3) / 4 * 4;
+    if (i < n4 && !toks) {
+        int4 v;                                   // (a volatile load: host memory, rewritten between launches)
+        asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src + i));
+        dst[i] = v;
+    }
+    if (toks) {
+        int* d = reinterpret_cast<int*>(dst) + i * 4;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (i * 4 + j - tok_off < n_tok) d[j] = tok_src[i * 4 + j - tok_off];
+    }
+}
+
 // The status words of a step's kernels brought together: out[0] = OR of the words at the given device
 // addresses.  Launched behind a step; its one word travels to the host with the step's sampled tokens, so the
 // host learns without any further synchronisation whether a kernel's bounded wait gave up.
@@ -253,6 +276,17 @@ int kp_cast(const void* in, void* out, long long n, int dtype_in, int dtype_out,
         kp_launch_pdl(cast_kernel<bf16, float>, dim3(g), dim3(256), 0, s, (const bf16*)in, (float*)out, (size_t)n);
     else
         return KP_ERR_BAD_ARG;
+    return kp_launch_status();
+}
+
+// n_words a multiple of 4, both buffers 16-byte aligned.  tok_src (may be null): n_tok token ids on the device that
+// go to words tok_off ... of dst (tok_off a multiple of 4) instead of what src holds there.
+int kp_step_tables(const void* src, void* dst, int n_words, const int* tok_src, int tok_off, int n_tok, void* stream) {
+    if (n_words <= 0 || (n_words & 3) || (tok_off & 3) || ((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) return KP_ERR_BAD_ARG;
+    if (tok_src != nullptr && (tok_off < 0 || n_tok < 0 || tok_off + n_tok > n_words)) return KP_ERR_BAD_ARG;
+    const int n4 = n_words / 4;
+    kp_launch_pdl(step_tables_kernel, dim3((n4 + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const int4*)src, (int4*)dst,
+                  n4, tok_src, tok_off, n_tok);
     return kp_launch_status();
 }
 

@@ -111,8 +111,11 @@ class _DecodeGraph:
                     raise RuntimeError(f"step tables {key!r}: '{name}' changed its size in a captured decode step")
                 self.host[o:o + m] = arr
 
-    def fill(self, runner, reqs: Sequence[Hashable], tokens: Optional[Sequence[int]]) -> None:
-        """Write this step's tables into the next staging buffer and start its copy."""
+    def fill(self, runner, reqs: Sequence[Hashable], tokens: Optional[Sequence[int]],
+             device_tokens: Optional[torch.Tensor] = None) -> None:
+        """Write this step's tables into the next staging buffer and bring them to the device (a kernel reads the
+        pinned buffer: cheaper between two graph launches than a copy engine's 2 KB), with ``device_tokens`` in
+        the tokens' place if given."""
         i = self.turn
         self.turn = (i + 1) % N_PINNED
         if self.events[i] is not None:
@@ -141,7 +144,7 @@ class _DecodeGraph:
         if self.part_layout:
             self._fill_part_tables(lens)
         np.copyto(self.pinned_np[i], a)
-        self.dev.copy_(self.pinned[i], non_blocking=True)
+        K.step_tables(self.pinned[i], self.dev, device_tokens, self.off["token_ids"])
         ev = self.events[i] or torch.cuda.Event()
         ev.record()
         self.events[i] = ev
@@ -211,9 +214,7 @@ class DecodeGraphs:
         self.clock += 1
         g.last_used = self.clock
         tokens = None if device_tokens is not None else [int(e.tokens[0]) for e in entries]
-        g.fill(r, reqs, tokens)
-        if device_tokens is not None:
-            g.ctx.token_ids.copy_(device_tokens)
+        g.fill(r, reqs, tokens, device_tokens)
         if g.graph is None:
             # run once eagerly (kernels get built, scratch gets its size), restore the state it changed, capture
             self._capture(g)

@@ -247,6 +247,21 @@ class StatusGather:
 
 # -------------------------------------------------------------------- rowwise
 
+def step_tables(src_pinned: torch.Tensor, dst: torch.Tensor, tokens: Optional[torch.Tensor] = None, tok_off: int = 0) -> None:
+    """The int32 tables of a captured step from their staging buffer in pinned host memory to the device buffer
+    ``dst`` by a kernel (the device reads the host buffer itself), and with them ``tokens`` (int32, on the device)
+    to words ``tok_off`` ... of ``dst``."""
+    if src_pinned.dtype != torch.int32 or not src_pinned.is_pinned() or src_pinned.numel() != dst.numel():
+        raise KernelError("step_tables: the source is an int32 tensor in pinned memory, as long as the destination")
+    _need(dst, "dst", torch.int32)
+    n_tok = 0
+    if tokens is not None:
+        _need(tokens, "tokens", torch.int32)
+        n_tok = tokens.numel()
+    _run("step_tables", load_library("rowwise").kp_step_tables, ctypes.c_void_p(src_pinned.data_ptr()), _ptr(dst), dst.numel(),
+         _ptr(tokens), tok_off, n_tok, STREAM)
+
+
 def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
     _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
     n, d = out.shape
