@@ -2,10 +2,11 @@
 
 One door for every product of the model; it picks the kernel by dtype and
 shape: float32 operands always run the CUDA-core float32 kernel (the true
-32-bit path); bfloat16 products of up to 64 rows run the weight-streaming
+32-bit path); bfloat16 products of up to 16 rows run the weight-streaming
 kernels (decode steps) except where the tcgen05 kernel was measured faster
 (``kernels.tc_pays_for_few_rows``), larger ones the tcgen05 tensor-core kernel
-(prompt portions).  The product is this package's own kernel in every case;
+(decode steps of 17 rows and more, where it cuts the product along K, and
+prompt portions).  The product is this package's own kernel in every case;
 no library matrix product is called.
 """
 from __future__ import annotations
