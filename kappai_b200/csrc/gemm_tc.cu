@@ -308,18 +308,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             // split over K: this part's sums of the whole accumulator (BN columns) go to this CTA's shared memory
             // (the ring is free: every MMA of the unit has completed), laid out [piece of 32 columns][float4 of
-            // the piece][row][4] so that a warp's rows lie one behind the other; the tile's CTAs -- a cluster --
+            // the piece][row of the tile][4] so that a warp's rows lie one behind the other; the tile's CTAs -- a cluster --
             // add them up below
             float4* mine = reinterpret_cast<float4*>(tiles);
+            const int R = min(TC_BM, p.M - m0);                          // rows of this tile
 #pragma unroll 1
             for (int c = half * 32; c < BN; c += 32 * TC_EPI_PER_Q) {
                 uint32_t r[32];
                 kp_tmem_ld32(lane_base + c, r);
                 if (m < p.M) {
-                    float4* dst = mine + (size_t)(c >> 5) * 8 * p.M + m;
+                    float4* dst = mine + (size_t)(c >> 5) * 8 * R + (m - m0);
 #pragma unroll
                     for (int j = 0; j < 8; j++)
-                        dst[(size_t)j * p.M] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                        dst[(size_t)j * R] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                                            __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
                 }
             }
@@ -342,10 +343,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (warp >= 2 && parts_ok) {
             const int tile = blockIdx.x / S, part = blockIdx.x - tile * S;
             const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * N_OUT_TILE;
-            const int n_vec = N_OUT_TILE / 32 * p.M * 8;                  // float4s of the tile's output
+            const int R = min(TC_BM, p.M - m0);                           // rows of this tile
+            const int n_vec = N_OUT_TILE / 32 * R * 8;                    // float4s of the tile's output
             const int lo = (int)((long long)n_vec * part / S), hi = (int)((long long)n_vec * (part + 1) / S);
             const uint32_t mine = kp_smem_u32(tiles);
-            const uint32_t up_off = (uint32_t)(BN / 64) * 8 * p.M * 16;   // bytes from a gate piece to its up piece
+            const uint32_t up_off = (uint32_t)(BN / 64) * 8 * R * 16;     // bytes from a gate piece to its up piece
             constexpr int NT = TC_EPI_PER_Q * 128;
             // VI float4s a thread at a time, the parts four by four: the loads of a round are all in flight
             // together (each is a trip to another SM), the sums still run in the order of the parts
@@ -381,8 +383,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const int idx = i0 + v * NT;
                     if (idx < hi) {
                         const float g4[4] = {g[v].x, g[v].y, g[v].z, g[v].w}, u4[4] = {up[v].x, up[v].y, up[v].z, up[v].w};
-                        const int piece = idx / (p.M * 8), rem = idx - piece * (p.M * 8);
-                        const int j4 = rem / p.M, row = rem - j4 * p.M;
+                        const int piece = idx / (R * 8), rem = idx - piece * (R * 8);
+                        const int j4 = rem / R, row = rem - j4 * R;
                         tc_finish<EPI, 4>(p, n_out, g4, u4, m0 + row, n0 + piece * 32 + j4 * 4);
                     }
                 }
@@ -396,6 +398,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // ------------------------------------------------------------------------------------------ host side
 #define TC_SMEM_KB 208                       // shared memory for the ring
+#ifndef TC_SPLIT_MAX_M_TILES
+#define TC_SPLIT_MAX_M_TILES 8               // rows of tiles up to which a product may be cut along K
+#endif
 #ifndef TC_SPLIT_COST_KB
 #define TC_SPLIT_COST_KB 64                  // what a split over K costs beside the operand reads, as KB brought into an SM
 #endif
@@ -558,18 +563,21 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
     a.splits = 1;
     a.kb_per_split = (K + TC_BK - 1) / TC_BK;
     a.a_rows = M >= TC_BM ? TC_BM : (M + 7) / 8 * 8;
-    if (m_tiles == 1 && M > 16 && split) {
+    if (m_tiles <= TC_SPLIT_MAX_M_TILES && M > 16 && split) {
+        // (the same holds for a few rows of tiles -- a prompt portion or decoded tokens beside one, 129 to 1024
+        // rows -- where the product has few tiles and a long K: 264 rows by 2048 x 5632 are 48 tiles of 88 k-blocks)
+        const int rows = M < TC_BM ? M : TC_BM;                          // rows of a tile
         const int n_kb = (K + TC_BK - 1) / TC_BK;
         long long best = -1;
         int best_bn = bn, best_sp = 1;
         for (int w = 256; w >= (lowest < 64 ? 64 : lowest); w /= 2) {
-            const int tiles = tiles_at(w);
+            const int tiles = tiles_at(w) * (int)m_tiles;
             const long long rounds = (tiles + sms - 1) / sms;
             int stages = 0;
             const size_t ring = tc_smem(a.a_rows, w, &stages) - 2048;
             for (int sp = 1; sp <= 8; sp++) {
                 if (sp > 1) {
-                    if (tiles * sp > sms || sp * 2 > n_kb || (size_t)M * w * 4 > ring) break;
+                    if (tiles * sp > sms || sp * 2 > n_kb || (size_t)rows * w * 4 > ring) break;
                     if (tiles > tc_max_clusters(w, epi, sp, a.a_rows)) continue;  // the clusters would not all run at once
                 }
                 const int kbs = (n_kb + sp - 1) / sp;
@@ -577,7 +585,7 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
                 long long cost = (sp == 1 ? rounds * n_kb : kbs) * (long long)(TC_BK * 2) * (w + a.a_rows);
                 if (sp > 1) {
                     // the sums that a CTA reads from the others come in over the same port
-                    cost += TC_SPLIT_COST_KB * 1024 + (long long)M * w * 4 * (sp - 1) / sp;
+                    cost += TC_SPLIT_COST_KB * 1024 + (long long)rows * w * 4 * (sp - 1) / sp;
                 }
                 if (best < 0 || cost < best) { best = cost; best_bn = w; best_sp = sp; }
             }

@@ -99,10 +99,47 @@ class _Tables:
         self.__dict__.update(kw)
 
 
+@dataclass
+class HostStep:
+    """A step's tables laid out on the host: one int32 array of 16-byte aligned pieces, and where each piece is."""
+
+    flat: np.ndarray                                   # int32, all pieces
+    offs: List[int]                                    # first word of piece i
+    sizes: List[int]                                   # words of piece i
+    n_rows: int
+    n_seg: int
+    n_out: int
+    host_cu_rows: List[int]
+    host_seg_pos: List[int]
+    host_seg_slot: List[int]
+    max_seg_len: int
+    max_context: int
+    decode_only: bool
+    paged: Dict[Hashable, tuple]                       # group -> (index of its block-table piece, its shape, page size)
+    part_tables: list                                  # (key, [(name, index of the piece)], scalars)
+
+    def signature(self) -> tuple:
+        """Everything that a launch of the step may depend on beside the tables' contents: two steps with the same
+        signature launch the same kernels with the same arguments, given the same addresses."""
+        return (self.n_rows, self.n_seg, self.n_out, self.max_seg_len, self.max_context, self.decode_only,
+                tuple(self.sizes), tuple((gk, shape) for gk, (_, shape, _) in self.paged.items()),
+                tuple((key, tuple(sorted(sc.items()))) for key, _, sc in self.part_tables))
+
+
 def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int], device: torch.device,
                        vocab_size: int, max_positions: int, table_builders: Optional[Dict[Hashable, object]] = None
                        ) -> StepContext:
-    """Validate the segments on the host and upload their tables in one copy.
+    """Validate the segments on the host and upload their tables in one copy."""
+    return upload_step(lay_out_step(segments, groups, vocab_size, max_positions, table_builders), device)
+
+
+def lay_out_step(segments: Sequence[Segment], groups: Dict[Hashable, int], vocab_size: int, max_positions: int,
+                 table_builders: Optional[Dict[Hashable, object]] = None, round_blocks=None, round_context=None
+                 ) -> HostStep:
+    """Validate the segments and lay their tables out on the host.
+
+    ``round_blocks`` / ``round_context`` (for steps that may be captured): the width of the block tables and the
+    step's largest context are rounded up by them, so that steps that differ a little share a signature.
 
     ``groups`` maps each page group to its page size.  Everything that could
     make a kernel read or write out of bounds is refused here, before any
@@ -168,6 +205,8 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
     paged_host = {}
     for gk, page_size in groups.items():
         max_blocks = max(1, max(len(s.block_tables.get(gk, ())) for s in segments))
+        if round_blocks is not None:
+            max_blocks = int(round_blocks(max_blocks))
         bt = np.full((n_seg, max_blocks), -1, np.int32)
         sm = np.empty(n_rows, np.int32)
         r = 0
@@ -187,27 +226,46 @@ def build_step_context(segments: Sequence[Segment], groups: Dict[Hashable, int],
         parts.append(bt.reshape(-1))
         parts.append(sm)
 
-    sizes = [p.size for p in parts]
+    sizes = [int(p.size) for p in parts]
     offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])])     # 16-byte aligned pieces
-    flat = torch.empty(int(offs[-1]), dtype=torch.int32, pin_memory=device.type == "cuda")
-    fl = flat.numpy()
+    flat = np.zeros(int(offs[-1]), dtype=np.int32)
     for p, o in zip(parts, offs[:-1]):
-        fl[o:o + p.size] = p
-    dev = flat.to(device, non_blocking=True)
-    piece = lambda i: dev[int(offs[i]):int(offs[i]) + sizes[i]]
+        flat[o:o + p.size] = p
+    max_context = max(s.pos_start + len(s.tokens) for s in segments)
+    if round_context is not None:
+        max_context = int(round_context(max_context))
+    return HostStep(flat=flat, offs=[int(o) for o in offs[:-1]], sizes=sizes, n_rows=n_rows, n_seg=n_seg,
+                    n_out=len(logit_rows), host_cu_rows=cu_rows.tolist(), host_seg_pos=seg_pos.tolist(),
+                    host_seg_slot=seg_slot.tolist(), max_seg_len=host_segs.max_seg_len, max_context=max_context,
+                    decode_only=host_segs.decode_only, paged=paged_host, part_tables=part_tables)
+
+
+def upload_step(host: HostStep, device: torch.device, into: Optional[torch.Tensor] = None) -> StepContext:
+    """The device's view of a laid-out step.  Without ``into`` the tables travel now, in one copy from pinned
+    memory; with it (an int32 device buffer as long as ``host.flat``) the context's tensors are views of that
+    buffer and the caller brings the tables there (a captured step: the same buffer every time)."""
+    if into is None:
+        flat = torch.empty(host.flat.size, dtype=torch.int32, pin_memory=device.type == "cuda")
+        flat.numpy()[:] = host.flat
+        dev = flat.to(device, non_blocking=True)
+    else:
+        if into.dtype != torch.int32 or into.numel() != host.flat.size:
+            raise BatchError("upload_step: the buffer does not fit the step's tables")
+        flat, dev = None, into
+    offs, sizes = host.offs, host.sizes
+    piece = lambda i: dev[offs[i]:offs[i] + sizes[i]]
 
     paged = {}
-    for gk, (i, shape, page_size) in paged_host.items():
+    for gk, (i, shape, page_size) in host.paged.items():
         paged[gk] = PagedView(piece(i).view(shape), piece(i + 1), page_size)
     tables = {key: _Tables(**{name: piece(i) for name, i in names}, **scalars)
-              for key, names, scalars in part_tables}
+              for key, names, scalars in host.part_tables}
     ctx = StepContext(
-        n_rows=n_rows, n_seg=n_seg, token_ids=piece(0), positions=piece(1), row_seg=piece(2), cu_rows=piece(3),
-        seg_pos=piece(4), seg_slot=piece(5), logit_rows=piece(6), n_out=len(logit_rows), paged=paged,
-        host_cu_rows=cu_rows.tolist(), host_seg_pos=seg_pos.tolist(), host_seg_slot=seg_slot.tolist(),
-        max_seg_len=host_segs.max_seg_len,
-        max_context=max(s.pos_start + len(s.tokens) for s in segments),
-        decode_only=host_segs.decode_only, tables=tables)
+        n_rows=host.n_rows, n_seg=host.n_seg, token_ids=piece(0), positions=piece(1), row_seg=piece(2), cu_rows=piece(3),
+        seg_pos=piece(4), seg_slot=piece(5), logit_rows=piece(6), n_out=host.n_out, paged=paged,
+        host_cu_rows=host.host_cu_rows, host_seg_pos=host.host_seg_pos, host_seg_slot=host.host_seg_slot,
+        max_seg_len=host.max_seg_len, max_context=host.max_context,
+        decode_only=host.decode_only, tables=tables)
     ctx._pinned = flat          # keep the pinned buffer alive until the copy has run
-    ctx.h2d_bytes = flat.numel() * 4
+    ctx.h2d_bytes = host.flat.size * 4
     return ctx

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from ..ops import kernels as K
-from .batch import PagedView, StepContext, StepSegments, _Tables
+from .batch import PagedView, StepContext, StepSegments, _Tables, upload_step
 
 N_PINNED = 4          # staging buffers in rotation, so a refill never overtakes a copy in flight
 
@@ -150,6 +150,35 @@ class _DecodeGraph:
         self.events[i] = ev
 
 
+class _StepGraph:
+    """A captured step of any shape (prompt portions, portions beside decoded tokens): its tables live in one static
+    device buffer, laid out as :func:`~kappai_b200.engine.batch.lay_out_step` lays them out; a later step with
+    the same signature brings its tables there and replays."""
+
+    def __init__(self, runner, host):
+        self.dev = torch.zeros(host.flat.size, dtype=torch.int32, device=runner.device)
+        self.pinned = [torch.zeros(host.flat.size, dtype=torch.int32, pin_memory=True) for _ in range(N_PINNED)]
+        self.pinned_np = [p.numpy() for p in self.pinned]
+        self.events = [None] * N_PINNED
+        self.turn = 0
+        self.ctx = upload_step(host, runner.device, into=self.dev)
+        self.last_used = 0
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.n_kernels = 0
+
+    def fill(self, host, device_tokens: Optional[torch.Tensor] = None) -> None:
+        i = self.turn
+        self.turn = (i + 1) % N_PINNED
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        np.copyto(self.pinned_np[i], host.flat)
+        K.step_tables(self.pinned[i], self.dev, device_tokens, host.offs[0])
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
 class DecodeGraphs:
     """Captured decode steps of one :class:`ModelRunner`."""
 
@@ -157,7 +186,11 @@ class DecodeGraphs:
         self.runner = runner
         self.graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self.seen: Dict[Tuple[int, int], int] = {}     # how often a shape has come without being captured
+        self.step_graphs: Dict[tuple, _StepGraph] = {}   # captured steps of other shapes, by their tables' signature
+        self.step_last, self.step_run = None, 0          # the signature of the last such step, and how often in a row
+        self.n_step_captures = 0
         self.pool = None                               # the captures' shared memory pool
+        self.capture_stream = None                     # the stream that captures run on
         self.clock = 0                                 # counts the steps: a graph remembers when it last ran
         self.n_evicted = 0
         self.n_captures = 0
@@ -225,7 +258,61 @@ class DecodeGraphs:
         r.last_h2d_bytes = g.ctx.h2d_bytes
         return g.logits
 
-    def _capture(self, g: _DecodeGraph) -> None:
+    # Steps that are not pure decode (a prompt portion, portions beside decoded tokens) launch some 130 kernels
+    # from Python, about 2 ms of host time, which is more than the device needs for less than a thousand rows.
+    # Where the same shape comes again -- a long prompt fed in equal portions, beside the same decoding requests --
+    # the step is captured like a decode step: by its tables' signature, with the block tables' width and the
+    # largest context rounded up so that the signature holds while the prompt grows.
+    # Measured (LFM2-1.2B shape, 8 decoded tokens beside a prompt portion): 72 rows 2.19 -> 1.36 ms a step, 264 rows
+    # 2.29 -> 2.04 ms (there the device itself needs 2 ms); a capture costs about 23 ms.
+    STEP_MAX_ROWS = 160            # larger steps keep the device busy for about as long as the host needs to launch them
+    STEP_CAPTURE_AFTER = 3         # times in a row: the shape must look like staying
+
+    def round_blocks(self, blocks: int) -> int:
+        return self.width_for(blocks)
+
+    @staticmethod
+    def round_context(tokens: int) -> int:
+        c = 2048
+        while c < tokens:
+            c *= 2
+        return c
+
+    def wants_step(self, host) -> bool:
+        """Should this step run from a captured graph: one that exists, or one that is due because the same shape
+        has now come STEP_CAPTURE_AFTER times in a row (a shape that merely comes back now and then, like a
+        prompt of some length, is not worth a capture)."""
+        if host.n_rows > self.STEP_MAX_ROWS:
+            self.step_last, self.step_run = None, 0
+            return False
+        key = host.signature()
+        self.step_run = self.step_run + 1 if key == self.step_last else 1
+        self.step_last = key
+        g = self.step_graphs.get(key)
+        return (g is not None and g.graph is not None) or self.step_run >= self.STEP_CAPTURE_AFTER
+
+    def run_step(self, host, device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Run a laid-out step from its captured graph (captured now if it is not yet).  Returns the static logits
+        buffer (valid until the next step of this signature), None if the step wants none."""
+        r = self.runner
+        key = host.signature()
+        g = self.step_graphs.get(key)
+        if g is None:
+            g = _StepGraph(r, host)
+            self.step_graphs[key] = g
+        self.clock += 1
+        g.last_used = self.clock
+        g.fill(host, device_tokens)
+        if g.graph is None:
+            self._capture(g)
+        else:
+            g.graph.replay()
+            K.LAUNCHES[0] += g.n_kernels
+            self.n_replays += 1
+        r.last_h2d_bytes = g.ctx.h2d_bytes
+        return g.logits
+
+    def _capture(self, g) -> None:
         r = self.runner
         # the eager warm-up run changes fixed-size state (and rewrites this step's keys, harmlessly);
         # keep a copy of the state tensors and put them back before the captured run replays the step
@@ -241,15 +328,25 @@ class DecodeGraphs:
         before = K.LAUNCHES[0]
         # Python's cycle collector must not run inside the capture: a dead cycle may hold captured graphs of
         # an engine that is gone, and destroying a CUDA graph while a stream captures invalidates the capture.
-        # So the dead cycles are collected now and the collector rests until the capture has ended.
-        gc.collect()
+        # So the collector rests until the capture has ended.  The capture is begun and ended by hand, on a
+        # stream of its own: torch.cuda.graph() would first synchronise the device, run a full collection and
+        # empty the allocator's cache, which is most of the 40 to 100 ms that a capture took with it.
         gc_was_on = gc.isenabled()
         gc.disable()
         try:
             if self.pool is None:
                 self.pool = torch.cuda.graph_pool_handle()
-            with torch.cuda.graph(graph, pool=self.pool):
-                g.logits = r.model.forward(g.ctx, r.storage.views)
+            if self.capture_stream is None:
+                self.capture_stream = torch.cuda.Stream()
+            cur = torch.cuda.current_stream()
+            self.capture_stream.wait_stream(cur)
+            with torch.cuda.stream(self.capture_stream):
+                graph.capture_begin(pool=self.pool)
+                try:
+                    g.logits = r.model.forward(g.ctx, r.storage.views)
+                finally:
+                    graph.capture_end()
+            cur.wait_stream(self.capture_stream)
         finally:
             if gc_was_on:
                 gc.enable()
@@ -257,13 +354,16 @@ class DecodeGraphs:
         for t, s in zip(states, saved):
             t.copy_(s)
         g.graph = graph
-        self.n_captures += 1
-        captured = [k for k, v in self.graphs.items() if v.graph is not None]
+        if isinstance(g, _StepGraph):
+            self.n_step_captures += 1
+        else:
+            self.n_captures += 1
+        captured = [(d, k) for d in (self.graphs, self.step_graphs) for k, v in d.items() if v.graph is not None]
         if len(captured) > self.MAX_GRAPHS:
             # (no kernel of the oldest graph can still be running behind the replays that came after it on this stream)
-            oldest = min((k for k in captured if self.graphs[k] is not g), key=lambda k: self.graphs[k].last_used)
+            d, oldest = min(((d, k) for d, k in captured if d[k] is not g), key=lambda dk: dk[0][dk[1]].last_used)
             torch.cuda.current_stream().synchronize()
-            del self.graphs[oldest]
+            del d[oldest]
             self.seen.pop(oldest, None)
             self.n_evicted += 1
         graph.replay()

@@ -25,7 +25,7 @@ from ..cache.storage import CacheStorage
 from ..config.registry import load_config
 from ..parts.base import BuildEnv
 from ..weights.loader import load_weights
-from .batch import Segment, StepContext, build_step_context
+from .batch import Segment, StepContext, lay_out_step, upload_step
 from ..ops import kernels as K
 from ..ops.kernels import MAX_STEP_ROWS
 from .graphs import DecodeGraphs
@@ -180,8 +180,8 @@ class ModelRunner:
             # cover positions the request will need anyway and are freed with it
             raise
 
-    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
-        """Reserve cache for the entries and build the step's tables."""
+    def _lay_out(self, entries: Sequence[StepEntry], capturable: bool):
+        """Reserve cache for the entries and lay the step's tables out on the host."""
         plan = self._reserve(entries)
         segs = []
         for e, (req, old_len, new_len) in zip(entries, plan):
@@ -191,9 +191,16 @@ class ModelRunner:
                 block_tables={gk: self.cache.block_table(req, gk) for gk in self.group_page_size},
                 token_slots={gk: self.cache.token_slots(req, gk, old_len, len(e.tokens))
                              for gk in self.group_page_size}))
-        ctx = build_step_context(segs, self.group_page_size, self.device, self.vocab_size, self.max_model_len,
-                                 self.model.table_builders)
-        return ctx, [(req, new_len) for req, _, new_len in plan]
+        g = self.graphs if capturable else None
+        host = lay_out_step(segs, self.group_page_size, self.vocab_size, self.max_model_len, self.model.table_builders,
+                            round_blocks=g.round_blocks if g else None,
+                            round_context=(lambda t: min(self.max_model_len, g.round_context(t))) if g else None)
+        return host, [(req, new_len) for req, _, new_len in plan]
+
+    def prepare(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+        """Reserve cache for the entries and build the step's tables."""
+        host, after = self._lay_out(entries, False)
+        return upload_step(host, self.device), after
 
     def run(self, ctx: StepContext) -> Optional[torch.Tensor]:
         return self.model.forward(ctx, self.storage.views, self.observer)
@@ -216,11 +223,19 @@ class ModelRunner:
             for req, _, new_len in plan:
                 self.cache.advance(req, new_len)
             return logits
-        ctx, after = self.prepare(entries)
-        if device_tokens is not None:
-            ctx.token_ids.copy_(device_tokens)
-        self.last_h2d_bytes = ctx.h2d_bytes
-        logits = self.run(ctx)
+        # (a decode step that is not captured yet runs as it is; other shapes may be captured as they are laid out)
+        capturable = (self.graphs is not None and self.model.graph_safe and self.observer is None
+                      and K.TIMER[0] is None and not DecodeGraphs.eligible(entries))
+        host, after = self._lay_out(entries, capturable)
+        if capturable and self.graphs.wants_step(host):
+            # a shape that has come before: from its captured graph (see DecodeGraphs.run_step)
+            logits = self.graphs.run_step(host, device_tokens)
+        else:
+            ctx = upload_step(host, self.device)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens)
+            self.last_h2d_bytes = ctx.h2d_bytes
+            logits = self.run(ctx)
         for req, new_len in after:
             self.cache.advance(req, new_len)
         return logits

@@ -83,7 +83,7 @@ def test_gemm_tc_rows_do_not_depend_on_m():
     K, N = 520, 300
     a = dev(rt(rng.standard_normal((700, K)), DT), DT)
     w = dev(rt(rng.standard_normal((N, K)) / 20, DT), DT)
-    full = Kn.gemm_tc(a, w, torch.empty((700, N), device="cuda"))
+    full = Kn.gemm_tc(a, w, torch.empty((700, N), device="cuda"), split=False)
     for lo, hi in ((0, 65), (130, 400), (699, 700), (5, 133)):
         part = Kn.gemm_tc(a[lo:hi], w, torch.empty((hi - lo, N), device="cuda"), split=False)
         assert torch.equal(part, full[lo:hi]), (lo, hi)

@@ -94,8 +94,26 @@ def wide_model(tmp_path_factory):
     return d, PlainLfm2(d)
 
 
+@pytest.fixture(scope="module")
+def wide_bf16_bound(wide_model):
+    """The bfloat16 bound at this width, measured as at the LFM2-1.2B shape (tolerances.bf16_bounds_from_ideal): the
+    largest error of a row that an ideal implementation with the engine's 16-bit storage points makes, as a fraction
+    of the row's standard deviation, times BF16_IDEAL_FACTOR.  (At width 512 the ideal error alone is 4.4 to 4.8 %:
+    the 5 % of the tiny models' bound leaves no room for another order of summation.)"""
+    from plain_lfm2 import PlainLfm2
+    from tolerances import bf16_bounds_from_ideal
+    d, plain = wide_model
+    emulated = PlainLfm2(d, storage="bfloat16")
+    rng = np.random.default_rng(356)
+    big = 0.0
+    for _ in range(6):
+        s = rng.integers(0, WIDE_CONFIG["vocab_size"], 40).tolist()
+        big = max(big, bf16_bounds_from_ideal(plain.logits(s), emulated.logits(s))[0])
+    return big
+
+
 @pytest.mark.parametrize("n_req", [3, 20, 40, 64, 100, 256])
-def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model):
+def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model, wide_bf16_bound):
     """Width 512 (a multiple of the bulk-copy kernel's 512-column chunks): decode steps of 3, 20, 40 and 64
     requests run the weight-streaming products in all their forms (half tile, two, three and four m-tiles,
     16-row weight tiles) inside the model, from captured graphs; steps of 100 and 256 requests run every product
@@ -115,7 +133,8 @@ def test_decode_batches_at_a_width_the_streaming_kernels_take(n_req, wide_model)
         entries = [StepEntry(i, [s[L + step]], [0]) for i, (s, L) in enumerate(zip(seqs, lens))]
         lg = r.step(entries).float().cpu().numpy()
         for i, L in enumerate(lens):
-            assert np.abs(lg[i] - refs[i][L + step]).max() <= tol_for("bfloat16", refs[i]), (n_req, step, i)
+            ref = refs[i][L + step]
+            assert np.abs(lg[i] - ref).max() <= wide_bf16_bound * float(ref.std()), (n_req, step, i)
     assert r.graphs.n_replays >= 2
     assert K.tc_status() == 0 and K.stream_status() == 0
 
@@ -185,8 +204,8 @@ def test_captured_graphs_share_a_pool_and_the_oldest_goes(wide_model):
     seqs = [rng.integers(0, V, 40).tolist() for _ in range(4)]
     refs = [plain.logits(s) for s in seqs]
     for i, s in enumerate(seqs):
-        r.step([StepEntry(i, s[:5], [])])
-    fed = [5] * 4
+        r.step([StepEntry(i, s[:5 + i], [])])        # (prompts of different lengths: no shape comes thrice in a row)
+    fed = [5 + i for i in range(4)]
 
     def decode(which, steps):
         for _ in range(steps):
@@ -202,3 +221,36 @@ def test_captured_graphs_share_a_pool_and_the_oldest_goes(wide_model):
     assert r.graphs.n_captures == 3 and r.graphs.n_evicted == 1 and (4, 8) not in r.graphs.graphs
     decode([0, 1, 2, 3], 3)          # and is captured again when it comes back
     assert r.graphs.n_captures == 4 and r.graphs.n_evicted == 2
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_a_prompt_fed_in_equal_portions_beside_decoding_requests_runs_from_a_captured_step(wide_model, dtype):
+    """Steps that are not pure decode are captured too where the same shape comes again: two requests decode while
+    a third's prompt is fed 16 tokens a step.  The captured steps must give the bits of the steps launched kernel
+    by kernel (a second runner without graphs), replays must have happened, and the logits agree with the plain
+    model; the portions cross pages and the block table's width grows under way."""
+    from kappai_b200 import ModelRunner, StepEntry
+    d, plain = wide_model
+    rng = np.random.default_rng(12)
+    V = WIDE_CONFIG["vocab_size"]
+    seqs = [rng.integers(0, V, 60).tolist() for _ in range(2)] + [rng.integers(0, V, 16 * 14).tolist()]
+    refs = [plain.logits(s) for s in seqs]
+
+    def run(graphs):
+        r = ModelRunner(d, dtype=dtype, max_tokens=1024, max_requests=4, page_size=16, max_model_len=512, cuda_graphs=graphs)
+        for i in (0, 1):
+            r.step([StepEntry(i, seqs[i][:20], [])])
+        out = []
+        for t in range(14):
+            ent = [StepEntry(i, [seqs[i][20 + t]], [0]) for i in (0, 1)]
+            ent.append(StepEntry(2, seqs[2][16 * t:16 * t + 16], [3, 15]))
+            out.append(r.step(ent).float().cpu().numpy().copy())
+        return out, r
+
+    eager, _ = run(False)
+    captured, r = run(True)
+    assert r.graphs.n_replays >= 6 and r.graphs.n_step_captures >= 1, (r.graphs.n_replays, r.graphs.n_step_captures)
+    for t, (a, b) in enumerate(zip(eager, captured)):
+        assert np.array_equal(a, b), f"step {t}: the captured step and the eager step differ"
+        for j, (i, pos) in enumerate(((0, 20 + t), (1, 20 + t), (2, 16 * t + 3), (2, 16 * t + 15))):
+            assert np.abs(a[j] - refs[i][pos]).max() <= tol_for(dtype, refs[i]), (t, i, pos)
