@@ -151,6 +151,7 @@ def lay_out_step(segments: Sequence[Segment], groups: Dict[Hashable, int], vocab
         raise BatchError("a step needs at least one segment")
     seen = set()
     n_rows = 0
+    token_arrays = []
     for s in segments:
         if s.req in seen:
             raise BatchError(f"request {s.req!r} appears twice in one step")
@@ -160,9 +161,11 @@ def lay_out_step(segments: Sequence[Segment], groups: Dict[Hashable, int], vocab
         if s.pos_start < 0 or s.pos_start + len(s.tokens) > max_positions:
             raise BatchError(f"request {s.req!r}: positions {s.pos_start}..{s.pos_start + len(s.tokens) - 1} "
                              f"exceed the engine's limit of {max_positions}")
-        for t in s.tokens:
-            if not (0 <= int(t) < vocab_size):
-                raise BatchError(f"request {s.req!r}: token id {t} outside the vocabulary of {vocab_size}")
+        ids = np.asarray(s.tokens, dtype=np.int64)
+        if ids.min() < 0 or ids.max() >= vocab_size:
+            t = int(ids[(ids < 0) | (ids >= vocab_size)][0])
+            raise BatchError(f"request {s.req!r}: token id {t} outside the vocabulary of {vocab_size}")
+        token_arrays.append(ids)
         for w in s.want:
             if not (0 <= int(w) < len(s.tokens)):
                 raise BatchError(f"request {s.req!r}: wanted index {w} outside its {len(s.tokens)} tokens")
@@ -179,7 +182,7 @@ def lay_out_step(segments: Sequence[Segment], groups: Dict[Hashable, int], vocab
     r = 0
     for i, s in enumerate(segments):
         n = len(s.tokens)
-        token_ids[r:r + n] = np.asarray(s.tokens, dtype=np.int64)
+        token_ids[r:r + n] = token_arrays[i]
         positions[r:r + n] = np.arange(s.pos_start, s.pos_start + n)
         row_seg[r:r + n] = i
         seg_pos[i], seg_slot[i] = s.pos_start, s.slot

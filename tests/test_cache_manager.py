@@ -136,3 +136,24 @@ def test_random_orders_keep_every_page_accounted(seed):
         m.free(r)
     m.check()
     assert all(p.n_free == p.n_pages for p in m.pools.values()) and m.slots.n_free == 5
+
+
+def test_token_slots_of_a_long_portion_are_those_of_its_positions_one_by_one():
+    """Portions of more than 32 tokens take their slots by arrays: the same slots as asked one by one, from any
+    start, across page edges; a released page in the range is refused by its first position."""
+    m = CacheManager({"full": (64, 8, None), "win": (64, 8, 40)}, n_slots=2)
+    m.admit("a")
+    m.extend("a", 300)
+    rnd = random.Random(3)
+    for _ in range(50):
+        start = rnd.randrange(0, 250)
+        n = rnd.randrange(33, 300 - start + 1) if 300 - start > 33 else 33
+        n = min(n, 300 - start)
+        one_by_one = [m.token_slots("a", "full", p, 1)[0] for p in range(start, start + n)]
+        assert m.token_slots("a", "full", start, n) == one_by_one
+    m.advance("a", 300)                            # window 40 at next position 300: blocks before 261 // 8 are behind
+    first_kept = next(i for i, p in enumerate(m.block_table("a", "win")) if p != RELEASED) * 8
+    assert m.token_slots("a", "win", first_kept, 300 - first_kept) == \
+        [m.token_slots("a", "win", p, 1)[0] for p in range(first_kept, 300)]
+    with pytest.raises(CacheError, match=f"position {first_kept - 8} "):
+        m.token_slots("a", "win", first_kept - 8, 40)
