@@ -448,11 +448,12 @@ def run_timeline(model_dir, a, rng) -> int:
     step = ks[per_step:2 * per_step + 1]
     # the names of the captured step's launches, then the sampler's; only if they account for every launch seen
     n_sampling = sum(1 for k in step[:-1] if k["lib"] == "sampling")
-    in_graph = per_step - n_sampling
+    in_graph = per_step - n_sampling - 1                  # (one launch before the graph brings the step's tables)
     print(f"launches: {len(ks)} in three steps, {n_sampling} of the sampler a step, {len(names or [])} names logged",
           file=sys.stderr)
     if names is not None and in_graph > 0 and len(names) >= in_graph:
-        names = names[-in_graph:] + ["argmax"] * n_sampling      # (the capturing call runs the step more than once: the last run)
+        # (the capturing call runs the step more than once: the last run)
+        names = ["step_tables"] + names[-in_graph:] + ["argmax"] * n_sampling
     else:
         names = None
     span = step[-1]["waited_first"] - step[0]["waited_first"]     # from this step's first kernel to the next step's
