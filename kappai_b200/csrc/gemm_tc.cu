@@ -26,7 +26,8 @@
 // matching BN/2 up rows (two TMA boxes into one tile), so accumulator columns c and BN/2 + c are the gate and
 // up of one output column: the epilogue writes silu(gate) * up.
 //
-// Split over K (17 to 128 rows: one row of tiles): the product is cut along K into `splits` parts, the unit of
+// Split over K (17 to 1024 rows: up to eight rows of tiles, where that brings fewer bytes into the busiest SM): the
+// product is cut along K into `splits` parts, the unit of
 // work being (tile, part), all units in one round over the SMs and the parts of a tile one thread-block cluster.
 // Every CTA leaves the float32 sums of its unit in its own shared memory (the ring is free by then); after the
 // cluster's barrier each adds up its share of the tile, reading the other CTAs' sums over the cluster's shared
@@ -518,7 +519,7 @@ static int tc_max_clusters(int bn, int epi, int cluster, int a_rows) {
 extern "C" {
 
 // epi: 0 store bf16, 1 store f32, 2 accumulate into f32, 3 SwiGLU (W = [gate; up], N = 2*ff, output [M, ff] bf16).
-// split: products of 17 to 128 rows may be cut along K (0: never).
+// split: products of 17 to 1024 rows may be cut along K (0: never).
 int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float* bias, void* C, int ldc, int M, int N,
                      int K, int epi, int split, void* stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -554,7 +555,7 @@ int kp_gemm_tc_split(const void* A, int lda, const void* W, int ldw, const float
         bn = 256;
         while (bn > lowest && tiles_at(bn / 2) <= sms) bn /= 2;
     }
-    // 17 to 128 rows (one row of tiles): what bounds the product is the bytes that the busiest SM brings in, about
+    // 17 to 128 rows (one row of tiles; for more see below): what bounds the product is the bytes that the busiest SM brings in, about
     // 45 GB/s an SM whatever the source -- its share of W and, for every tile, all the rows of A.  Unsplit, a
     // narrow tile reads A once for a few rows of W (64 rows by 2048 x 5632 in 32-row tiles: 720 KB of A for 360 KB
     // of W) and wide tiles leave SMs idle.  So the product is cut along K as well: (tile width, parts) is chosen

@@ -601,7 +601,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             accumulate: bool = False, swiglu: bool = False, split: bool = True) -> torch.Tensor:
     """out = a @ w.T (+ bias) on the tcgen05 tensor cores (TMA-fed, accumulator in tensor memory); with
     ``swiglu`` ``w`` holds gate rows then up rows and out = silu(gate) * up.  With ``split`` a product of 17 to
-    128 rows is cut along K where that brings fewer bytes into the busiest SM (the parts of a tile are a
+    1024 rows is cut along K where that brings fewer bytes into the busiest SM (the parts of a tile are a
     thread-block cluster and are added in a fixed order)."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(w, "w", torch.bfloat16, contiguous=False)
     _need(out, "out", contiguous=False)
