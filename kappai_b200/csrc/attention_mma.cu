@@ -318,7 +318,7 @@ __host__ __device__ constexpr size_t ar_stage_bytes() { return (size_t)2 * AR_NW
 template <int HD>
 static size_t ar_smem_bytes() {
     return 1024 + AR_STAGES * ar_stage_bytes<HD>() + AR_STAGES * sizeof(ArMeta) + 2 * AR_STAGES * 8 +
-           AR_GROUPS * sizeof(float) * (AR_NW * AM_RMAX * HD + 2 * AR_NW * AM_RMAX) + 16;
+           AR_GROUPS * sizeof(float) * (AR_NW * AM_RMAX * HD + 2 * AR_NW * AM_RMAX) + 32;
 }
 
 template <int HD>
@@ -335,12 +335,14 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
     ArMeta* metas = reinterpret_cast<ArMeta*>(base + AR_STAGES * STAGE);
     uint64_t* full = reinterpret_cast<uint64_t*>(metas + AR_STAGES);
     uint64_t* empty = full + AR_STAGES;
-    float* scratch = reinterpret_cast<float*>(empty + AR_STAGES);       // [group]: wO [NW][RMAX][HD], wm, wl [NW][RMAX]
+    volatile int* gave_up = reinterpret_cast<volatile int*>(empty + AR_STAGES);   // [group, padded to 4]: a warp's wait ran out
+    float* scratch = reinterpret_cast<float*>(empty + AR_STAGES) + 4;   // [group]: wO [NW][RMAX][HD], wm, wl [NW][RMAX]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int R = H / G;
 
     if (tid == 0) {
         for (int s = 0; s < AR_STAGES; s++) { kp_mbar_init(&full[s], 1); kp_mbar_init(&empty[s], AR_NW); }
+        for (int g2 = 0; g2 < 4; g2++) gave_up[g2] = 0;
         kp_mbar_init_fence();
     }
     __syncthreads();
@@ -437,10 +439,13 @@ attn_split_ring_kernel(const __grid_constant__ CUtensorMap tmC, const bf16* __re
     auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "n"(AR_NW * 32) : "memory"); };
     for (int k = grp;; k += AR_GROUPS) {
         const int s = k % AR_STAGES;
+        // The four warps of the group leave the loop together or not at all (the group's barriers below count all
+        // of them): a warp whose wait ran out says so, and all of them look after a barrier.
         if (!kp_mbar_wait_bounded(&full[s], (k / AR_STAGES) & 1)) {
-            if (lane == 0) atomicExch(&g_attn_status, 1);
-            break;
+            if (lane == 0) { atomicExch(&g_attn_status, 1); gave_up[grp] = 1; }
         }
+        group_sync();
+        if (gave_up[grp]) break;
         const ArMeta me = metas[s];
         if (me.row < 0) break;
         unsigned char* st = base + (size_t)s * STAGE;
